@@ -1,0 +1,247 @@
+"""Cache manager: pages of keys and values with a block table per request, one
+pool per group of layers with the same needs, and slots of fixed-size state.
+
+The reference gives every batch slot a static range of page ids and never shares
+pages between slots (batchspec/backends/utils/paging.py:196,232;
+backends/base/page_table.py:55-137), doing the arithmetic with device tensors.
+Here all bookkeeping is on the host: a pool is a LIFO free list shared by all
+requests, a request holds ceil(len / page_size) table entries per group (none when
+empty), finished requests' pages go back to the list and are handed out again, and
+a windowed group also gives back pages that the window has passed (their table
+entries become -1; no kernel reads them).
+
+Nothing is zeroed on reuse: kernels never read past a request's length.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..parts.base import CacheSpec, StateSpec
+
+
+class OutOfPages(RuntimeError):
+    """A reservation needs more pages than a pool has free."""
+
+
+class PagePool:
+    """Free list of page ids 0..num_pages-1.  ``allocate`` pops, ``free`` pushes;
+    both check that no page is handed out twice or returned twice."""
+
+    def __init__(self, num_pages: int):
+        if num_pages <= 0:
+            raise ValueError("a page pool needs at least one page")
+        self.num_pages = int(num_pages)
+        self._free: List[int] = list(range(self.num_pages - 1, -1, -1))
+        self._held = [False] * self.num_pages
+        self.high_water = 0
+
+    @property
+    def num_free(self) -> int:
+        return len(self._free)
+
+    @property
+    def num_held(self) -> int:
+        return self.num_pages - len(self._free)
+
+    def allocate(self, n: int) -> List[int]:
+        if n > len(self._free):
+            raise OutOfPages(f"need {n} pages, {len(self._free)} of {self.num_pages} are free")
+        out = [self._free.pop() for _ in range(n)]
+        for p in out:
+            assert not self._held[p], f"page {p} handed out twice"
+            self._held[p] = True
+        self.high_water = max(self.high_water, self.num_held)
+        return out
+
+    def free(self, pages: Sequence[int]) -> None:
+        for p in pages:
+            if not (0 <= p < self.num_pages) or not self._held[p]:
+                raise RuntimeError(f"page {p} freed but not held")
+            self._held[p] = False
+            self._free.append(p)
+
+
+class StateSlots:
+    """Ids 0..n-1 for per-request state of fixed size."""
+
+    def __init__(self, n: int):
+        self.n = int(n)
+        self._free = list(range(self.n - 1, -1, -1))
+        self._held = [False] * self.n
+
+    @property
+    def num_free(self) -> int:
+        return len(self._free)
+
+    def take(self) -> int:
+        if not self._free:
+            raise OutOfPages(f"all {self.n} request slots are in use")
+        s = self._free.pop()
+        self._held[s] = True
+        return s
+
+    def give(self, s: int) -> None:
+        if not (0 <= s < self.n) or not self._held[s]:
+            raise RuntimeError(f"slot {s} returned but not held")
+        self._held[s] = False
+        self._free.append(s)
+
+
+@dataclass
+class CacheGroup:
+    """Layers whose mixers asked for the same thing share a pool and block tables."""
+    spec: CacheSpec
+    page_size: int
+    pool: PagePool
+    runs: List[int] = field(default_factory=list)        # indices into the model's order
+    pages: Optional[torch.Tensor] = None                  # [len(runs), num_pages, 2, page_size * entry_elems]
+
+    @property
+    def entry_elems(self) -> int:
+        n = 1
+        for s in self.spec.entry_shape:
+            n *= s
+        return n
+
+
+@dataclass
+class RequestCache:
+    req_id: object
+    slot: int
+    length: int = 0
+    tables: List[List[int]] = field(default_factory=list)   # per group: page id per logical page, -1 once released
+
+
+class CacheManager:
+    """Built from the model's per-run needs (``DecoderModel.cache_needs()``).
+
+    ``num_pages`` is the size of every group's pool (an int, or a list per
+    group).  ``allocate=False`` keeps the bookkeeping only (tests, planning)."""
+
+    def __init__(self, needs, page_size: int, num_pages, max_requests: int, dtype: torch.dtype, device,
+                 allocate: bool = True):
+        from ..models.decoder import LayerCache
+        self.page_size = int(page_size)
+        if self.page_size <= 0:
+            raise ValueError("page_size must be positive")
+        self.max_requests = int(max_requests)
+        self.dtype, self.device = dtype, device
+        self.groups: List[CacheGroup] = []
+        self.slots = StateSlots(self.max_requests)
+        self.requests: Dict[object, RequestCache] = {}
+        key_to_group: Dict[Tuple, int] = {}
+        run_group: Dict[int, Tuple[int, int]] = {}           # run -> (group, index in group)
+        for e, need in enumerate(needs):
+            if need.cache is None or need.cache_from is not None:
+                continue
+            key = (need.cache.policy, need.cache.window, tuple(need.cache.entry_shape))
+            if key not in key_to_group:
+                key_to_group[key] = len(self.groups)
+                n = num_pages[len(self.groups)] if isinstance(num_pages, (list, tuple)) else num_pages
+                self.groups.append(CacheGroup(need.cache, self.page_size, PagePool(n)))
+            g = key_to_group[key]
+            run_group[e] = (g, len(self.groups[g].runs))
+            self.groups[g].runs.append(e)
+        if allocate:
+            for grp in self.groups:
+                grp.pages = torch.empty((len(grp.runs), grp.pool.num_pages, 2, self.page_size * grp.entry_elems),
+                                        dtype=dtype, device=device)
+        self.state_tensors: List[Optional[torch.Tensor]] = []
+        self.layer_caches: List[Optional[LayerCache]] = []
+        for e, need in enumerate(needs):
+            state = None
+            if need.state is not None and allocate:
+                state = torch.zeros((self.max_requests, *need.state.shape), dtype=need.state.dtype, device=device)
+            self.state_tensors.append(state)
+            owner_run = e if need.cache_from is None else need.cache_from
+            if needs[owner_run].cache is None:
+                kv, g = None, -1
+            else:
+                g, idx = run_group[owner_run]
+                kv = self.groups[g].pages[idx] if allocate else None
+            if kv is None and state is None and need.cache is None and need.state is None:
+                self.layer_caches.append(None)
+            else:
+                self.layer_caches.append(LayerCache(kv=kv, group=g, state=state, owner=need.cache_from is None))
+
+    # -- requests ---------------------------------------------------------------
+    def admit(self, req_id) -> RequestCache:
+        if req_id in self.requests:
+            raise KeyError(f"request {req_id!r} is already live")
+        slot = self.slots.take()
+        for st in self.state_tensors:
+            if st is not None:
+                st[slot].zero_()
+        rc = RequestCache(req_id, slot, 0, [[] for _ in self.groups])
+        self.requests[req_id] = rc
+        return rc
+
+    def is_live(self, req_id) -> bool:
+        return req_id in self.requests
+
+    def length(self, req_id) -> int:
+        return self.requests[req_id].length
+
+    def pages_needed(self, length: int, n_new: int) -> int:
+        ps = self.page_size
+        return -(-(length + n_new) // ps) - (-(-length // ps))
+
+    def can_reserve(self, demands: Sequence[Tuple[int, int]]) -> bool:
+        """demands: (current length, new tokens) per request; True if every pool
+        can serve all of them together."""
+        need = sum(self.pages_needed(l, n) for l, n in demands)
+        return all(need <= g.pool.num_free for g in self.groups)
+
+    def reserve(self, req_id, n_new: int) -> None:
+        """Make table entries for positions length .. length+n_new-1 in every group;
+        all or nothing (raises OutOfPages and leaves the request as it was)."""
+        rc = self.requests[req_id]
+        need = self.pages_needed(rc.length, n_new)
+        if need == 0:
+            return
+        for g in self.groups:
+            if need > g.pool.num_free:
+                raise OutOfPages(f"request {req_id!r} needs {need} pages, a pool has {g.pool.num_free} free")
+        for g, table in zip(self.groups, rc.tables):
+            table.extend(g.pool.allocate(need))
+
+    def commit(self, req_id, n_new: int) -> None:
+        """The step wrote n_new tokens: grow the length and give back pages that a
+        window has passed (every later query reads keys >= length - window + 1)."""
+        rc = self.requests[req_id]
+        rc.length += n_new
+        assert all(len(t) == -(-rc.length // self.page_size) for t in rc.tables), "block table out of step"
+        for g, table in zip(self.groups, rc.tables):
+            if g.spec.policy != "window":
+                continue
+            first_needed = max(0, rc.length - g.spec.window + 1)
+            dead = first_needed // self.page_size          # pages wholly before first_needed
+            gone = [p for p in table[:dead] if p >= 0]
+            if gone:
+                g.pool.free(gone)
+                for i in range(dead):
+                    table[i] = -1
+
+    def release(self, req_id) -> None:
+        rc = self.requests.pop(req_id)
+        for g, table in zip(self.groups, rc.tables):
+            g.pool.free([p for p in table if p >= 0])
+        self.slots.give(rc.slot)
+
+    def release_all(self) -> None:
+        for rid in list(self.requests):
+            self.release(rid)
+
+    # -- inspection -------------------------------------------------------------
+    def check_invariants(self) -> None:
+        """No page lost, none held twice: free + held-by-requests == pool."""
+        for gi, g in enumerate(self.groups):
+            held = [p for rc in self.requests.values() for p in rc.tables[gi] if p >= 0]
+            assert len(held) == len(set(held)), "a page is in two block tables"
+            assert len(held) == g.pool.num_held, f"group {gi}: {g.pool.num_held} pages out, {len(held)} in tables"
+            assert set(held).isdisjoint(g.pool._free), "a held page is on the free list"
+            assert len(set(g.pool._free)) == len(g.pool._free), "a page is on the free list twice"
+        assert len(self.requests) == self.slots.n - self.slots.num_free

@@ -1,0 +1,250 @@
+// Row-wise kernels of the decoder: embedding gather, residual add + RMSNorm,
+// row gather for the head, SiLU(gate)*up, rotary encoding fused with the write of
+// keys and values into cache pages.  All arithmetic is float32; storage is float32
+// or bfloat16 as the caller says.
+#include "common.cuh"
+using namespace bspec;
+
+// ---------------------------------------------------------------- embedding
+// out[t, :] = scale * table[ids[t], :]   (out is the float32 residual stream)
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out,
+                             int d, int vocab, float scale) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  const bool ok = id >= 0 && id < vocab;
+  const T* row = table + (size_t)(ok ? id : 0) * d;
+  float* o = out + (size_t)t * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = ok ? to_f32(row[i]) * scale : 0.f;
+}
+
+BSPEC_API int bspec_embed(const int* ids, const void* table, int table_dtype, float* out, int n, int d, int vocab,
+                          float scale, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int threads = d >= 1024 ? 256 : 128;
+  if (table_dtype == BSPEC_F32)
+    embed_kernel<float><<<n, threads, 0, stream>>>(ids, (const float*)table, out, d, vocab, scale);
+  else
+    embed_kernel<__nv_bfloat16><<<n, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, d, vocab, scale);
+  return BSPEC_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- add + RMSNorm
+// resid[t,:] += delta[t,:] (if delta);  out[t,:] = cast(resid * rsqrt(mean(resid^2)+eps)) * w
+// The product with w is taken after the cast to the output type, in that type.
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
+                                   const void* __restrict__ weight, int w_dtype, TO* __restrict__ out, int d,
+                                   float eps) {
+  __shared__ float scratch[32];
+  const size_t base = (size_t)blockIdx.x * d;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float v = resid[base + i];
+    if (delta != nullptr) {
+      v += to_f32(delta[base + i]);
+      resid[base + i] = v;
+    }
+    ss += v * v;
+  }
+  const float total = block_sum(ss, scratch);
+  const float r = rsqrtf(total / (float)d + eps);
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float n = resid[base + i] * r;
+    const float w = load_as_f32(weight, w_dtype, i);
+    out[base + i] = from_f32<TO>(to_f32(from_f32<TO>(n)) * w);
+  }
+}
+
+BSPEC_API int bspec_add_rmsnorm(float* resid, const void* delta, int delta_dtype, const void* weight, int w_dtype,
+                                void* out, int out_dtype, int n, int d, float eps, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+#define L(TD, TO) add_rmsnorm_kernel<TD, TO><<<n, threads, 0, stream>>>(resid, (const TD*)delta, weight, w_dtype, (TO*)out, d, eps)
+  if (delta_dtype == BSPEC_F32 && out_dtype == BSPEC_F32) L(float, float);
+  else if (delta_dtype == BSPEC_BF16 && out_dtype == BSPEC_BF16) L(__nv_bfloat16, __nv_bfloat16);
+  else if (delta_dtype == BSPEC_F32 && out_dtype == BSPEC_BF16) L(float, __nv_bfloat16);
+  else L(__nv_bfloat16, float);
+#undef L
+  return BSPEC_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- row gather (+ pending add)
+template <typename TD>
+__global__ void gather_rows_add_kernel(const float* __restrict__ resid, const TD* __restrict__ pending,
+                                       const int* __restrict__ rows, float* __restrict__ out, int d) {
+  const size_t src = (size_t)rows[blockIdx.x] * d, dst = (size_t)blockIdx.x * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float v = resid[src + i];
+    if (pending != nullptr) v += to_f32(pending[src + i]);
+    out[dst + i] = v;
+  }
+}
+
+BSPEC_API int bspec_gather_rows_add(const float* resid, const void* pending, int pending_dtype, const int* rows,
+                                    float* out, int n_out, int d, cudaStream_t stream) {
+  if (n_out <= 0) return 0;
+  if (pending_dtype == BSPEC_F32)
+    gather_rows_add_kernel<float><<<n_out, 256, 0, stream>>>(resid, (const float*)pending, rows, out, d);
+  else
+    gather_rows_add_kernel<__nv_bfloat16><<<n_out, 256, 0, stream>>>(resid, (const __nv_bfloat16*)pending, rows, out, d);
+  return BSPEC_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- SiLU(gate) * up
+// u [n, 2I] = [gate | up]  ->  m [n, I]
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ u, T* __restrict__ m, int inter, size_t total) {
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = idx / inter, col = idx - row * inter;
+    const float g = to_f32(u[row * 2 * inter + col]);
+    const float up = to_f32(u[row * 2 * inter + inter + col]);
+    const float s = g / (1.f + expf(-g));
+    m[idx] = from_f32<T>(s * up);
+  }
+}
+
+BSPEC_API int bspec_silu_mul(const void* u, void* m, int dtype, int n, int inter, cudaStream_t stream) {
+  const size_t total = (size_t)n * inter;
+  if (total == 0) return 0;
+  const int threads = 256;
+  size_t want = (total + threads - 1) / threads;
+  const int blocks = (int)(want > 148 * 32 ? 148 * 32 : want);
+  if (dtype == BSPEC_F32)
+    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)u, (float*)m, inter, total);
+  else
+    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)u, (__nv_bfloat16*)m, inter, total);
+  return BSPEC_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------- rotary + cache append
+// qkv [n, (Hq + 2 Hkv) * hd]: rotate the q heads in place; rotate the k heads and
+// write them, with the v heads, into the cache page of each token's position.
+// Cache layer layout: [pages][2 (k, v)][Hkv][page_size][hd].
+// Pairing: half-split (j, j + rot/2) or interleaved (2j, 2j+1); dims >= rot pass through.
+// angle = float(position) * inv_freq[j], all float32.
+template <typename T>
+__global__ void rope_kv_append_kernel(T* __restrict__ qkv, int Hq, int Hkv, int hd, const float* __restrict__ inv_freq,
+                                      int rot, int interleaved, const int* __restrict__ positions,
+                                      const int* __restrict__ tok_entry, const int* __restrict__ kv_indptr,
+                                      const int* __restrict__ kv_indices, T* __restrict__ cache, int page_size,
+                                      int write_kv) {
+  extern __shared__ float cs[];  // [rot/2] cos, [rot/2] sin
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int half = rot / 2;
+  for (int j = threadIdx.x; j < half; j += blockDim.x) {
+    float s, c;
+    sincosf((float)pos * inv_freq[j], &s, &c);
+    cs[j] = c;
+    cs[half + j] = s;
+  }
+  __syncthreads();
+  T* row = qkv + (size_t)t * (Hq + 2 * Hkv) * hd;
+  T* kdst = nullptr;
+  T* vdst = nullptr;
+  if (write_kv) {
+    const int e = tok_entry[t];
+    const int page = kv_indices[kv_indptr[e] + pos / page_size];
+    const int r = pos % page_size;
+    const size_t page_elems = (size_t)Hkv * page_size * hd;
+    kdst = cache + ((size_t)page * 2) * page_elems + (size_t)r * hd;
+    vdst = kdst + page_elems;
+  }
+  const int hp = hd / 2;  // work items per head: one per pair of dims
+  // q and k heads: each work item handles dims (a, b)
+  for (int w = threadIdx.x; w < (Hq + Hkv) * hp; w += blockDim.x) {
+    const int h = w / hp, j = w - h * hp;
+    T* x = row + (size_t)h * hd;
+    int a, b;
+    bool rotate;
+    if (j < half) {
+      rotate = true;
+      a = interleaved ? 2 * j : j;
+      b = interleaved ? 2 * j + 1 : j + half;
+    } else {  // pass-through dims rot .. hd-1, two at a time
+      rotate = false;
+      a = rot + 2 * (j - half);
+      b = a + 1;
+    }
+    float xa = to_f32(x[a]), xb = to_f32(x[b]);
+    if (rotate) {
+      const float c = cs[j], s = cs[half + j];
+      const float ra = xa * c - xb * s, rb = xa * s + xb * c;
+      xa = ra;
+      xb = rb;
+    }
+    const T ya = from_f32<T>(xa), yb = from_f32<T>(xb);
+    if (h < Hq) {
+      if (rotate) { x[a] = ya; x[b] = yb; }
+    } else if (write_kv) {
+      T* kd = kdst + (size_t)(h - Hq) * page_size * hd;
+      kd[a] = ya;
+      kd[b] = yb;
+    }
+  }
+  if (write_kv) {
+    const T* v = row + (size_t)(Hq + Hkv) * hd;
+    for (int w = threadIdx.x; w < Hkv * hd; w += blockDim.x) {
+      const int h = w / hd, dcol = w - h * hd;
+      vdst[(size_t)h * page_size * hd + dcol] = v[w];
+    }
+  }
+}
+
+BSPEC_API int bspec_rope_kv_append(void* qkv, int dtype, int n, int Hq, int Hkv, int hd, const float* inv_freq, int rot,
+                                   int interleaved, const int* positions, const int* tok_entry, const int* kv_indptr,
+                                   const int* kv_indices, void* cache, int page_size, int write_kv,
+                                   cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int threads = 256;
+  const size_t smem = (size_t)(rot > 0 ? rot : 0) * sizeof(float);
+  if (dtype == BSPEC_F32)
+    rope_kv_append_kernel<float><<<n, threads, smem, stream>>>((float*)qkv, Hq, Hkv, hd, inv_freq, rot, interleaved,
+                                                              positions, tok_entry, kv_indptr, kv_indices,
+                                                              (float*)cache, page_size, write_kv);
+  else
+    rope_kv_append_kernel<__nv_bfloat16><<<n, threads, smem, stream>>>(
+        (__nv_bfloat16*)qkv, Hq, Hkv, hd, inv_freq, rot, interleaved, positions, tok_entry, kv_indptr, kv_indices,
+        (__nv_bfloat16*)cache, page_size, write_kv);
+  return BSPEC_LAUNCH_CHECK();
+}
+
+// Rotary encoding alone, on a strided view x [n, H, hd] (row stride given in elements).
+template <typename T>
+__global__ void rope_inplace_kernel(T* __restrict__ x, long long row_stride, int H, int hd,
+                                    const float* __restrict__ inv_freq, int rot, int interleaved,
+                                    const int* __restrict__ positions) {
+  extern __shared__ float cs[];
+  const int t = blockIdx.x, half = rot / 2;
+  const int pos = positions[t];
+  for (int j = threadIdx.x; j < half; j += blockDim.x) {
+    float s, c;
+    sincosf((float)pos * inv_freq[j], &s, &c);
+    cs[j] = c;
+    cs[half + j] = s;
+  }
+  __syncthreads();
+  T* row = x + (size_t)t * row_stride;
+  for (int w = threadIdx.x; w < H * half; w += blockDim.x) {
+    const int h = w / half, j = w - h * half;
+    T* p = row + (size_t)h * hd;
+    const int a = interleaved ? 2 * j : j, b = interleaved ? 2 * j + 1 : j + half;
+    const float xa = to_f32(p[a]), xb = to_f32(p[b]);
+    const float c = cs[j], s = cs[half + j];
+    p[a] = from_f32<T>(xa * c - xb * s);
+    p[b] = from_f32<T>(xa * s + xb * c);
+  }
+}
+
+BSPEC_API int bspec_rope_inplace(void* x, int dtype, int n, long long row_stride, int H, int hd, const float* inv_freq,
+                                 int rot, int interleaved, const int* positions, cudaStream_t stream) {
+  if (n <= 0 || rot <= 0) return 0;
+  const size_t smem = (size_t)rot * sizeof(float);
+  if (dtype == BSPEC_F32)
+    rope_inplace_kernel<float><<<n, 128, smem, stream>>>((float*)x, row_stride, H, hd, inv_freq, rot, interleaved, positions);
+  else
+    rope_inplace_kernel<__nv_bfloat16><<<n, 128, smem, stream>>>((__nv_bfloat16*)x, row_stride, H, hd, inv_freq, rot, interleaved, positions);
+  return BSPEC_LAUNCH_CHECK();
+}

@@ -1,0 +1,195 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+The reference's step is ``StandardEngine.forward(batch)`` over a ``BatchPack``
+(batchspec/backends/standard_engine.py:109-128, backends/continuous/batch_builder.py:30-81):
+exactly one entry per batch slot, dummy entries for empty slots, logits for every
+token, then the last row of each slot.  Here a step holds any number of entries,
+each ``n >= 1`` new tokens of a live request (a portion of a prompt or a decoded
+token, cut anywhere), runs only those tokens against the cache that earlier steps
+left, and returns float32 logits at the places asked for.
+
+Order inside a step: reserve pages for every entry (all or nothing) -> pack the
+metadata into one pinned buffer and copy it once -> model forward -> commit the
+new lengths.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+
+
+@dataclass
+class StepEntry:
+    """``tokens``: the request's next tokens; ``want``: indices into ``tokens``
+    whose logits are returned (may be empty)."""
+    req_id: object
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class GroupTables:
+    """Block tables of one cache group for the entries of the step, as CSR."""
+    page_size: int
+    kv_indptr: torch.Tensor            # int32 [n_entries + 1]
+    kv_indices: torch.Tensor           # int32 [sum of table lengths], -1 for released pages
+    h_kv_indptr: np.ndarray
+    h_kv_indices: np.ndarray
+
+
+@dataclass
+class StepContext:
+    """Everything the parts may read about the step.  Device tensors are int32
+    views into one buffer; ``h_*`` are the same values on the host."""
+    n_tokens: int
+    n_entries: int
+    token_ids: torch.Tensor            # [n_tokens]
+    positions: torch.Tensor            # [n_tokens] absolute position of each token in its request
+    tok_entry: torch.Tensor            # [n_tokens] index of the token's entry
+    qo_indptr: torch.Tensor            # [n_entries + 1]
+    kv_len: torch.Tensor               # [n_entries] request length after this step
+    state_slots: torch.Tensor          # [n_entries] state slot of each entry's request
+    logit_rows: torch.Tensor           # [n_logit_rows] flat token indices whose logits are wanted
+    n_logit_rows: int
+    tables: List[GroupTables]
+    max_q_len: int
+    max_kv_len: int
+    h_qo_indptr: np.ndarray
+    h_kv_len: np.ndarray
+    h_state_slots: np.ndarray
+    h_positions: np.ndarray
+    extras: dict = field(default_factory=dict)
+
+
+class _Staging:
+    """Pinned host buffers (a small ring) and one device buffer for the packed
+    metadata.  A host buffer is rewritten only after the copy that last read it
+    has finished."""
+
+    def __init__(self, device, capacity: int = 1 << 16, ring: int = 3):
+        self.device = device
+        self.ring = ring
+        self.capacity = 0
+        self._grow(capacity)
+
+    def _grow(self, capacity: int) -> None:
+        if self.capacity:
+            torch.cuda.current_stream().synchronize()
+        self.capacity = capacity
+        pin = self.device.type == "cuda"
+        self.host = [torch.empty(capacity, dtype=torch.int32, pin_memory=pin) for _ in range(self.ring)]
+        self.dev = [torch.empty(capacity, dtype=torch.int32, device=self.device) for _ in range(self.ring)]
+        self.events = [None] * self.ring
+        self.turn = 0
+
+    def upload(self, packed: np.ndarray) -> torch.Tensor:
+        n = packed.shape[0]
+        if n > self.capacity:
+            self._grow(max(n, 2 * self.capacity))
+        i = self.turn
+        self.turn = (self.turn + 1) % self.ring
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        self.host[i].numpy()[:n] = packed
+        self.dev[i][:n].copy_(self.host[i][:n], non_blocking=True)
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record()
+            self.events[i] = ev
+        return self.dev[i]
+
+
+def _align4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class StepRunner:
+    def __init__(self, model, cache: CacheManager, vocab_size: int, device):
+        self.model, self.cache, self.vocab_size = model, cache, int(vocab_size)
+        self.device = torch.device(device)
+        self.staging = _Staging(self.device)
+        self.last_h2d_bytes = 0
+
+    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+        """Pack the metadata of a step whose pages are already reserved."""
+        cache = self.cache
+        n = len(entries)
+        lens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=n)
+        before = np.fromiter((cache.requests[e.req_id].length for e in entries), dtype=np.int64, count=n)
+        qo = np.zeros(n + 1, dtype=np.int32)
+        np.cumsum(lens, out=qo[1:])
+        nnz = int(qo[-1])
+        tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64).reshape(-1) for e in entries])
+        if tokens.size and (tokens.min() < 0 or tokens.max() >= self.vocab_size):
+            raise ValueError(f"token id outside [0, {self.vocab_size}) in the step")
+        tok_entry = np.repeat(np.arange(n, dtype=np.int32), lens)
+        positions = (np.arange(nnz, dtype=np.int64) - np.repeat(qo[:-1].astype(np.int64), lens)
+                     + np.repeat(before, lens)).astype(np.int32)
+        kv_len = (before + lens).astype(np.int32)
+        slots = np.fromiter((cache.requests[e.req_id].slot for e in entries), dtype=np.int32, count=n)
+        rows: List[int] = []
+        for i, e in enumerate(entries):
+            for w in e.want:
+                if not 0 <= w < lens[i]:
+                    raise ValueError(f"request {e.req_id!r}: wanted place {w} is outside its {lens[i]} tokens")
+                rows.append(int(qo[i]) + int(w))
+        rows_np = np.asarray(rows, dtype=np.int32)
+        parts = [tokens.astype(np.int32), positions, tok_entry, qo, kv_len, slots, rows_np]
+        group_parts = []
+        for gi, g in enumerate(cache.groups):
+            tabs = [cache.requests[e.req_id].tables[gi] for e in entries]
+            indptr = np.zeros(n + 1, dtype=np.int32)
+            np.cumsum([len(t) for t in tabs], out=indptr[1:])
+            indices = np.fromiter((p for t in tabs for p in t), dtype=np.int32, count=int(indptr[-1]))
+            group_parts.append((indptr, indices))
+            parts += [indptr, indices]
+        offsets, total = [], 0
+        for p in parts:
+            offsets.append(total)
+            total += _align4(max(p.shape[0], 1))
+        packed = np.zeros(total, dtype=np.int32)
+        for o, p in zip(offsets, parts):
+            packed[o:o + p.shape[0]] = p
+        dev = self.staging.upload(packed)
+        self.last_h2d_bytes = total * 4
+        view = lambda k: dev[offsets[k]:offsets[k] + parts[k].shape[0]]
+        tables = []
+        for gi, g in enumerate(cache.groups):
+            k = 7 + 2 * gi
+            tables.append(GroupTables(g.page_size, view(k), view(k + 1), group_parts[gi][0], group_parts[gi][1]))
+        return StepContext(
+            n_tokens=nnz, n_entries=n, token_ids=view(0), positions=view(1), tok_entry=view(2), qo_indptr=view(3),
+            kv_len=view(4), state_slots=view(5), logit_rows=view(6), n_logit_rows=len(rows), tables=tables,
+            max_q_len=int(lens.max()), max_kv_len=int(kv_len.max()), h_qo_indptr=qo, h_kv_len=kv_len,
+            h_state_slots=slots, h_positions=positions)
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run the entries as one batch; float32 logits [sum of len(want), vocab] in
+        the order of the entries and of their ``want``."""
+        cache = self.cache
+        if not entries:
+            return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+        seen = set()
+        for e in entries:
+            if len(e.tokens) < 1:
+                raise ValueError(f"request {e.req_id!r}: an entry needs at least one token")
+            if e.req_id in seen:
+                raise ValueError(f"request {e.req_id!r} appears twice in one step")
+            seen.add(e.req_id)
+            if not cache.is_live(e.req_id):
+                raise KeyError(f"request {e.req_id!r} is not live (admit it first)")
+        if not cache.can_reserve([(cache.requests[e.req_id].length, len(e.tokens)) for e in entries]):
+            from ..cache.manager import OutOfPages
+            raise OutOfPages("the step needs more pages than are free; nothing was run")
+        for e in entries:
+            cache.reserve(e.req_id, len(e.tokens))
+        ctx = self.build_context(entries)
+        logits = self.model.forward(ctx)
+        for e in entries:
+            cache.commit(e.req_id, len(e.tokens))
+        return logits

@@ -1,0 +1,244 @@
+"""Python face of the CUDA kernels: loads the shared library built from
+``csrc/`` and wraps each exported entry point.  Every wrapper checks dtypes,
+shapes and contiguity, launches on torch's current stream and raises on a launch
+error.  There is no fallback: without a CUDA device or without the library these
+functions raise.
+
+Matrix products in bfloat16 go to the vendor library through ``torch.mm`` (the
+reference's ``nn.Linear`` does the same, batchspec/models/modules/attention/base.py:32-39);
+float32 products use this package's own FFMA kernel so that no reduced-precision
+mode can slip in.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
+from typing import Optional
+
+import torch
+
+_lib = None
+_lock = threading.Lock()
+_launches = 0          # kernels of this package launched (for the benchmark's count)
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _dtype_code(t: torch.dtype) -> int:
+    if t == torch.float32:
+        return F32
+    if t == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {t}")
+
+
+_SIGNATURES = {
+    "bspec_embed": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+    "bspec_add_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+    "bspec_gather_rows_add": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "bspec_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "bspec_rope_kv_append": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                             c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "bspec_rope_inplace": [c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p],
+    "bspec_attention_generic": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "bspec_sgemm_tn": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p],
+    "bspec_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p],
+    "bspec_sample": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ulonglong, c_void_p,
+                     c_void_p],
+}
+
+
+def load_library():
+    """Load (building on first use) the kernel library.  Raises if it cannot."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        from ..csrc.build import library_path
+        path = library_path(build=True)
+        lib = ctypes.CDLL(str(path))
+        for name, argtypes in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = argtypes
+            fn.restype = c_int
+        _lib = lib
+    return _lib
+
+
+def library_file() -> str:
+    load_library()
+    from ..csrc.build import library_path
+    return str(library_path(build=False))
+
+
+def launch_count() -> int:
+    return _launches
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("batchspec_b200 kernels run on a CUDA device only; got a tensor on " + str(t.device))
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(err: int, name: str) -> None:
+    global _launches
+    _launches += 1
+    if err != 0:
+        raise KernelError(f"{name}: CUDA error {err}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+# ---------------------------------------------------------------------------- rows
+
+def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    _require_cuda(ids, table, out)
+    assert ids.dtype == torch.int32 and out.dtype == torch.float32 and table.is_contiguous() and out.is_contiguous()
+    n, d = out.shape
+    assert table.shape[1] == d and ids.numel() == n
+    _check(load_library().bspec_embed(ids.data_ptr(), table.data_ptr(), _dtype_code(table.dtype), out.data_ptr(),
+                                      n, d, table.shape[0], float(scale), _stream()), "embed")
+
+
+def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: torch.Tensor) -> None:
+    _require_cuda(resid, delta, weight, out)
+    assert resid.dtype == torch.float32 and resid.is_contiguous() and out.is_contiguous()
+    n, d = resid.shape
+    assert out.shape == resid.shape and weight.numel() == d
+    if delta is not None:
+        assert delta.shape == resid.shape and delta.is_contiguous()
+    dd = _dtype_code(delta.dtype) if delta is not None else _dtype_code(out.dtype)
+    _check(load_library().bspec_add_rmsnorm(resid.data_ptr(), _ptr(delta), dd, weight.data_ptr(),
+                                            _dtype_code(weight.dtype), out.data_ptr(), _dtype_code(out.dtype),
+                                            n, d, float(eps), _stream()), "add_rmsnorm")
+
+
+def gather_rows_add(resid: torch.Tensor, pending: Optional[torch.Tensor], rows: torch.Tensor,
+                    out: torch.Tensor) -> None:
+    _require_cuda(resid, pending, rows, out)
+    assert resid.dtype == torch.float32 and out.dtype == torch.float32 and rows.dtype == torch.int32
+    assert resid.is_contiguous() and out.is_contiguous() and (pending is None or pending.is_contiguous())
+    pd = _dtype_code(pending.dtype) if pending is not None else F32
+    _check(load_library().bspec_gather_rows_add(resid.data_ptr(), _ptr(pending), pd, rows.data_ptr(), out.data_ptr(),
+                                                out.shape[0], out.shape[1], _stream()), "gather_rows_add")
+
+
+def silu_mul(u: torch.Tensor, out: torch.Tensor) -> None:
+    _require_cuda(u, out)
+    n, inter = out.shape
+    assert u.shape == (n, 2 * inter) and u.dtype == out.dtype and u.is_contiguous() and out.is_contiguous()
+    _check(load_library().bspec_silu_mul(u.data_ptr(), out.data_ptr(), _dtype_code(u.dtype), n, inter, _stream()),
+           "silu_mul")
+
+
+def rope_kv_append(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                   inv_freq: Optional[torch.Tensor], rotary_dim: int, interleaved: bool, positions: torch.Tensor,
+                   tok_entry: torch.Tensor, kv_indptr: torch.Tensor, kv_indices: torch.Tensor, cache: torch.Tensor,
+                   page_size: int, write_kv: bool = True) -> None:
+    """Rotate q (in place) and k, and write k and v of every token into the cache
+    page of its position.  ``cache``: one layer's pages, any shape with
+    2 * n_kv_heads * page_size * head_dim elements per page, laid out
+    [page][k|v][kv head][row][dim]."""
+    _require_cuda(qkv, positions, cache)
+    n = qkv.shape[0]
+    assert qkv.is_contiguous() and qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim
+    assert cache.dtype == qkv.dtype and cache.is_contiguous()
+    assert positions.dtype == torch.int32 and tok_entry.dtype == torch.int32
+    if rotary_dim:
+        assert inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2
+    _check(load_library().bspec_rope_kv_append(
+        qkv.data_ptr(), _dtype_code(qkv.dtype), n, n_heads, n_kv_heads, head_dim, _ptr(inv_freq), int(rotary_dim),
+        int(bool(interleaved)), positions.data_ptr(), tok_entry.data_ptr(), kv_indptr.data_ptr(),
+        kv_indices.data_ptr(), cache.data_ptr(), int(page_size), int(bool(write_kv)), _stream()), "rope_kv_append")
+
+
+def rope_inplace(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int,
+                 interleaved: bool = False) -> None:
+    """x: [n, H, hd] view whose last two dims are dense; rows may be strided."""
+    _require_cuda(x, positions, inv_freq)
+    n, H, hd = x.shape
+    assert x.stride(2) == 1 and x.stride(1) == hd and positions.dtype == torch.int32
+    _check(load_library().bspec_rope_inplace(x.data_ptr(), _dtype_code(x.dtype), n, x.stride(0), H, hd,
+                                             inv_freq.data_ptr(), int(rotary_dim), int(bool(interleaved)),
+                                             positions.data_ptr(), _stream()), "rope_inplace")
+
+
+# ---------------------------------------------------------------------------- attention
+
+def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, ctx, tables, n_heads: int,
+                    n_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
+    """Causal attention of the step's tokens over their requests' cached keys.
+    ``qkv``: [n, >= n_heads*head_dim] rows with the (already rotated) query heads
+    first.  ``ctx`` gives qo_indptr / positions / n_entries / max_q_len, ``tables``
+    the block tables of the cache group."""
+    _require_cuda(qkv, out, cache)
+    assert qkv.stride(1) == 1 and out.is_contiguous() and out.dtype == qkv.dtype == cache.dtype
+    _check(load_library().bspec_attention_generic(
+        qkv.data_ptr(), qkv.stride(0), out.data_ptr(), cache.data_ptr(), _dtype_code(qkv.dtype),
+        ctx.qo_indptr.data_ptr(), ctx.positions.data_ptr(), tables.kv_indptr.data_ptr(), tables.kv_indices.data_ptr(),
+        ctx.n_entries, ctx.max_q_len, n_heads, n_kv_heads, head_dim, tables.page_size, float(scale), int(window),
+        _stream()), "attention_generic")
+
+
+# ---------------------------------------------------------------------------- matrix products
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """x [M, K] @ w[N, K]^T -> [M, N] in ``out_dtype`` (default: x's dtype)."""
+    _require_cuda(x, w)
+    out_dtype = out_dtype or x.dtype
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and x.dtype == w.dtype, (x.shape, w.shape, x.dtype, w.dtype)
+    if x.dtype == torch.float32:
+        assert out_dtype == torch.float32 and x.stride(1) == 1 and w.stride(1) == 1
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+        _check(load_library().bspec_sgemm_tn(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, x.stride(0),
+                                             w.stride(0), N, _stream()), "sgemm_tn")
+        return out
+    if out_dtype == x.dtype:
+        return torch.mm(x, w.t())
+    return torch.mm(x, w.t(), out_dtype=out_dtype)
+
+
+# ---------------------------------------------------------------------------- sampling
+
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    _require_cuda(logits)
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
+    _check(load_library().bspec_argmax(logits.data_ptr(), logits.shape[0], logits.shape[1], out.data_ptr(), _stream()),
+           "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           stream_id: torch.Tensor, counter: torch.Tensor, seed: int) -> torch.Tensor:
+    """Per-row parameters on the device: temperature f32 (<= 0: greedy), top_k i32
+    (<= 0: off), top_p f32 (<= 0 or >= 1: off), stream_id i64 and counter i64 (the
+    random stream of the row's request and the index of the draw in it)."""
+    _require_cuda(logits, temperature, top_k, top_p, stream_id, counter)
+    rows = logits.shape[0]
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    assert temperature.dtype == torch.float32 and top_k.dtype == torch.int32 and top_p.dtype == torch.float32
+    assert stream_id.dtype == torch.int64 and counter.dtype == torch.int64
+    out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    _check(load_library().bspec_sample(logits.data_ptr(), rows, logits.shape[1], temperature.data_ptr(),
+                                       top_k.data_ptr(), top_p.data_ptr(), stream_id.data_ptr(), counter.data_ptr(),
+                                       int(seed) & 0xFFFFFFFFFFFFFFFF, out.data_ptr(), _stream()), "sample")
+    return out

@@ -1,0 +1,33 @@
+"""SwiGLU feed-forward part (batchspec/models/modules/feedforward.py:25-27,62):
+u = x W13^T with W13 = [gate; up] fused at load (feedforward.py:35-38),
+m = silu(u[:, :I]) * u[:, I:], out = m W2^T.  No biases."""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..kernels import ops
+from .base import FEED_FORWARDS, FeedForward, ParamSpec, Runtime, register_part
+
+
+@register_part(FEED_FORWARDS, "swiglu")
+class SwiGLU(FeedForward):
+    def __init__(self, runtime: Runtime, dim: int, intermediate: int):
+        self.runtime, self.dim, self.intermediate = runtime, int(dim), int(intermediate)
+        self.w13 = self.w2 = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {"gate": ParamSpec((self.intermediate, self.dim)),
+                "up": ParamSpec((self.intermediate, self.dim)),
+                "down": ParamSpec((self.dim, self.intermediate))}
+
+    def bind(self, params):
+        self.w13 = torch.cat([params["gate"], params["up"]], dim=0).contiguous()
+        self.w2 = params["down"].contiguous()
+
+    def forward(self, x, ctx):
+        u = ops.linear(x, self.w13)
+        m = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
+        ops.silu_mul(u, m)
+        return ops.linear(m, self.w2)
