@@ -19,7 +19,11 @@ from ..cache.manager import CacheManager
 from ..config import get_config, load_config
 from ..models import get_model
 from ..parts.base import Runtime
+from ..profiler import get_active_profiler
 from ..weights import load_weights, random_weights
+from ..sampling import Sampler, SamplingParams
+from .scheduler import Scheduler, Workload
+from .sequence import Sequence, Status
 from .step import StepEntry, StepRunner
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, "bf16": torch.bfloat16, "fp32": torch.float32}
@@ -49,6 +53,16 @@ class Engine:
         self.cache: Optional[CacheManager] = None
         self.runner: Optional[StepRunner] = None
         self.page_size = None
+        self.max_batch_size = None
+        self.max_seq_length = None
+        self.prefill_chunk_size = 128
+        self.max_tokens_per_step = 2048
+        self.sampling = SamplingParams()
+        self.sampler: Optional[Sampler] = None
+        self.ignore_eos = False
+        self.eos_token_ids = ()
+        self.tracer = None
+        self.last_stats = {}
 
     # -- model -------------------------------------------------------------------
     def load_model(self, model_dir=None, config=None, config_name: Optional[str] = None,
@@ -82,7 +96,8 @@ class Engine:
 
     # -- cache -------------------------------------------------------------------
     def setup_caches(self, max_batch_size: int, max_seq_length: Optional[int] = None, page_size: int = 16,
-                     num_pages: Optional[int] = None) -> None:
+                     prefill_chunk_size: int = 128, num_pages: Optional[int] = None,
+                     max_tokens_per_step: Optional[int] = None) -> None:
         """``num_pages`` sizes every pool directly; else the pool holds
         ``max_batch_size`` requests of ``max_seq_length`` tokens (the reference's
         sizing rule, backends/base/engine.py:66-93, without its +1 page)."""
@@ -93,6 +108,10 @@ class Engine:
                 raise ValueError("give num_pages or max_seq_length")
             num_pages = max_batch_size * (-(-max_seq_length // page_size))
         self.page_size = page_size
+        self.max_batch_size = int(max_batch_size)
+        self.max_seq_length = max_seq_length
+        self.prefill_chunk_size = int(prefill_chunk_size)
+        self.max_tokens_per_step = int(max_tokens_per_step or max(prefill_chunk_size, max_batch_size))
         self.cache = CacheManager(self.model.cache_needs(), page_size, num_pages, max_batch_size, self.dtype,
                                   self.device)
         self.model.attach_caches(self.cache.layer_caches)
@@ -108,3 +127,79 @@ class Engine:
     @torch.inference_mode()
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         return self.runner.step(entries)
+
+    # -- sampling ------------------------------------------------------------------
+    def setup_sampling_params(self, temperature: float = 0.0, top_k: int = -1, top_p: float = 0.0,
+                              force_budget: bool = False, seed: int = 0) -> None:
+        """Names as in the reference (backends/base/engine.py:95-113).  ``force_budget``
+        keeps generating to the token budget, never stopping at EOS
+        (standard_engine.py:230-232); the reference's replacement of an
+        end-of-thinking token by filler words is not part of this engine."""
+        self.sampling = SamplingParams(float(temperature), int(top_k), float(top_p))
+        self.ignore_eos = bool(force_budget)
+        self.sampler = Sampler(self.device, seed, self.sampling)
+
+    def setup_special_tokens(self, eos_token_ids=None) -> None:
+        """EOS ids: the argument, else the tokenizer's, else config.json's
+        (backends/base/engine.py:116-147 takes them from the tokenizer)."""
+        if eos_token_ids is not None:
+            self.eos_token_ids = tuple(int(t) for t in eos_token_ids)
+        elif self.tokenizer is not None and getattr(self.tokenizer, "eos_token_id", None) is not None:
+            self.eos_token_ids = (int(self.tokenizer.eos_token_id),)
+        else:
+            self.eos_token_ids = tuple(getattr(self.config, "eos_token_ids", ()) or ())
+
+    # -- generation ----------------------------------------------------------------
+    def make_scheduler(self) -> Scheduler:
+        max_len = getattr(self.config, "max_position_embeddings", None) or (1 << 30)
+        if self.max_seq_length:
+            max_len = min(max_len, self.max_seq_length)
+        return Scheduler(self.cache, self.max_batch_size, self.max_tokens_per_step, self.prefill_chunk_size,
+                         max_len, self.eos_token_ids, self.ignore_eos)
+
+    def sample_workloads(self, workloads: List[Workload], logits: torch.Tensor) -> torch.Tensor:
+        wanting = [w.seq for w in workloads if w.wants_token]
+        d = self.sampling
+        return self.sampler.sample(
+            logits,
+            [d.temperature if s.temperature is None else s.temperature for s in wanting],
+            [d.top_k if s.top_k is None else s.top_k for s in wanting],
+            [d.top_p if s.top_p is None else s.top_p for s in wanting],
+            [s.seq_id for s in wanting], [len(s.output_ids) for s in wanting])
+
+    @torch.inference_mode()
+    def generate(self, sequences: List[Sequence]) -> List[Sequence]:
+        """Continuous batching until every sequence is finished
+        (standard_engine.py:145-172): plan -> step -> sample -> update.  Token ids
+        go in and come out on the host."""
+        if self.sampler is None:
+            self.setup_sampling_params()
+        self.cache.release_all()
+        sched = self.make_scheduler()
+        sched.add_sequences(sequences)
+        steps = tokens_in = 0
+        prof = get_active_profiler()
+        while not sched.is_done():
+            with prof.host_bucket("host.plan"):
+                work = sched.plan()
+            if not work:
+                break
+            if self.tracer is not None:
+                self.tracer.on_plan(steps, sched, work)
+            with prof.step_timing_ctx():
+                entries = [StepEntry(w.seq.seq_id, w.seq.known_tokens(w.start, w.start + w.n_tokens),
+                                     (w.n_tokens - 1,) if w.wants_token else ()) for w in work]
+                logits = self.runner.step(entries)
+                wanting = [w for w in work if w.wants_token]
+                with prof.bucket("sampling"):
+                    toks = self.sample_workloads(work, logits).cpu().tolist() if wanting else []
+                prof.set_step_tokens(len(wanting))
+                prof.set_step_seq_len([w.start + w.n_tokens for w in work])
+            sched.process_results(work, {w.seq.seq_id: t for w, t in zip(wanting, toks)})
+            if self.tracer is not None:
+                self.tracer.on_update(steps, sched, work, toks)
+            steps += 1
+            tokens_in += sum(w.n_tokens for w in work)
+        self.last_stats = dict(steps=steps, tokens_fed=tokens_in, preemptions=sched.num_preemptions,
+                               generated=sum(len(s.output_ids) for s in sched.completed))
+        return sched.completed

@@ -12,6 +12,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..kernels import ops
+from ..profiler import bucket
 from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, CacheSpec, ParamSpec, Runtime, StateSpec,
                           build_part)
 from .spec import ModelSpec
@@ -109,7 +110,8 @@ class DecoderModel:
         s = self.spec
         n = ctx.n_tokens
         resid = torch.empty((n, s.hidden_size), dtype=torch.float32, device=self.runtime.device)
-        ops.embed(ctx.token_ids, self.embed, resid, s.embed_scale)
+        with bucket("embed"):
+            ops.embed(ctx.token_ids, self.embed, resid, s.embed_scale)
         pending = None
         for e, run in enumerate(s.order):
             resid, pending = self.blocks[run.layer].forward(resid, pending, ctx, self.caches[e])
@@ -119,4 +121,5 @@ class DecoderModel:
         picked = torch.empty((n_out, s.hidden_size), dtype=torch.float32, device=self.runtime.device)
         ops.gather_rows_add(resid, pending, ctx.logit_rows, picked)
         z = self.final_norm.forward(picked, None)
-        return ops.linear(z, self.head, out_dtype=torch.float32)
+        with bucket("lm_head"):
+            return ops.linear(z, self.head, out_dtype=torch.float32)

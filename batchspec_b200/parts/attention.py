@@ -17,6 +17,7 @@ from typing import Dict, Optional
 import torch
 
 from ..kernels import ops
+from ..profiler import bucket
 from .base import (MIXERS, POSITION_ENCODINGS, CacheSpec, Mixer, ParamSpec, PartSpec, Runtime, build_part,
                    register_part)
 
@@ -54,7 +55,8 @@ class Attention(Mixer):
     def forward(self, x, ctx, cache):
         n = x.shape[0]
         Hq, Hkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
-        qkv = ops.linear(x, self.wqkv)
+        with bucket("attn.qkv_proj"):
+            qkv = ops.linear(x, self.wqkv)
         tables = ctx.tables[cache.group]
         table = self.position.rope_table()
         if table is None:
@@ -64,9 +66,12 @@ class Attention(Mixer):
             inv_freq, rotary_dim, interleaved = None, 0, False
         else:
             inv_freq, rotary_dim, interleaved = table
-        ops.rope_kv_append(qkv, Hq, Hkv, hd, inv_freq, rotary_dim, interleaved, ctx.positions, ctx.tok_entry,
-                           tables.kv_indptr, tables.kv_indices, cache.kv, tables.page_size,
-                           write_kv=cache.owner)
+        with bucket("attn.rope"):
+            ops.rope_kv_append(qkv, Hq, Hkv, hd, inv_freq, rotary_dim, interleaved, ctx.positions, ctx.tok_entry,
+                               tables.kv_indptr, tables.kv_indices, cache.kv, tables.page_size,
+                               write_kv=cache.owner)
         out = torch.empty((n, Hq * hd), dtype=x.dtype, device=x.device)
-        ops.paged_attention(qkv, out, cache.kv, ctx, tables, Hq, Hkv, hd, self.scale, self.window)
-        return ops.linear(out, self.wo)
+        with bucket("attn.compute"):
+            ops.paged_attention(qkv, out, cache.kv, ctx, tables, Hq, Hkv, hd, self.scale, self.window)
+        with bucket("attn.o_proj"):
+            return ops.linear(out, self.wo)

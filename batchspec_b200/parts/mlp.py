@@ -8,6 +8,7 @@ from typing import Dict
 import torch
 
 from ..kernels import ops
+from ..profiler import bucket
 from .base import FEED_FORWARDS, FeedForward, ParamSpec, Runtime, register_part
 
 
@@ -27,7 +28,10 @@ class SwiGLU(FeedForward):
         self.w2 = params["down"].contiguous()
 
     def forward(self, x, ctx):
-        u = ops.linear(x, self.w13)
+        with bucket("mlp.gate_up_proj"):
+            u = ops.linear(x, self.w13)
         m = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
-        ops.silu_mul(u, m)
-        return ops.linear(m, self.w2)
+        with bucket("mlp.act"):
+            ops.silu_mul(u, m)
+        with bucket("mlp.down_proj"):
+            return ops.linear(m, self.w2)

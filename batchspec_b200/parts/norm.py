@@ -8,6 +8,7 @@ from typing import Dict, Optional
 import torch
 
 from ..kernels import ops
+from ..profiler import bucket
 from .base import NORMS, Norm, ParamSpec, Runtime, register_part
 
 
@@ -25,5 +26,6 @@ class RMSNorm(Norm):
 
     def forward(self, resid, delta=None):
         out = torch.empty(resid.shape, dtype=self.runtime.dtype, device=resid.device)
-        ops.add_rmsnorm(resid, delta, self.weight, self.eps, out)
+        with bucket("norm"):
+            ops.add_rmsnorm(resid, delta, self.weight, self.eps, out)
         return out

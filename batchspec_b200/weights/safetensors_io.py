@@ -13,6 +13,7 @@ from __future__ import annotations
 import json
 import mmap
 import struct
+import warnings
 from pathlib import Path
 from typing import Dict, Iterable, List, Tuple
 
@@ -60,7 +61,9 @@ class SafetensorsFile:
             return torch.empty(shape, dtype=dtype)
         if (end - begin) != count * torch.empty((), dtype=dtype).element_size():
             raise ValueError(f"{self.path}: tensor '{name}' byte range does not match its shape")
-        t = torch.frombuffer(self._map, dtype=dtype, count=count, offset=self._base + begin)
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore", UserWarning)       # the read-only map is never written through
+            t = torch.frombuffer(self._map, dtype=dtype, count=count, offset=self._base + begin)
         return t.reshape(shape)
 
 
