@@ -10,6 +10,7 @@ separate call.
 """
 from __future__ import annotations
 
+import time
 from pathlib import Path
 from typing import List, Optional, Sequence
 
@@ -128,6 +129,11 @@ class Engine:
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         return self.runner.step(entries)
 
+    def decode_session(self, req_ids, first_tokens):
+        """A device-resident greedy decode loop over live requests (see DecodeSession)."""
+        from .decode_session import DecodeSession
+        return DecodeSession(self, req_ids, first_tokens)
+
     # -- sampling ------------------------------------------------------------------
     def setup_sampling_params(self, temperature: float = 0.0, top_k: int = -1, top_p: float = 0.0,
                               force_budget: bool = False, seed: int = 0) -> None:
@@ -178,8 +184,11 @@ class Engine:
         sched = self.make_scheduler()
         sched.add_sequences(sequences)
         steps = tokens_in = 0
+        dec_steps = dec_tokens = dec_h2d = dec_d2h = 0
+        dec_seconds = 0.0
         prof = get_active_profiler()
         while not sched.is_done():
+            t_step = time.perf_counter()
             with prof.host_bucket("host.plan"):
                 work = sched.plan()
             if not work:
@@ -200,6 +209,15 @@ class Engine:
                 self.tracer.on_update(steps, sched, work, toks)
             steps += 1
             tokens_in += sum(w.n_tokens for w in work)
+            if len(wanting) == len(work) and all(w.n_tokens == 1 for w in work):      # a pure decode step
+                dec_steps += 1
+                dec_tokens += len(work)
+                dec_seconds += time.perf_counter() - t_step
+                dec_h2d += self.runner.last_h2d_bytes
+                dec_d2h += 4 * len(work)
         self.last_stats = dict(steps=steps, tokens_fed=tokens_in, preemptions=sched.num_preemptions,
-                               generated=sum(len(s.output_ids) for s in sched.completed))
+                               generated=sum(len(s.output_ids) for s in sched.completed),
+                               decode_steps=dec_steps, decode_tokens=dec_tokens, decode_seconds=dec_seconds,
+                               decode_h2d_bytes_per_step=dec_h2d // max(dec_steps, 1),
+                               decode_d2h_bytes_per_step=dec_d2h // max(dec_steps, 1))
         return sched.completed

@@ -115,8 +115,10 @@ class StepRunner:
         self.staging = _Staging(self.device)
         self.last_h2d_bytes = 0
 
-    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
-        """Pack the metadata of a step whose pages are already reserved."""
+    def build_context(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> StepContext:
+        """Pack the metadata of a step whose pages are already reserved.  With
+        ``device_tokens`` (int32 [n_tokens], already on the device) the entries'
+        token values are not looked at, only their counts."""
         cache = self.cache
         n = len(entries)
         lens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=n)
@@ -124,9 +126,12 @@ class StepRunner:
         qo = np.zeros(n + 1, dtype=np.int32)
         np.cumsum(lens, out=qo[1:])
         nnz = int(qo[-1])
-        tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64).reshape(-1) for e in entries])
-        if tokens.size and (tokens.min() < 0 or tokens.max() >= self.vocab_size):
-            raise ValueError(f"token id outside [0, {self.vocab_size}) in the step")
+        if device_tokens is None:
+            tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64).reshape(-1) for e in entries])
+            if tokens.size and (tokens.min() < 0 or tokens.max() >= self.vocab_size):
+                raise ValueError(f"token id outside [0, {self.vocab_size}) in the step")
+        else:
+            tokens = np.zeros(0, dtype=np.int64)
         tok_entry = np.repeat(np.arange(n, dtype=np.int32), lens)
         positions = (np.arange(nnz, dtype=np.int64) - np.repeat(qo[:-1].astype(np.int64), lens)
                      + np.repeat(before, lens)).astype(np.int32)
@@ -163,12 +168,13 @@ class StepRunner:
             k = 7 + 2 * gi
             tables.append(GroupTables(g.page_size, view(k), view(k + 1), group_parts[gi][0], group_parts[gi][1]))
         return StepContext(
-            n_tokens=nnz, n_entries=n, token_ids=view(0), positions=view(1), tok_entry=view(2), qo_indptr=view(3),
+            n_tokens=nnz, n_entries=n, token_ids=view(0) if device_tokens is None else device_tokens,
+            positions=view(1), tok_entry=view(2), qo_indptr=view(3),
             kv_len=view(4), state_slots=view(5), logit_rows=view(6), n_logit_rows=len(rows), tables=tables,
             max_q_len=int(lens.max()), max_kv_len=int(kv_len.max()), h_qo_indptr=qo, h_kv_len=kv_len,
             h_state_slots=slots, h_positions=positions)
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run the entries as one batch; float32 logits [sum of len(want), vocab] in
         the order of the entries and of their ``want``."""
         cache = self.cache
@@ -188,7 +194,7 @@ class StepRunner:
             raise OutOfPages("the step needs more pages than are free; nothing was run")
         for e in entries:
             cache.reserve(e.req_id, len(e.tokens))
-        ctx = self.build_context(entries)
+        ctx = self.build_context(entries, device_tokens)
         logits = self.model.forward(ctx)
         for e in entries:
             cache.commit(e.req_id, len(e.tokens))

@@ -1,0 +1,254 @@
+#!/usr/bin/env python3
+"""Headline benchmark: decode tokens per second of the Llama-3-8B-sized model
+(random weights, bfloat16) on one B200, plus prefill of 2,048 tokens and decode at
+batch 1 and 64.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one decode step of the whole batch.  Prints ONE JSON line.  The
+decode steps are timed on the device with CUDA events; every request holds a
+2,048-token prompt in the cache (put there by the engine's own prefill steps,
+outside the timed region) and grows by one token per step.  A decode step reads
+every weight once (15 GB, far beyond the 126 MB L2), so consecutive steps do not
+reuse cached inputs.  ``e2e`` is the same workload through ``Engine.generate``
+with host token ids in and out.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+PROMPT_LEN = 2048
+FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.is_file():
+        try:
+            d = json.loads(p.read_text())
+            out = dict(FALLBACK_PEAKS)
+            for k in out:
+                if isinstance(d.get(k), (int, float)) and d[k] > 0:
+                    out[k] = float(d[k])
+            out["source"] = "measured"
+            return out
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc, self.thread = [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6:
+                self.rows.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = [int(r[0]) for r in self.rows if r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows)]
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=reasons, samples=len(sm))
+
+
+def model_numbers(cfg, n_layers):
+    """Bytes of weights one decode step reads, cache bytes per token, flops per token."""
+    d, I, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    q, kv = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
+    per_layer = d * (q + 2 * kv) + q * d + 2 * I * d + I * d + 2 * d
+    weights = n_layers * per_layer + V * d + d                  # the head once; embedding rows are negligible
+    return dict(weight_bytes=2 * weights, kv_bytes_per_token=n_layers * 2 * kv * 2,
+                gemm_flops_per_token=2 * n_layers * (per_layer - 2 * d), head_flops_per_row=2 * V * d,
+                attn_flops_per_pair=4 * n_layers * q)
+
+
+def build_engine(layers):
+    import dataclasses
+    import torch
+    from batchspec_b200.config import get_config
+    from batchspec_b200.engine import Engine
+    cfg = get_config("llama-3-8b")
+    full_layers = cfg.num_hidden_layers
+    if layers and layers != full_layers:
+        cfg = dataclasses.replace(cfg, num_hidden_layers=layers)
+    eng = Engine(dtype="bfloat16", device="cuda:0")
+    eng.load_model(config=cfg, random_seed=0, draw_on_device=True)
+    eng.setup_sampling_params(temperature=0.0)
+    return eng, cfg, full_layers
+
+
+def prompts_for(batch, vocab, seed):
+    import random
+    rng = random.Random(seed)
+    return [[rng.randrange(vocab) for _ in range(PROMPT_LEN)] for _ in range(batch)]
+
+
+def run_decode(eng, cfg, batch, steps, warmup, page_size=16):
+    """Device-timed decode: prefill the prompts through the engine, then
+    ``warmup`` + ``steps`` decode steps; returns (ms per step, launches)."""
+    import torch
+    from batchspec_b200.engine import StepEntry
+    from batchspec_b200.kernels import ops
+    max_len = PROMPT_LEN + warmup + steps + 1
+    eng.setup_caches(max_batch_size=batch, max_seq_length=max_len, page_size=page_size)
+    prompts = prompts_for(batch, cfg.vocab_size, 1)
+    last = []
+    for i, p in enumerate(prompts):
+        eng.admit(i)
+        logits = eng.step([StepEntry(i, p, want=(len(p) - 1,))])
+        last.append(int(ops.argmax(logits).cpu()[0]))
+    session = eng.decode_session(list(range(batch)), last)
+    for _ in range(warmup):
+        session.step()
+    torch.cuda.synchronize()
+    l0 = session.launches
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        session.step()
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / steps
+    launches = session.launches - l0
+    session.close()
+    for i in range(batch):
+        eng.release(i)
+    return ms, launches
+
+
+def run_prefill(eng, cfg, warmup=2, iters=3, page_size=16):
+    import torch
+    from batchspec_b200.engine import StepEntry
+    eng.setup_caches(max_batch_size=1, max_seq_length=PROMPT_LEN + 16, page_size=page_size)
+    p = prompts_for(1, cfg.vocab_size, 2)[0]
+    times = []
+    for it in range(warmup + iters):
+        eng.admit("p")
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        eng.step([StepEntry("p", p, want=(PROMPT_LEN - 1,))])
+        e.record()
+        torch.cuda.synchronize()
+        eng.release("p")
+        if it >= warmup:
+            times.append(s.elapsed_time(e))
+    return statistics.median(times)
+
+
+def run_e2e(eng, cfg, batch, steps, page_size=16):
+    """The same decode workload through Engine.generate: host token ids in, host
+    token ids out; returns decode tokens per second over the decode steps and the
+    host<->device bytes per decode step."""
+    from batchspec_b200.engine import Sequence
+    eng.setup_caches(max_batch_size=batch, max_seq_length=PROMPT_LEN + steps + 2, page_size=page_size,
+                     prefill_chunk_size=PROMPT_LEN, max_tokens_per_step=PROMPT_LEN)
+    eng.ignore_eos = True
+    seqs = [Sequence(i, p, max_new_tokens=steps + 1) for i, p in enumerate(prompts_for(batch, cfg.vocab_size, 3))]
+    eng.generate(seqs)
+    st = eng.last_stats
+    return st["decode_tokens"] / st["decode_seconds"], st["decode_h2d_bytes_per_step"], st["decode_d2h_bytes_per_step"]
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0: all)")
+    ap.add_argument("--skip-points", action="store_true", help="only the headline batch (no prefill, b1, b64, e2e)")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "siihwanpark/BatchSpec has no setup.py/pyproject.toml (pip: 'not installable') and its "
+                          "standard benchmark path calls StandardEngine.prefill/decode, which do not exist in the tree"}))
+        return 0
+    if a.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
+        return 2
+    a.warmup = max(a.warmup, 3)
+    import torch
+    pk = peaks()
+    eng, cfg, full_layers = build_engine(a.layers)
+    L = cfg.num_hidden_layers
+    nums = model_numbers(cfg, L)
+    clocks = ClockSampler()
+    clocks.start()
+    ms, launches = run_decode(eng, cfg, a.batch, a.steps, a.warmup)
+    clock_rec = clocks.stop()
+    value = a.batch * 1000.0 / ms
+    mean_ctx = PROMPT_LEN + a.warmup + (a.steps + 1) / 2.0
+    step_bytes = nums["weight_bytes"] + a.batch * mean_ctx * nums["kv_bytes_per_token"]
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    out = {
+        "metric": "decode tok/s (Llama-3-8B sizes, bf16, batch 8, 2048-token prompts)", "value": round(value, 2),
+        "unit": "tok/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "impl": "ours",
+        "config": {"model": "llama-3-8b", "global_batch": a.batch, "seq_len": PROMPT_LEN, "parallelism": "single",
+                   "layers": L, "layers_full": full_layers, "hidden": cfg.hidden_size,
+                   "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+                   "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "page_size": 16,
+                   "weights": "random N(0,0.02)", "l2": "inputs_exceed_l2 (15 GB of weights per step)",
+                   "peaks": pk["source"]},
+        "gpu_launches": launches, "clocks": clock_rec,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+    }
+    if not a.skip_points:
+        pms = run_prefill(eng, cfg)
+        flops = (PROMPT_LEN * nums["gemm_flops_per_token"] + nums["head_flops_per_row"]
+                 + nums["attn_flops_per_pair"] * PROMPT_LEN * (PROMPT_LEN + 1) / 2)
+        out["prefill"] = {"value": round(PROMPT_LEN / (pms * 1e-3), 1), "tokens": PROMPT_LEN, "ms": round(pms, 3),
+                          "frac": round(flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+        points = {}
+        for b in (1, 64):
+            bms, _ = run_decode(eng, cfg, b, a.steps, a.warmup)
+            points[f"decode_b{b}"] = round(b * 1000.0 / bms, 2)
+        out["points"] = points
+        e2e, h2d, d2h = run_e2e(eng, cfg, a.batch, a.steps)
+        out["e2e"] = {"value": round(e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
