@@ -1,0 +1,522 @@
+// Paged causal attention in bfloat16 on the tensor cores (mma.sync m16n8k16,
+// float32 scores, softmax statistics and accumulators), head_dim 64 / 128 / 256,
+// any number of heads and groups, any page size.
+//
+// Rows of a tile are (query token, query head of one kv group) pairs, so the G
+// query heads that share a kv head also share every K/V tile that is loaded.
+//
+//  * attn_decode_kernel: requests with few new tokens (q_len <= max_q_short).  A
+//    CTA owns one 16-row tile of one (request, kv head) and ONE SPLIT of its keys;
+//    its 4 warps take different 16-key blocks of every 64-key tile and are
+//    combined through shared memory at the end.  With more than one split the
+//    un-normalised partial results go to scratch and attn_merge_kernel joins them.
+//  * attn_prefill_kernel: requests with many new tokens.  A CTA owns 64 rows
+//    (4 warps x 16) of one (request, kv head) and walks all visible keys.
+//
+// Both skip requests that belong to the other kernel, so a mixed step launches
+// both.  Cache layer layout: [pages][2 (k, v)][Hkv][page_size][HD].
+#include "common.cuh"
+#include <math.h>
+using namespace bspec;
+
+namespace {
+
+constexpr int KT = 64;          // keys per shared-memory tile
+constexpr int NTHREADS = 128;   // 4 warps
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const uint32_t d = smem_u32(dst);
+  const int n = valid ? 16 : 0;   // src-size 0: the 16 bytes are zero-filled, src is not read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// element offset of (row, col) in a [rows][HD] bf16 tile whose 16-byte chunks are XOR-swizzled by the row
+template <int HD> __device__ __forceinline__ int swz(int row, int col) {
+  return row * HD + ((((col >> 3) ^ (row & 7))) << 3) + (col & 7);
+}
+
+struct TileGeom {
+  int e, g, q_begin, q_len, pos0, G, rows_total;
+};
+
+// Load K and V rows [k0, k0 + KT) of one kv head into swizzled shared tiles; keys outside [k_lo, k_end) are
+// zero-filled and their table entries (which may be released pages) are not read.
+template <int HD>
+__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* Ks, __nv_bfloat16* Vs, const __nv_bfloat16* cache,
+                                             const int* table, int k0, int k_lo, int k_end, int page_size, int Hkv,
+                                             int g) {
+  constexpr int CH = HD / 8;                     // 16-byte chunks per row
+  const size_t page_elems = (size_t)Hkv * page_size * HD;
+  for (int idx = threadIdx.x; idx < KT * CH; idx += NTHREADS) {
+    const int row = idx / CH, ch = idx - row * CH;
+    const int key = k0 + row;
+    const bool valid = key < k_end && key >= k_lo;
+    const __nv_bfloat16* src = cache;
+    if (valid) {
+      const int page = table[key / page_size];
+      src = cache + (size_t)page * 2 * page_elems + ((size_t)g * page_size + (key % page_size)) * HD + ch * 8;
+    }
+    const int off = row * HD + ((ch ^ (row & 7)) << 3);
+    cp_async16(Ks + off, src, valid);
+    cp_async16(Vs + off, src + (valid ? page_elems : 0), valid);
+  }
+}
+
+// Load a 16-row query tile (rows = (token, head in group)) into swizzled shared memory, zero beyond rows_total.
+template <int HD>
+__device__ __forceinline__ void load_q_tile(__nv_bfloat16* Qs, const __nv_bfloat16* q, long long q_row_stride,
+                                            const TileGeom& t, int row0, int nrows) {
+  constexpr int CH = HD / 8;
+  for (int idx = threadIdx.x; idx < nrows * CH; idx += NTHREADS) {
+    const int row = idx / CH, ch = idx - row * CH;
+    const int r = row0 + row;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < t.rows_total) {
+      const int qi = r / t.G, h = t.g * t.G + (r - qi * t.G);
+      v = *reinterpret_cast<const uint4*>(q + (size_t)(t.q_begin + qi) * q_row_stride + (size_t)h * HD + ch * 8);
+    }
+    *reinterpret_cast<uint4*>(Qs + row * HD + ((ch ^ (row & 7)) << 3)) = v;
+  }
+}
+
+// One warp: scores of its 16 rows against 16 keys (kb .. kb+15 of the tile), online softmax, P*V.
+// qf: A fragments of the rows for every 16-dim step.  Row state (m, l) per thread for rows lane/4 and lane/4+8.
+template <int HD>
+__device__ __forceinline__ void block16(const uint32_t (&qf)[HD / 16][4], const __nv_bfloat16* Ks,
+                                        const __nv_bfloat16* Vs, int kb, int key0, int row_lim0, int row_lim1,
+                                        int row_lo0, int row_lo1, int k_end, float scale_log2, float (&m)[2],
+                                        float (&l)[2], float (&o)[HD / 8][4]) {
+  const int lane = threadIdx.x & 31;
+  float s[2][4];
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s[nt][i] = 0.f;
+  const int mat = lane >> 3, r8 = lane & 7;
+#pragma unroll
+  for (int ks = 0; ks < HD / 16; ++ks) {
+    uint32_t b[4];
+    ldmatrix_x4(b, Ks + swz<HD>(kb + 8 * (mat >> 1) + r8, 16 * ks + 8 * (mat & 1)));
+    mma_bf16(s[0], qf[ks], b[0], b[1]);
+    mma_bf16(s[1], qf[ks], b[2], b[3]);
+  }
+  // mask and scale; element i of n-tile nt: row (i >> 1), key column 2*(lane&3) + (i&1)
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int key = key0 + kb + 8 * nt + 2 * (lane & 3) + (i & 1);
+      const int lim = (i >> 1) ? row_lim1 : row_lim0, lo = (i >> 1) ? row_lo1 : row_lo0;
+      const bool ok = key <= lim && key >= lo && key < k_end;
+      s[nt][i] = ok ? s[nt][i] * scale_log2 : -INFINITY;
+      mx[i >> 1] = fmaxf(mx[i >> 1], s[nt][i]);
+    }
+  float corr[2], msafe[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+    const float mn = fmaxf(m[r], mx[r]);
+    msafe[r] = (mn == -INFINITY) ? 0.f : mn;
+    corr[r] = exp2f(m[r] - msafe[r]);          // m = -inf -> 0
+    m[r] = mn;
+    l[r] *= corr[r];
+  }
+  uint32_t pf[4];
+  {
+    float p[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        p[nt][i] = exp2f(s[nt][i] - msafe[i >> 1]);
+        l[i >> 1] += p[nt][i];
+      }
+    pf[0] = pack_bf16(p[0][0], p[0][1]);
+    pf[1] = pack_bf16(p[0][2], p[0][3]);
+    pf[2] = pack_bf16(p[1][0], p[1][1]);
+    pf[3] = pack_bf16(p[1][2], p[1][3]);
+  }
+#pragma unroll
+  for (int nd = 0; nd < HD / 8; nd += 2) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      o[nd][i] *= corr[i >> 1];
+      o[nd + 1][i] *= corr[i >> 1];
+    }
+    uint32_t b[4];
+    ldmatrix_x4_trans(b, Vs + swz<HD>(kb + 8 * (mat & 1) + r8, 8 * (nd + (mat >> 1))));
+    mma_bf16(o[nd], pf, b[0], b[1]);
+    mma_bf16(o[nd + 1], pf, b[2], b[3]);
+  }
+}
+
+__device__ __forceinline__ bool tile_geometry(TileGeom& t, const int* qo_indptr, const int* positions, int e, int g,
+                                              int Hq, int Hkv) {
+  t.e = e;
+  t.g = g;
+  t.q_begin = qo_indptr[e];
+  t.q_len = qo_indptr[e + 1] - t.q_begin;
+  if (t.q_len <= 0) return false;
+  t.pos0 = positions[t.q_begin];
+  t.G = Hq / Hkv;
+  t.rows_total = t.q_len * t.G;
+  return true;
+}
+
+// ------------------------------------------------------------------------------------ decode (split keys)
+template <int HD>
+__global__ void __launch_bounds__(NTHREADS)
+attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride, __nv_bfloat16* __restrict__ out,
+                   float* __restrict__ o_part, float* __restrict__ ml_part, const __nv_bfloat16* __restrict__ cache,
+                   const int* __restrict__ qo_indptr, const int* __restrict__ positions,
+                   const int* __restrict__ kv_indptr, const int* __restrict__ kv_indices, int Hq, int Hkv,
+                   int page_size, float scale_log2, int window, int n_splits, int row_tiles, int max_q_short) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);           // [16][HD]
+  __nv_bfloat16* KV = Qs + 16 * HD;                                        // 2 stages x (K [KT][HD], V [KT][HD])
+  const int split = blockIdx.x, g = blockIdx.y;
+  const int e = blockIdx.z / row_tiles, rt = blockIdx.z - e * row_tiles;
+  TileGeom t;
+  if (!tile_geometry(t, qo_indptr, positions, e, g, Hq, Hkv)) return;
+  if (t.q_len > max_q_short) return;
+  const int row0 = rt * 16;
+  if (row0 >= t.rows_total) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qi_lo = row0 / t.G, qi_hi = min(t.q_len - 1, (row0 + 15) / t.G);
+  const int hi_key = t.pos0 + qi_hi;
+  const int lo_key = window > 0 ? max(0, t.pos0 + qi_lo - window + 1) : 0;
+  const int lo_al = (lo_key / KT) * KT;
+  const int n_keys = hi_key + 1 - lo_al;
+  const int chunk = ((((n_keys + n_splits - 1) / n_splits) + KT - 1) / KT) * KT;
+  const int k_begin = lo_al + split * chunk;
+  const int k_end = min(hi_key + 1, k_begin + chunk);
+  const int* table = kv_indices + kv_indptr[e];
+
+  // per-thread rows: lane/4 and lane/4 + 8 of the tile
+  int lim[2], lo[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = row0 + (lane >> 2) + 8 * r;
+    const int qi = row / t.G;
+    lim[r] = row < t.rows_total ? t.pos0 + qi : -1;
+    lo[r] = window > 0 ? max(0, t.pos0 + qi - window + 1) : 0;
+  }
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+
+  if (k_begin < k_end) {
+    load_q_tile<HD>(Qs, q, q_row_stride, t, row0, 16);
+    const int n_tiles = (k_end - k_begin + KT - 1) / KT;
+    load_kv_tile<HD>(KV, KV + KT * HD, cache, table, k_begin, lo_key, k_end, page_size, Hkv, g);
+    cp_async_commit();
+    __syncthreads();
+    uint32_t qf[HD / 16][4];
+    {
+      const int mat = lane >> 3, r8 = lane & 7;
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks)
+        ldmatrix_x4(qf[ks], Qs + swz<HD>(8 * (mat & 1) + r8, 16 * ks + 8 * (mat >> 1)));
+    }
+    for (int it = 0; it < n_tiles; ++it) {
+      __nv_bfloat16* Ks = KV + (it & 1) * 2 * KT * HD;
+      __nv_bfloat16* Vs = Ks + KT * HD;
+      if (it + 1 < n_tiles) {
+        __nv_bfloat16* Kn = KV + ((it + 1) & 1) * 2 * KT * HD;
+        load_kv_tile<HD>(Kn, Kn + KT * HD, cache, table, k_begin + (it + 1) * KT, lo_key, k_end, page_size, Hkv, g);
+        cp_async_commit();
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
+      }
+      __syncthreads();
+      const int key0 = k_begin + it * KT;
+      if (key0 + 16 * warp < k_end)
+        block16<HD>(qf, Ks, Vs, 16 * warp, key0, lim[0], lim[1], lo[0], lo[1], k_end, scale_log2, m, l, o);
+      __syncthreads();
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+  // combine the 4 warps through shared memory (reusing the K/V stages)
+  float* Os = reinterpret_cast<float*>(KV);                 // [4][16][HD]
+  float* Ms = Os + 4 * 16 * HD;                             // [4][16]
+  float* Ls = Ms + 4 * 16;                                  // [4][16]
+#pragma unroll
+  for (int nd = 0; nd < HD / 8; ++nd)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = (lane >> 2) + 8 * (i >> 1), col = 8 * nd + 2 * (lane & 3) + (i & 1);
+      Os[(warp * 16 + row) * HD + col] = o[nd][i];
+    }
+  if ((lane & 3) == 0) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      Ms[warp * 16 + (lane >> 2) + 8 * r] = m[r];
+      Ls[warp * 16 + (lane >> 2) + 8 * r] = l[r];
+    }
+  }
+  __syncthreads();
+  const int nrows = min(16, t.rows_total - row0);
+  for (int idx = threadIdx.x; idx < nrows * HD; idx += NTHREADS) {
+    const int row = idx / HD, col = idx - row * HD;
+    float mt = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mt = fmaxf(mt, Ms[w * 16 + row]);
+    float lt = 0.f, acc = 0.f;
+    if (mt != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float f = exp2f(Ms[w * 16 + row] - mt);
+        lt += Ls[w * 16 + row] * f;
+        acc += Os[(w * 16 + row) * HD + col] * f;
+      }
+    }
+    const int r = row0 + row, qi = r / t.G, h = g * t.G + (r - qi * t.G);
+    const size_t th = (size_t)(t.q_begin + qi) * Hq + h;
+    if (n_splits == 1) {
+      out[th * HD + col] = __float2bfloat16_rn(lt > 0.f ? acc / lt : 0.f);
+    } else {
+      o_part[(th * n_splits + split) * HD + col] = acc;
+      if (col == 0) {
+        ml_part[(th * n_splits + split) * 2] = mt;
+        ml_part[(th * n_splits + split) * 2 + 1] = lt;
+      }
+    }
+  }
+}
+
+// Join the splits of every (token, head): one warp each.
+template <int HD>
+__global__ void attn_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
+                                  __nv_bfloat16* __restrict__ out, const int* __restrict__ qo_indptr,
+                                  const int* __restrict__ tok_entry, int n_tokens, int Hq, int n_splits,
+                                  int max_q_short) {
+  const int th = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (th >= n_tokens * Hq) return;
+  const int tkn = th / Hq;
+  const int e = tok_entry[tkn];
+  if (qo_indptr[e + 1] - qo_indptr[e] > max_q_short) return;      // that request went through the prefill kernel
+  const int lane = threadIdx.x & 31;
+  float mt = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) mt = fmaxf(mt, ml_part[((size_t)th * n_splits + s) * 2]);
+  float lt = 0.f;
+  float acc[HD / 32];
+#pragma unroll
+  for (int i = 0; i < HD / 32; ++i) acc[i] = 0.f;
+  if (mt != -INFINITY) {
+    for (int s = 0; s < n_splits; ++s) {
+      const float ms = ml_part[((size_t)th * n_splits + s) * 2];
+      if (ms == -INFINITY) continue;
+      const float f = exp2f(ms - mt);
+      lt += ml_part[((size_t)th * n_splits + s) * 2 + 1] * f;
+      const float* op = o_part + ((size_t)th * n_splits + s) * HD;
+#pragma unroll
+      for (int i = 0; i < HD / 32; ++i) acc[i] += op[lane + 32 * i] * f;
+    }
+  }
+  const float inv = lt > 0.f ? 1.f / lt : 0.f;
+#pragma unroll
+  for (int i = 0; i < HD / 32; ++i) out[(size_t)th * HD + lane + 32 * i] = __float2bfloat16_rn(acc[i] * inv);
+}
+
+// ------------------------------------------------------------------------------------ prefill (64 rows per CTA)
+template <int HD>
+__global__ void __launch_bounds__(NTHREADS)
+attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride, __nv_bfloat16* __restrict__ out,
+                    const __nv_bfloat16* __restrict__ cache, const int* __restrict__ qo_indptr,
+                    const int* __restrict__ positions, const int* __restrict__ kv_indptr,
+                    const int* __restrict__ kv_indices, int Hq, int Hkv, int page_size, float scale_log2, int window,
+                    int min_q_long) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);           // [64][HD]
+  __nv_bfloat16* KV = Qs + 64 * HD;                                        // 2 stages x (K, V)
+  const int g = blockIdx.y, e = blockIdx.z;
+  TileGeom t;
+  if (!tile_geometry(t, qo_indptr, positions, e, g, Hq, Hkv)) return;
+  if (t.q_len < min_q_long) return;
+  // heavy (late) tiles first: they see the most keys
+  const int n_row_tiles = (t.rows_total + 63) / 64;
+  if ((int)blockIdx.x >= n_row_tiles) return;
+  const int row0 = (n_row_tiles - 1 - blockIdx.x) * 64;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qi_lo = row0 / t.G, qi_hi = min(t.q_len - 1, (row0 + 63) / t.G);
+  const int hi_key = t.pos0 + qi_hi;
+  const int lo_key = window > 0 ? max(0, t.pos0 + qi_lo - window + 1) : 0;
+  const int k_begin = (lo_key / KT) * KT, k_end = hi_key + 1;
+  const int* table = kv_indices + kv_indptr[e];
+  const int wrow0 = row0 + 16 * warp;
+  int lim[2], lo[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = wrow0 + (lane >> 2) + 8 * r;
+    const int qi = row / t.G;
+    lim[r] = row < t.rows_total ? t.pos0 + qi : -1;
+    lo[r] = window > 0 ? max(0, t.pos0 + qi - window + 1) : 0;
+  }
+  // keys this warp's rows can see at all (skip tiles beyond its own last row)
+  const int warp_hi = t.pos0 + min(t.q_len - 1, (wrow0 + 15) / t.G);
+  const bool warp_live = wrow0 < t.rows_total;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+
+  load_q_tile<HD>(Qs, q, q_row_stride, t, row0, 64);
+  const int n_tiles = (k_end - k_begin + KT - 1) / KT;
+  load_kv_tile<HD>(KV, KV + KT * HD, cache, table, k_begin, lo_key, k_end, page_size, Hkv, g);
+  cp_async_commit();
+  __syncthreads();
+  uint32_t qf[HD / 16][4];
+  {
+    const int mat = lane >> 3, r8 = lane & 7;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks)
+      ldmatrix_x4(qf[ks], Qs + swz<HD>(16 * warp + 8 * (mat & 1) + r8, 16 * ks + 8 * (mat >> 1)));
+  }
+  for (int it = 0; it < n_tiles; ++it) {
+    __nv_bfloat16* Ks = KV + (it & 1) * 2 * KT * HD;
+    __nv_bfloat16* Vs = Ks + KT * HD;
+    if (it + 1 < n_tiles) {
+      __nv_bfloat16* Kn = KV + ((it + 1) & 1) * 2 * KT * HD;
+      load_kv_tile<HD>(Kn, Kn + KT * HD, cache, table, k_begin + (it + 1) * KT, lo_key, k_end, page_size, Hkv, g);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const int key0 = k_begin + it * KT;
+    if (warp_live) {
+#pragma unroll
+      for (int kb = 0; kb < KT; kb += 16)
+        if (key0 + kb <= warp_hi)
+          block16<HD>(qf, Ks, Vs, kb, key0, lim[0], lim[1], lo[0], lo[1], k_end, scale_log2, m, l, o);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = wrow0 + (lane >> 2) + 8 * r;
+    if (row >= t.rows_total) continue;
+    const int qi = row / t.G, h = g * t.G + (row - qi * t.G);
+    const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+    __nv_bfloat16* op = out + ((size_t)(t.q_begin + qi) * Hq + h) * HD;
+#pragma unroll
+    for (int nd = 0; nd < HD / 8; ++nd) {
+      const int col = 8 * nd + 2 * (lane & 3);
+      *reinterpret_cast<__nv_bfloat162*>(op + col) = __floats2bfloat162_rn(o[nd][2 * r] * inv, o[nd][2 * r + 1] * inv);
+    }
+  }
+}
+
+template <int HD> size_t decode_smem() {
+  const size_t stages = (size_t)(16 + 4 * KT) * HD * 2;
+  const size_t combine = (size_t)16 * HD * 2 + (size_t)(4 * 16 * HD + 8 * 16) * 4;
+  return stages > combine ? stages : combine;
+}
+template <int HD> size_t prefill_smem() { return (size_t)(64 + 4 * KT) * HD * 2; }
+
+template <int HD>
+int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, float* o_part, float* ml_part,
+           const __nv_bfloat16* cache, const int* qo_indptr, const int* positions, const int* tok_entry,
+           const int* kv_indptr, const int* kv_indices, int n_entries, int n_tokens, int max_q_len, int Hq, int Hkv,
+           int page_size, float scale, int window, int n_splits, int max_q_short, int run_decode, int run_prefill,
+           cudaStream_t stream) {
+  const float scale_log2 = scale * 1.4426950408889634f;
+  const int G = Hq / Hkv;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem<HD>());
+    cudaFuncSetAttribute(attn_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_smem<HD>());
+    attr_set = true;
+  }
+  if (run_decode) {
+    const int short_q = max_q_len < max_q_short ? max_q_len : max_q_short;
+    const int row_tiles = (short_q * G + 15) / 16;
+    dim3 grid(n_splits, Hkv, n_entries * row_tiles);
+    if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidConfiguration;
+    attn_decode_kernel<HD><<<grid, NTHREADS, decode_smem<HD>(), stream>>>(
+        q, q_row_stride, out, o_part, ml_part, cache, qo_indptr, positions, kv_indptr, kv_indices, Hq, Hkv, page_size,
+        scale_log2, window, n_splits, row_tiles, max_q_short);
+    int err = (int)cudaGetLastError();
+    if (err) return err;
+    if (n_splits > 1) {
+      const int warps = 4;
+      attn_merge_kernel<HD><<<(n_tokens * Hq + warps - 1) / warps, warps * 32, 0, stream>>>(
+          o_part, ml_part, out, qo_indptr, tok_entry, n_tokens, Hq, n_splits, max_q_short);
+      err = (int)cudaGetLastError();
+      if (err) return err;
+    }
+  }
+  if (run_prefill) {
+    dim3 grid((max_q_len * G + 63) / 64, Hkv, n_entries);
+    if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidConfiguration;
+    attn_prefill_kernel<HD><<<grid, NTHREADS, prefill_smem<HD>(), stream>>>(
+        q, q_row_stride, out, cache, qo_indptr, positions, kv_indptr, kv_indices, Hq, Hkv, page_size, scale_log2,
+        window, max_q_short + 1);
+    return (int)cudaGetLastError();
+  }
+  return 0;
+}
+}  // namespace
+
+// Requests with q_len <= max_q_short go through the split-key kernel (if run_decode), the others through the
+// 64-row kernel (if run_prefill).  n_splits > 1 needs scratch: o_part float32 [n_tokens * Hq * n_splits * hd],
+// ml_part float32 [n_tokens * Hq * n_splits * 2].  Returns cudaErrorInvalidValue for an unsupported head_dim.
+BSPEC_API int bspec_attention_bf16(const void* q, long long q_row_stride, void* out, float* o_part, float* ml_part,
+                                   const void* cache, const int* qo_indptr, const int* positions,
+                                   const int* tok_entry, const int* kv_indptr, const int* kv_indices, int n_entries,
+                                   int n_tokens, int max_q_len, int Hq, int Hkv, int hd, int page_size, float scale,
+                                   int window, int n_splits, int max_q_short, int run_decode, int run_prefill,
+                                   cudaStream_t stream) {
+  if (n_entries <= 0 || n_tokens <= 0) return 0;
+  if (Hq % Hkv != 0 || n_splits < 1) return (int)cudaErrorInvalidValue;
+#define GO(HDV)                                                                                                    \
+  return launch<HDV>((const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, o_part, ml_part,                  \
+                     (const __nv_bfloat16*)cache, qo_indptr, positions, tok_entry, kv_indptr, kv_indices, n_entries, \
+                     n_tokens, max_q_len, Hq, Hkv, page_size, scale, window, n_splits, max_q_short, run_decode,      \
+                     run_prefill, stream)
+  if (hd == 64) GO(64);
+  if (hd == 128) GO(128);
+  if (hd == 256) GO(256);
+#undef GO
+  return (int)cudaErrorInvalidValue;
+}

@@ -172,7 +172,7 @@ class StepRunner:
             positions=view(1), tok_entry=view(2), qo_indptr=view(3),
             kv_len=view(4), state_slots=view(5), logit_rows=view(6), n_logit_rows=len(rows), tables=tables,
             max_q_len=int(lens.max()), max_kv_len=int(kv_len.max()), h_qo_indptr=qo, h_kv_len=kv_len,
-            h_state_slots=slots, h_positions=positions)
+            h_state_slots=slots, h_positions=positions, extras={"min_q_len": int(lens.min())})
 
     def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run the entries as one batch; float32 logits [sum of len(want), vocab] in

@@ -47,6 +47,9 @@ _SIGNATURES = {
     "bspec_rope_inplace": [c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "bspec_attention_generic": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "bspec_attention_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                             c_int, c_int, c_int, c_int, c_void_p],
     "bspec_sgemm_tn": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p],
     "bspec_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p],
     "bspec_sample": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ulonglong, c_void_p,
@@ -181,15 +184,53 @@ def rope_inplace(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tenso
 
 # ---------------------------------------------------------------------------- attention
 
+FORCE_GENERIC_ATTENTION = False      # tests set this to compare the tensor-core kernels with the generic one
+_SM_COUNT = 148
+
+
+def attention_splits(n_entries: int, n_kv_heads: int, group: int, max_q_len: int, max_kv_len: int) -> int:
+    """How many ways the split-key kernel cuts each request's keys: enough CTAs to
+    fill the device, never chunks shorter than 128 keys.  1 when the step also
+    holds long portions (they go to the 64-row kernel and already fill it)."""
+    short = max(1, 16 // group)
+    if max_q_len > short:
+        return 1
+    row_tiles = -(-(max_q_len * group) // 16)
+    ctas = max(1, n_entries * n_kv_heads * row_tiles)
+    return max(1, min(-(-(_SM_COUNT * 4) // ctas), -(-max_kv_len // 128), 64))
+
+
 def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, ctx, tables, n_heads: int,
                     n_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
     """Causal attention of the step's tokens over their requests' cached keys.
     ``qkv``: [n, >= n_heads*head_dim] rows with the (already rotated) query heads
     first.  ``ctx`` gives qo_indptr / positions / n_entries / max_q_len, ``tables``
-    the block tables of the cache group."""
+    the block tables of the cache group.  bfloat16 with head_dim 64/128/256 runs
+    on the tensor-core kernels; everything else on the generic float32-math kernel."""
     _require_cuda(qkv, out, cache)
     assert qkv.stride(1) == 1 and out.is_contiguous() and out.dtype == qkv.dtype == cache.dtype
-    _check(load_library().bspec_attention_generic(
+    lib = load_library()
+    if qkv.dtype == torch.bfloat16 and head_dim in (64, 128, 256) and not FORCE_GENERIC_ATTENTION:
+        group = n_heads // n_kv_heads
+        short = max(1, 16 // group)
+        n_splits = ctx.extras.get("attn_splits") or attention_splits(ctx.n_entries, n_kv_heads, group, ctx.max_q_len,
+                                                                     ctx.max_kv_len)
+        o_part = ml_part = None
+        if n_splits > 1:
+            o_part = torch.empty((ctx.n_tokens * n_heads * n_splits * head_dim,), dtype=torch.float32, device=qkv.device)
+            ml_part = torch.empty((ctx.n_tokens * n_heads * n_splits * 2,), dtype=torch.float32, device=qkv.device)
+        run_decode = int(ctx.extras.get("min_q_len", 1) <= short)
+        run_prefill = int(ctx.max_q_len > short)
+        _check(lib.bspec_attention_bf16(
+            qkv.data_ptr(), qkv.stride(0), out.data_ptr(), _ptr(o_part), _ptr(ml_part), cache.data_ptr(),
+            ctx.qo_indptr.data_ptr(), ctx.positions.data_ptr(), ctx.tok_entry.data_ptr(), tables.kv_indptr.data_ptr(),
+            tables.kv_indices.data_ptr(), ctx.n_entries, ctx.n_tokens, ctx.max_q_len, n_heads, n_kv_heads, head_dim,
+            tables.page_size, float(scale), int(window), n_splits, short, run_decode, run_prefill, _stream()),
+            "attention_bf16")
+        global _launches
+        _launches += (1 if n_splits > 1 and run_decode else 0) + (1 if run_decode and run_prefill else 0)
+        return
+    _check(lib.bspec_attention_generic(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), cache.data_ptr(), _dtype_code(qkv.dtype),
         ctx.qo_indptr.data_ptr(), ctx.positions.data_ptr(), tables.kv_indptr.data_ptr(), tables.kv_indices.data_ptr(),
         ctx.n_entries, ctx.max_q_len, n_heads, n_kv_heads, head_dim, tables.page_size, float(scale), int(window),

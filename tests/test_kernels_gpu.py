@@ -1,0 +1,305 @@
+"""Each CUDA kernel alone against a plain float32 PyTorch reference of the same
+operation, at sizes other than the engine's tiny models: widths and vocabularies
+that are no power of two, head sizes from 16 to 256, odd group sizes, page sizes
+from 1 up, ragged batches."""
+import math
+import random
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from batchspec_b200.kernels import ops
+    ops.load_library()
+    return ops
+
+
+def tol(dtype):
+    return dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,d,vocab", [(1, 48, 7), (37, 1000, 333), (5, 4096, 50)])
+def test_embed(ops, dtype, n, d, vocab):
+    g = torch.Generator(device=DEV).manual_seed(0)
+    table = torch.randn(vocab, d, device=DEV, generator=g).to(dtype)
+    ids = torch.randint(0, vocab, (n,), device=DEV, generator=g, dtype=torch.int32)
+    out = torch.empty(n, d, device=DEV)
+    ops.embed(ids, table, out, 1.5)
+    assert torch.equal(out, table[ids.long()].float() * 1.5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("wdtype", [torch.float32, None])
+@pytest.mark.parametrize("n,d,eps", [(3, 96, 1e-6), (17, 1000, 1e-5), (2, 4096, 1e-2), (1, 6144, 1e-5)])
+def test_add_rmsnorm(ops, dtype, wdtype, n, d, eps):
+    g = torch.Generator(device=DEV).manual_seed(1)
+    resid = torch.randn(n, d, device=DEV, generator=g) * 3
+    delta = torch.randn(n, d, device=DEV, generator=g).to(dtype)
+    w = (1 + 0.1 * torch.randn(d, device=DEV, generator=g)).to(wdtype or dtype)
+    want_resid = resid + delta.float()
+    normed = want_resid * torch.rsqrt((want_resid * want_resid).mean(-1, keepdim=True) + eps)
+    want = (normed.to(dtype).float() * w.float()).to(dtype)           # cast, then scale (reference order)
+    out = torch.empty(n, d, device=DEV, dtype=dtype)
+    r = resid.clone()
+    ops.add_rmsnorm(r, delta, w, eps, out)
+    assert torch.equal(r, want_resid), "the residual sum is exact float32"
+    torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+    out2 = torch.empty_like(out)
+    r2 = want_resid.clone()
+    ops.add_rmsnorm(r2, None, w, eps, out2)                            # without a pending branch
+    assert torch.equal(out, out2) and torch.equal(r2, want_resid)
+
+
+def test_gather_rows_add(ops):
+    g = torch.Generator(device=DEV).manual_seed(2)
+    resid = torch.randn(9, 200, device=DEV, generator=g)
+    pend = torch.randn(9, 200, device=DEV, generator=g).bfloat16()
+    rows = torch.tensor([8, 0, 3, 3], device=DEV, dtype=torch.int32)
+    out = torch.empty(4, 200, device=DEV)
+    ops.gather_rows_add(resid, pend, rows, out)
+    assert torch.equal(out, resid[rows.long()] + pend[rows.long()].float())
+    ops.gather_rows_add(resid, None, rows, out)
+    assert torch.equal(out, resid[rows.long()])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,inter", [(1, 7), (13, 176), (4, 14336)])
+def test_silu_mul(ops, dtype, n, inter):
+    g = torch.Generator(device=DEV).manual_seed(3)
+    u = (torch.randn(n, 2 * inter, device=DEV, generator=g) * 4).to(dtype)
+    out = torch.empty(n, inter, device=DEV, dtype=dtype)
+    ops.silu_mul(u, out)
+    gate, up = u[:, :inter].float(), u[:, inter:].float()
+    torch.testing.assert_close(out.float(), (gate * torch.sigmoid(gate) * up).to(dtype).float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 5, 3), (7, 130, 96), (64, 64, 16), (65, 1000, 257), (300, 33, 1024)])
+def test_sgemm_is_true_float32(ops, M, N, K):
+    g = torch.Generator(device=DEV).manual_seed(4)
+    a = torch.randn(M, K, device=DEV, generator=g)
+    w = torch.randn(N, K, device=DEV, generator=g)
+    got = ops.linear(a, w)
+    want = (a.double() @ w.double().T)
+    err = (got.double() - want).abs().max().item()
+    assert err <= 1e-6 * K ** 0.5 * 16, err                       # float32 accumulation error, far below tf32's 1e-3
+    # a row's result does not depend on the other rows of the batch
+    assert torch.equal(got[:1], ops.linear(a[:1].contiguous(), w))
+
+
+def _rope_reference(x, pos, inv_freq, rot, interleaved):
+    ang = pos.float()[:, None] * inv_freq[None, :]
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    out = x.clone()
+    if interleaved:
+        a, b = x[..., 0:rot:2], x[..., 1:rot:2]
+        out[..., 0:rot:2], out[..., 1:rot:2] = a * c - b * s, a * s + b * c
+    else:
+        a, b = x[..., :rot // 2], x[..., rot // 2:rot]
+        out[..., :rot // 2], out[..., rot // 2:rot] = a * c - b * s, a * s + b * c
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("Hq,Hkv,hd,rot,inter,ps", [(4, 2, 16, 16, False, 4), (3, 1, 32, 32, True, 1),
+                                                     (6, 3, 48, 24, False, 5), (32, 8, 128, 128, False, 16)])
+def test_rope_and_cache_append(ops, dtype, Hq, Hkv, hd, rot, inter, ps):
+    g = torch.Generator(device=DEV).manual_seed(5)
+    lens, before = [3, 1, 9], [0, 6, 11]                         # three requests: new tokens, tokens already cached
+    n = sum(lens)
+    qkv = torch.randn(n, (Hq + 2 * Hkv) * hd, device=DEV, generator=g).to(dtype)
+    inv_freq = (10000.0 ** (-torch.arange(0, rot // 2, device=DEV).float() * 2 / rot))
+    pos = torch.cat([torch.arange(b, b + l) for l, b in zip(lens, before)]).to(DEV, torch.int32)
+    ent = torch.cat([torch.full((l,), i) for i, l in enumerate(lens)]).to(DEV, torch.int32)
+    pages_per = [-(-(b + l) // ps) for l, b in zip(lens, before)]
+    n_pages = sum(pages_per) + 3
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(6))[:sum(pages_per)]
+    indptr = torch.tensor([0] + list(np.cumsum(pages_per)), dtype=torch.int32, device=DEV)
+    indices = perm.to(DEV, torch.int32)
+    cache = torch.full((n_pages, 2, Hkv, ps, hd), 7.0, device=DEV, dtype=dtype)
+    ref_q = _rope_reference(qkv[:, :Hq * hd].float().view(n, Hq, hd), pos, inv_freq, rot, inter).to(dtype)
+    ref_k = _rope_reference(qkv[:, Hq * hd:(Hq + Hkv) * hd].float().view(n, Hkv, hd), pos, inv_freq, rot, inter).to(dtype)
+    v = qkv[:, (Hq + Hkv) * hd:].view(n, Hkv, hd).clone()
+    work = qkv.clone()
+    ops.rope_kv_append(work, Hq, Hkv, hd, inv_freq, rot, inter, pos, ent, indptr, indices, cache, ps)
+    torch.testing.assert_close(work[:, :Hq * hd].float().view(n, Hq, hd), ref_q.float(), **tol(dtype))
+    want = torch.full_like(cache, 7.0)
+    for t in range(n):
+        e, p = int(ent[t]), int(pos[t])
+        page = int(indices[int(indptr[e]) + p // ps])
+        want[page, 0, :, p % ps, :] = ref_k[t]
+        want[page, 1, :, p % ps, :] = v[t]
+    torch.testing.assert_close(cache.float(), want.float(), **tol(dtype))
+    assert torch.equal(cache[:, 1], want[:, 1]), "values are copied bit for bit"
+    untouched = torch.ones(n_pages, dtype=torch.bool)
+    untouched[perm] = False
+    assert bool((cache[untouched.to(DEV)] == 7.0).all()), "pages of no request were written"
+    # read-only run (a layer that shares another layer's cache): q rotated, cache untouched
+    cache2 = torch.full_like(cache, 7.0)
+    work2 = qkv.clone()
+    ops.rope_kv_append(work2, Hq, Hkv, hd, inv_freq, rot, inter, pos, ent, indptr, indices, cache2, ps, write_kv=False)
+    assert torch.equal(work2[:, :Hq * hd], work[:, :Hq * hd]) and bool((cache2 == 7.0).all())
+    # the stand-alone rotation agrees with the fused one
+    alone = qkv.clone()
+    ops.rope_inplace(alone[:, :Hq * hd].view(n, Hq, hd), pos, inv_freq, rot, inter)
+    assert torch.equal(alone[:, :Hq * hd], work[:, :Hq * hd])
+
+
+def _attention_case(ops, dtype, Hq, Hkv, hd, ps, q_lens, kv_lens, window=0, spike=None, seed=0, force_generic=False,
+                    splits=None):
+    """Random q/k/v, pages in scrambled order; returns (got, want)."""
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    n_entries, G = len(q_lens), Hq // Hkv
+    n = sum(q_lens)
+    q = torch.randn(n, Hq * hd, device=DEV, generator=g)
+    ks = [torch.randn(L, Hkv, hd, device=DEV, generator=g) for L in kv_lens]
+    vs = [torch.randn(L, Hkv, hd, device=DEV, generator=g) for L in kv_lens]
+    if spike is not None:                   # one far key that must dominate one query's softmax
+        e, key, head = spike
+        t = sum(q_lens[:e]) + q_lens[e] - 1
+        q[t].view(Hq, hd)[head] = 0
+        q[t].view(Hq, hd)[head, 0] = 40.0
+        for kk in ks[e]:
+            kk[:, 0] = kk[:, 0].clamp(-1, 1)
+        ks[e][key, head // G, 0] = 30.0
+    q, ks, vs = q.to(dtype), [k.to(dtype) for k in ks], [v.to(dtype) for v in vs]
+    pages_per = [-(-L // ps) for L in kv_lens]
+    n_pages = sum(pages_per) + 2
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(seed + 1))[:sum(pages_per)]
+    cache = torch.randn(n_pages, 2, Hkv, ps, hd, device=DEV, generator=g).to(dtype)      # garbage where nothing lives
+    indptr = [0] + list(np.cumsum(pages_per))
+    for e, L in enumerate(kv_lens):
+        for p in range(L):
+            page = int(perm[indptr[e] + p // ps])
+            cache[page, 0, :, p % ps] = ks[e][p]
+            cache[page, 1, :, p % ps] = vs[e][p]
+    qo = [0] + list(np.cumsum(q_lens))
+    pos = torch.cat([torch.arange(L - ql, L) for ql, L in zip(q_lens, kv_lens)]).to(DEV, torch.int32)
+    ent = torch.cat([torch.full((ql,), i) for i, ql in enumerate(q_lens)]).to(DEV, torch.int32)
+    ctx = SimpleNamespace(qo_indptr=torch.tensor(qo, dtype=torch.int32, device=DEV), positions=pos, tok_entry=ent,
+                          n_entries=n_entries, n_tokens=n, max_q_len=max(q_lens), max_kv_len=max(kv_lens),
+                          extras={"min_q_len": min(q_lens), "attn_splits": splits})
+    tables = SimpleNamespace(kv_indptr=torch.tensor(indptr, dtype=torch.int32, device=DEV),
+                             kv_indices=perm.to(DEV, torch.int32), page_size=ps)
+    out = torch.full((n, Hq * hd), float("nan"), device=DEV, dtype=dtype)
+    scale = 1.0 / math.sqrt(hd)
+    ops.FORCE_GENERIC_ATTENTION = force_generic
+    try:
+        ops.paged_attention(q, out, cache, ctx, tables, Hq, Hkv, hd, scale, window)
+    finally:
+        ops.FORCE_GENERIC_ATTENTION = False
+    want = torch.empty(n, Hq, hd, device=DEV)
+    for e, (ql, L) in enumerate(zip(q_lens, kv_lens)):
+        qe = q[qo[e]:qo[e + 1]].float().view(ql, Hq, hd)
+        k, v = ks[e].float(), vs[e].float()
+        for i in range(ql):
+            p = L - ql + i
+            lo = max(0, p - window + 1) if window else 0
+            for h in range(Hq):
+                s = (k[lo:p + 1, h // G] @ qe[i, h]) * scale
+                want[qo[e] + i, h] = torch.softmax(s, 0) @ v[lo:p + 1, h // G]
+    return out.float().view(n, Hq, hd), want
+
+
+ATT_SHAPES = [
+    # Hq, Hkv, hd, page, q_lens, kv_lens
+    (4, 2, 16, 4, [5, 1, 2], [5, 9, 30]),
+    (3, 1, 32, 1, [1, 1, 7], [40, 1, 7]),
+    (6, 2, 48, 5, [3, 11], [17, 11]),
+    (8, 2, 64, 16, [1, 1, 1, 1], [300, 17, 64, 129]),
+    (8, 2, 64, 8, [70, 2, 1], [200, 5, 333]),
+    (32, 8, 128, 16, [1, 1, 1], [700, 2049, 33]),
+    (12, 4, 128, 16, [130, 1, 3, 64], [130, 555, 40, 600]),
+    (5, 5, 128, 32, [9, 200], [77, 200]),
+    (4, 1, 256, 16, [1, 40], [150, 90]),
+    (40, 2, 64, 16, [1, 2], [100, 65]),                # 20 query heads per kv head: more than one 16-row tile
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", ATT_SHAPES, ids=lambda s: f"H{s[0]}k{s[1]}d{s[2]}p{s[3]}")
+def test_paged_attention(ops, dtype, shape):
+    Hq, Hkv, hd, ps, q_lens, kv_lens = shape
+    got, want = _attention_case(ops, dtype, Hq, Hkv, hd, ps, q_lens, kv_lens, seed=len(q_lens))
+    assert not torch.isnan(got).any()
+    torch.testing.assert_close(got, want, **(dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else
+                                             dict(rtol=3e-2, atol=2e-2)))
+
+
+@pytest.mark.parametrize("splits", [1, 3, 8])
+def test_split_keys_agree_with_one_pass(ops, splits):
+    a, want = _attention_case(ops, torch.bfloat16, 8, 2, 128, 16, [1, 1, 2], [1000, 70, 513], splits=splits, seed=7)
+    torch.testing.assert_close(a, want, rtol=3e-2, atol=2e-2)
+    b, _ = _attention_case(ops, torch.bfloat16, 8, 2, 128, 16, [1, 1, 2], [1000, 70, 513], force_generic=True, seed=7)
+    torch.testing.assert_close(a, b, rtol=3e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hd,q_lens,kv_lens,window", [(64, [1, 20, 3], [100, 60, 35], 17), (32, [4, 1], [50, 9], 8),
+                                                      (128, [1, 90], [400, 300], 64)])
+def test_window(ops, dtype, hd, q_lens, kv_lens, window):
+    got, want = _attention_case(ops, dtype, 4, 2, hd, 8, q_lens, kv_lens, window=window, seed=3)
+    torch.testing.assert_close(got, want, **(dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else
+                                             dict(rtol=3e-2, atol=2e-2)))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("key", [0, 15, 16, 511, 512, 1023, 1500])
+def test_one_far_key_among_hundreds_is_found(ops, dtype, key):
+    """One key, scaled so that its score stands out, decides the output: a kernel
+    that skips or misplaces a page, a tile edge or a split shows here."""
+    got, want = _attention_case(ops, dtype, 8, 2, 128, 16, [1, 1], [64, 1501], spike=(1, key, 5), seed=11)
+    torch.testing.assert_close(got, want, **(dict(rtol=1e-4, atol=1e-4) if dtype == torch.float32 else
+                                             dict(rtol=3e-2, atol=3e-2)))
+
+
+def test_argmax_and_ties(ops):
+    g = torch.Generator(device=DEV).manual_seed(8)
+    logits = torch.randn(5, 128256, device=DEV, generator=g)
+    assert torch.equal(ops.argmax(logits).long(), torch.argmax(logits, -1))
+    tie = torch.zeros(2, 1000, device=DEV)
+    tie[0, [400, 17, 999]] = 3.0
+    tie[1, 999] = 1.0
+    assert ops.argmax(tie).tolist() == [17, 999]
+
+
+def _draw(ops, logits_row, n, T, top_k, top_p, seed=123, stream=5):
+    logits = logits_row.to(DEV).float().repeat(n, 1).contiguous()
+    f = lambda v, dt: torch.full((n,), v, device=DEV, dtype=dt)
+    return ops.sample(logits, f(T, torch.float32), f(top_k, torch.int32), f(top_p, torch.float32),
+                      f(stream, torch.int64), torch.arange(n, device=DEV, dtype=torch.int64), seed).cpu()
+
+
+def test_sampling_follows_the_softmax(ops):
+    import plain_llama as P
+    g = torch.Generator().manual_seed(9)
+    row = torch.randn(50, generator=g) * 2
+    n = 40000
+    for T, k, p in [(0.8, -1, 0.0), (1.3, 7, 0.0), (0.8, -1, 0.6), (1.0, 12, 0.9)]:
+        draws = _draw(ops, row, n, T, k, p)
+        want = P.top_k_top_p_filter(P.softmax_temperature(row, T), k, p).numpy()
+        counts = np.bincount(draws.numpy(), minlength=50)
+        assert counts[want == 0].sum() == 0, "a token outside the top-k / top-p set was drawn"
+        live = want > 0
+        chi2 = (((counts[live] - n * want[live]) ** 2) / (n * want[live])).sum()
+        assert chi2 < 3 * live.sum() + 30, (T, k, p, chi2)
+    assert _draw(ops, row, 8, 0.0, -1, 0.0).tolist() == [int(row.argmax())] * 8
+
+
+def test_sampling_depends_on_stream_and_counter_only(ops):
+    g = torch.Generator().manual_seed(10)
+    row = torch.randn(1000, generator=g)
+    a = _draw(ops, row, 64, 1.0, -1, 0.0, seed=1, stream=3)
+    assert torch.equal(a, _draw(ops, row, 64, 1.0, -1, 0.0, seed=1, stream=3))
+    assert torch.equal(a[:5], _draw(ops, row, 5, 1.0, -1, 0.0, seed=1, stream=3)), "independent of the batch"
+    assert not torch.equal(a, _draw(ops, row, 64, 1.0, -1, 0.0, seed=1, stream=4))
+    assert not torch.equal(a, _draw(ops, row, 64, 1.0, -1, 0.0, seed=2, stream=3))
+    assert len(set(a.tolist())) > 20
