@@ -64,6 +64,8 @@ class Engine:
         self.eos_token_ids = ()
         self.tracer = None
         self.last_stats = {}
+        self.use_cuda_graphs = True
+        self._graphs = {}
 
     # -- model -------------------------------------------------------------------
     def load_model(self, model_dir=None, config=None, config_name: Optional[str] = None,
@@ -116,6 +118,7 @@ class Engine:
         self.cache = CacheManager(self.model.cache_needs(), page_size, num_pages, max_batch_size, self.dtype,
                                   self.device)
         self.model.attach_caches(self.cache.layer_caches)
+        self._graphs = {}
         self.runner = StepRunner(self.model, self.cache, self.model.spec.vocab_size, self.device)
 
     # -- the step function ---------------------------------------------------------
@@ -128,6 +131,17 @@ class Engine:
     @torch.inference_mode()
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         return self.runner.step(entries)
+
+    def decode_graph(self, batch: int):
+        """The captured decode step for ``batch`` entries, or None when graphs are
+        off or the longest request is not bounded (no ``max_seq_length``)."""
+        if not self.use_cuda_graphs or not self.max_seq_length or not self.model.graph_safe:
+            return None
+        if batch not in self._graphs:
+            from .decode_graph import DecodeGraph
+            max_pages = -(-self.max_seq_length // self.page_size)
+            self._graphs[batch] = DecodeGraph(self, batch, max_pages, self.max_seq_length)
+        return self._graphs[batch]
 
     def decode_session(self, req_ids, first_tokens):
         """A device-resident greedy decode loop over live requests (see DecodeSession)."""
@@ -173,6 +187,23 @@ class Engine:
             [d.top_p if s.top_p is None else s.top_p for s in wanting],
             [s.seq_id for s in wanting], [len(s.output_ids) for s in wanting])
 
+    def _graph_decode_step(self, graph, work: List[Workload]) -> List[int]:
+        """A pure decode step through the captured graph: host token ids in, host
+        token ids out."""
+        d = self.sampling
+        seqs = [w.seq for w in work]
+        ids = [s.seq_id for s in seqs]
+        for rid in ids:
+            self.cache.reserve(rid, 1)
+        out = graph.run(ids, [s.known_token(w.start) for s, w in zip(seqs, work)],
+                        [d.temperature if s.temperature is None else s.temperature for s in seqs],
+                        [d.top_k if s.top_k is None else s.top_k for s in seqs],
+                        [d.top_p if s.top_p is None else s.top_p for s in seqs],
+                        ids, [len(s.output_ids) for s in seqs])
+        for rid in ids:
+            self.cache.commit(rid, 1)
+        return out.cpu().tolist()
+
     @torch.inference_mode()
     def generate(self, sequences: List[Sequence]) -> List[Sequence]:
         """Continuous batching until every sequence is finished
@@ -195,13 +226,20 @@ class Engine:
                 break
             if self.tracer is not None:
                 self.tracer.on_plan(steps, sched, work)
+            wanting = [w for w in work if w.wants_token]
+            graph = self.decode_graph(len(work)) if len(wanting) == len(work) and all(
+                w.n_tokens == 1 for w in work) else None
             with prof.step_timing_ctx():
-                entries = [StepEntry(w.seq.seq_id, w.seq.known_tokens(w.start, w.start + w.n_tokens),
-                                     (w.n_tokens - 1,) if w.wants_token else ()) for w in work]
-                logits = self.runner.step(entries)
-                wanting = [w for w in work if w.wants_token]
-                with prof.bucket("sampling"):
-                    toks = self.sample_workloads(work, logits).cpu().tolist() if wanting else []
+                if graph is not None:
+                    toks = self._graph_decode_step(graph, work)
+                    h2d = graph.last_h2d_bytes
+                else:
+                    entries = [StepEntry(w.seq.seq_id, w.seq.known_tokens(w.start, w.start + w.n_tokens),
+                                         (w.n_tokens - 1,) if w.wants_token else ()) for w in work]
+                    logits = self.runner.step(entries)
+                    with prof.bucket("sampling"):
+                        toks = self.sample_workloads(work, logits).cpu().tolist() if wanting else []
+                    h2d = self.runner.last_h2d_bytes
                 prof.set_step_tokens(len(wanting))
                 prof.set_step_seq_len([w.start + w.n_tokens for w in work])
             sched.process_results(work, {w.seq.seq_id: t for w, t in zip(wanting, toks)})
@@ -213,7 +251,7 @@ class Engine:
                 dec_steps += 1
                 dec_tokens += len(work)
                 dec_seconds += time.perf_counter() - t_step
-                dec_h2d += self.runner.last_h2d_bytes
+                dec_h2d += h2d
                 dec_d2h += 4 * len(work)
         self.last_stats = dict(steps=steps, tokens_fed=tokens_in, preemptions=sched.num_preemptions,
                                generated=sum(len(s.output_ids) for s in sched.completed),

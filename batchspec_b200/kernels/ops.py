@@ -86,6 +86,12 @@ def launch_count() -> int:
     return _launches
 
 
+def count_launches(n: int) -> None:
+    """Account for kernels of this package launched by a CUDA-graph replay."""
+    global _launches
+    _launches += int(n)
+
+
 def _require_cuda(*tensors):
     for t in tensors:
         if t is not None and not t.is_cuda:

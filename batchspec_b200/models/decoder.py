@@ -60,6 +60,13 @@ class DecoderModel:
         self.head: Optional[torch.Tensor] = None
         self.caches: List[Optional[LayerCache]] = [None] * len(spec.order)
 
+    @property
+    def graph_safe(self) -> bool:
+        parts = [self.final_norm]
+        for b in self.blocks:
+            parts += [b.norm1, b.mixer, b.norm2, b.ffn, getattr(b.mixer, "position", None)]
+        return all(getattr(p, "graph_safe", False) for p in parts if p is not None)
+
     # -- tensors ---------------------------------------------------------------
     def _slots(self, i):
         b = self.blocks[i]

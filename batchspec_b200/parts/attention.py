@@ -24,6 +24,7 @@ from .base import (MIXERS, POSITION_ENCODINGS, CacheSpec, Mixer, ParamSpec, Part
 
 @register_part(MIXERS, "attention")
 class Attention(Mixer):
+    graph_safe = True
     def __init__(self, runtime: Runtime, dim: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  position: PartSpec, window: Optional[int] = None, scale: Optional[float] = None):
         if n_heads % n_kv_heads:

@@ -74,7 +74,12 @@ class Runtime:
 
 class Part:
     """Common protocol.  ``param_specs`` -> local name -> ParamSpec;
-    ``bind`` receives the loaded tensors (on the device) under those names."""
+    ``bind`` receives the loaded tensors (on the device) under those names.
+    ``graph_safe``: True if ``forward`` only enqueues device work whose launch
+    sizes depend on the number of tokens and entries alone and reads everything
+    else from the step context's device tensors; such parts may be captured in a
+    CUDA graph.  A part that reads host fields of the context must leave it False."""
+    graph_safe = False
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         return {}

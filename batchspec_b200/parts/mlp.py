@@ -14,6 +14,7 @@ from .base import FEED_FORWARDS, FeedForward, ParamSpec, Runtime, register_part
 
 @register_part(FEED_FORWARDS, "swiglu")
 class SwiGLU(FeedForward):
+    graph_safe = True
     def __init__(self, runtime: Runtime, dim: int, intermediate: int):
         self.runtime, self.dim, self.intermediate = runtime, int(dim), int(intermediate)
         self.w13 = self.w2 = None

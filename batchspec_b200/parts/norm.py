@@ -14,6 +14,7 @@ from .base import NORMS, Norm, ParamSpec, Runtime, register_part
 
 @register_part(NORMS, "rmsnorm")
 class RMSNorm(Norm):
+    graph_safe = True
     def __init__(self, runtime: Runtime, dim: int, eps: float):
         self.runtime, self.dim, self.eps = runtime, int(dim), float(eps)
         self.weight: Optional[torch.Tensor] = None

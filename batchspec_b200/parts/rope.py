@@ -45,6 +45,7 @@ def rope_inv_freq(rotary_dim: int, theta: float, scaling: Optional[dict]) -> tor
 
 @register_part(POSITION_ENCODINGS, "rope")
 class RotaryEmbedding(PositionEncoding):
+    graph_safe = True
     def __init__(self, runtime: Runtime, head_dim: int, theta: float, scaling: Optional[dict] = None,
                  rotary_dim: Optional[int] = None, interleaved: bool = False):
         self.runtime = runtime
@@ -65,6 +66,7 @@ class RotaryEmbedding(PositionEncoding):
 
 @register_part(POSITION_ENCODINGS, "none")
 class NoPositionEncoding(PositionEncoding):
+    graph_safe = True
     def __init__(self, runtime: Runtime):
         self.runtime = runtime
 
