@@ -137,6 +137,9 @@ class Engine:
         off or the longest request is not bounded (no ``max_seq_length``)."""
         if not self.use_cuda_graphs or not self.max_seq_length or not self.model.graph_safe:
             return None
+        prof = get_active_profiler()
+        if prof.active and getattr(prof, "model_profiling", False):
+            return None                       # per-kernel buckets need the kernels launched one by one
         if batch not in self._graphs:
             from .decode_graph import DecodeGraph
             max_pages = -(-self.max_seq_length // self.page_size)

@@ -124,7 +124,7 @@ class Profiler:
 
     @contextlib.contextmanager
     def bucket(self, name):
-        if not (self._in_step and self.model_profiling):
+        if not (self._in_step and self.model_profiling) or torch.cuda.is_current_stream_capturing():
             yield
             return
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
