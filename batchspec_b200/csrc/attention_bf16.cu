@@ -9,7 +9,8 @@
 //    CTA owns one 16-row tile of one (request, kv head) and ONE SPLIT of its keys;
 //    its 4 warps take different 16-key blocks of every 64-key tile and are
 //    combined through shared memory at the end.  With more than one split the
-//    un-normalised partial results go to scratch and attn_merge_kernel joins them.
+//    un-normalised partial results go to scratch; the CTA that finishes a tile last
+//    (a counter per tile, reset by that CTA) joins the splits in their fixed order.
 //  * attn_prefill_kernel: requests with many new tokens.  A CTA owns 64 rows
 //    (4 warps x 16) of one (request, kv head) and walks all visible keys.
 //
@@ -65,8 +66,8 @@ struct TileGeom {
 // zero-filled and their table entries (which may be released pages) are not read.
 template <int HD>
 __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* Ks, __nv_bfloat16* Vs, const __nv_bfloat16* cache,
-                                             const int* table, int k0, int k_lo, int k_end, int page_size, int Hkv,
-                                             int g) {
+                                             const int* table, int table_page0, int k0, int k_lo, int k_end,
+                                             int page_size, int Hkv, int g) {
   constexpr int CH = HD / 8;                     // 16-byte chunks per row
   const size_t page_elems = (size_t)Hkv * page_size * HD;
   for (int idx = threadIdx.x; idx < KT * CH; idx += NTHREADS) {
@@ -75,8 +76,9 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* Ks, __nv_bfloat16* V
     const bool valid = key < k_end && key >= k_lo;
     const __nv_bfloat16* src = cache;
     if (valid) {
-      const int page = table[key / page_size];
-      src = cache + (size_t)page * 2 * page_elems + ((size_t)g * page_size + (key % page_size)) * HD + ch * 8;
+      const int pi = key / page_size;
+      const int page = table[pi - table_page0];
+      src = cache + (size_t)page * 2 * page_elems + ((size_t)g * page_size + (key - pi * page_size)) * HD + ch * 8;
     }
     const int off = row * HD + ((ch ^ (row & 7)) << 3);
     cp_async16(Ks + off, src, valid);
@@ -188,16 +190,21 @@ __device__ __forceinline__ bool tile_geometry(TileGeom& t, const int* qo_indptr,
 }
 
 // ------------------------------------------------------------------------------------ decode (split keys)
+constexpr int TBL_MAX = 1024;   // block-table entries of a split kept in shared memory
+
 template <int HD>
 __global__ void __launch_bounds__(NTHREADS)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride, __nv_bfloat16* __restrict__ out,
-                   float* __restrict__ o_part, float* __restrict__ ml_part, const __nv_bfloat16* __restrict__ cache,
-                   const int* __restrict__ qo_indptr, const int* __restrict__ positions,
-                   const int* __restrict__ kv_indptr, const int* __restrict__ kv_indices, int Hq, int Hkv,
-                   int page_size, float scale_log2, int window, int n_splits, int row_tiles, int max_q_short) {
+                   float* __restrict__ o_part, float* __restrict__ ml_part, int* __restrict__ tile_counters,
+                   const __nv_bfloat16* __restrict__ cache, const int* __restrict__ qo_indptr,
+                   const int* __restrict__ positions, const int* __restrict__ kv_indptr,
+                   const int* __restrict__ kv_indices, int Hq, int Hkv, int page_size, float scale_log2, int window,
+                   int n_splits, int row_tiles, int max_q_short) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);           // [16][HD]
   __nv_bfloat16* KV = Qs + 16 * HD;                                        // 2 stages x (K [KT][HD], V [KT][HD])
+  int* tbl = reinterpret_cast<int*>(KV + 4 * KT * HD);                     // [TBL_MAX]
+  __shared__ int s_last;
   const int split = blockIdx.x, g = blockIdx.y;
   const int e = blockIdx.z / row_tiles, rt = blockIdx.z - e * row_tiles;
   TileGeom t;
@@ -215,6 +222,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride, 
   const int k_begin = lo_al + split * chunk;
   const int k_end = min(hi_key + 1, k_begin + chunk);
   const int* table = kv_indices + kv_indptr[e];
+  int table_page0 = 0;
 
   // per-thread rows: lane/4 and lane/4 + 8 of the tile
   int lim[2], lo[2];
@@ -233,11 +241,19 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride, 
     for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
 
   if (k_begin < k_end) {
+    // the split's block-table entries, once, into shared memory (if they fit)
+    const int first_key = max(k_begin, lo_key);
+    const int pg0 = first_key / page_size, pg1 = (k_end - 1) / page_size;
+    if (pg1 - pg0 + 1 <= TBL_MAX) {
+      for (int i = threadIdx.x; i <= pg1 - pg0; i += NTHREADS) tbl[i] = table[pg0 + i];
+      table = tbl;
+      table_page0 = pg0;
+    }
     load_q_tile<HD>(Qs, q, q_row_stride, t, row0, 16);
-    const int n_tiles = (k_end - k_begin + KT - 1) / KT;
-    load_kv_tile<HD>(KV, KV + KT * HD, cache, table, k_begin, lo_key, k_end, page_size, Hkv, g);
-    cp_async_commit();
     __syncthreads();
+    const int n_tiles = (k_end - k_begin + KT - 1) / KT;
+    load_kv_tile<HD>(KV, KV + KT * HD, cache, table, table_page0, k_begin, lo_key, k_end, page_size, Hkv, g);
+    cp_async_commit();
     uint32_t qf[HD / 16][4];
     {
       const int mat = lane >> 3, r8 = lane & 7;
@@ -250,7 +266,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride, 
       __nv_bfloat16* Vs = Ks + KT * HD;
       if (it + 1 < n_tiles) {
         __nv_bfloat16* Kn = KV + ((it + 1) & 1) * 2 * KT * HD;
-        load_kv_tile<HD>(Kn, Kn + KT * HD, cache, table, k_begin + (it + 1) * KT, lo_key, k_end, page_size, Hkv, g);
+        load_kv_tile<HD>(Kn, Kn + KT * HD, cache, table, table_page0, k_begin + (it + 1) * KT, lo_key, k_end,
+                         page_size, Hkv, g);
         cp_async_commit();
         cp_async_wait<1>();
       } else {
@@ -314,40 +331,45 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride, 
       }
     }
   }
-}
-
-// Join the splits of every (token, head): one warp each.
-template <int HD>
-__global__ void attn_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
-                                  __nv_bfloat16* __restrict__ out, const int* __restrict__ qo_indptr,
-                                  const int* __restrict__ tok_entry, int n_tokens, int Hq, int n_splits,
-                                  int max_q_short) {
-  const int th = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (th >= n_tokens * Hq) return;
-  const int tkn = th / Hq;
-  const int e = tok_entry[tkn];
-  if (qo_indptr[e + 1] - qo_indptr[e] > max_q_short) return;      // that request went through the prefill kernel
-  const int lane = threadIdx.x & 31;
-  float mt = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) mt = fmaxf(mt, ml_part[((size_t)th * n_splits + s) * 2]);
-  float lt = 0.f;
-  float acc[HD / 32];
-#pragma unroll
-  for (int i = 0; i < HD / 32; ++i) acc[i] = 0.f;
-  if (mt != -INFINITY) {
-    for (int s = 0; s < n_splits; ++s) {
-      const float ms = ml_part[((size_t)th * n_splits + s) * 2];
-      if (ms == -INFINITY) continue;
-      const float f = exp2f(ms - mt);
-      lt += ml_part[((size_t)th * n_splits + s) * 2 + 1] * f;
-      const float* op = o_part + ((size_t)th * n_splits + s) * HD;
-#pragma unroll
-      for (int i = 0; i < HD / 32; ++i) acc[i] += op[lane + 32 * i] * f;
+  if (n_splits == 1) return;
+  // The CTA that gets here last for this tile joins the splits (in split order, so the result does not depend
+  // on which CTA it is) and resets the counter for the next launch.
+  __threadfence();
+  __syncthreads();
+  const int tile_id = (e * Hkv + g) * row_tiles + rt;
+  if (threadIdx.x == 0) s_last = (atomicAdd(&tile_counters[tile_id], 1) == n_splits - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  float* Wt = Os;                                           // [n_splits <= 64][16] weights exp2(m_s - m)
+  float* Inv = Os + 64 * 16;                                // [16]
+  for (int row = threadIdx.x; row < nrows; row += NTHREADS) {
+    const int r = row0 + row, qi = r / t.G, h = g * t.G + (r - qi * t.G);
+    const size_t th = (size_t)(t.q_begin + qi) * Hq + h;
+    float mt = -INFINITY;
+    for (int sp = 0; sp < n_splits; ++sp) mt = fmaxf(mt, __ldcg(ml_part + (th * n_splits + sp) * 2));
+    float lt = 0.f;
+    for (int sp = 0; sp < n_splits; ++sp) {
+      const float ms = __ldcg(ml_part + (th * n_splits + sp) * 2);
+      const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - mt);
+      Wt[sp * 16 + row] = f;
+      lt += __ldcg(ml_part + (th * n_splits + sp) * 2 + 1) * f;
     }
+    Inv[row] = lt > 0.f ? 1.f / lt : 0.f;
   }
-  const float inv = lt > 0.f ? 1.f / lt : 0.f;
-#pragma unroll
-  for (int i = 0; i < HD / 32; ++i) out[(size_t)th * HD + lane + 32 * i] = __float2bfloat16_rn(acc[i] * inv);
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < nrows * HD; idx += NTHREADS) {
+    const int row = idx / HD, col = idx - row * HD;
+    const int r = row0 + row, qi = r / t.G, h = g * t.G + (r - qi * t.G);
+    const size_t th = (size_t)(t.q_begin + qi) * Hq + h;
+    float acc = 0.f;
+    for (int sp = 0; sp < n_splits; ++sp) {
+      const float f = Wt[sp * 16 + row];
+      if (f != 0.f) acc += __ldcg(o_part + (th * n_splits + sp) * HD + col) * f;
+    }
+    out[th * HD + col] = __float2bfloat16_rn(acc * Inv[row]);
+  }
+  if (threadIdx.x == 0) tile_counters[tile_id] = 0;
 }
 
 // ------------------------------------------------------------------------------------ prefill (64 rows per CTA)
@@ -396,7 +418,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
 
   load_q_tile<HD>(Qs, q, q_row_stride, t, row0, 64);
   const int n_tiles = (k_end - k_begin + KT - 1) / KT;
-  load_kv_tile<HD>(KV, KV + KT * HD, cache, table, k_begin, lo_key, k_end, page_size, Hkv, g);
+  load_kv_tile<HD>(KV, KV + KT * HD, cache, table, 0, k_begin, lo_key, k_end, page_size, Hkv, g);
   cp_async_commit();
   __syncthreads();
   uint32_t qf[HD / 16][4];
@@ -411,7 +433,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
     __nv_bfloat16* Vs = Ks + KT * HD;
     if (it + 1 < n_tiles) {
       __nv_bfloat16* Kn = KV + ((it + 1) & 1) * 2 * KT * HD;
-      load_kv_tile<HD>(Kn, Kn + KT * HD, cache, table, k_begin + (it + 1) * KT, lo_key, k_end, page_size, Hkv, g);
+      load_kv_tile<HD>(Kn, Kn + KT * HD, cache, table, 0, k_begin + (it + 1) * KT, lo_key, k_end, page_size, Hkv, g);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -448,15 +470,14 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
 }
 
 template <int HD> size_t decode_smem() {
-  const size_t stages = (size_t)(16 + 4 * KT) * HD * 2;
-  const size_t combine = (size_t)16 * HD * 2 + (size_t)(4 * 16 * HD + 8 * 16) * 4;
-  return stages > combine ? stages : combine;
+  // Q tile, two K/V stages (reused by the combine: 4*16*HD + 128 floats, and by the join: 64*16 + 16 floats), table
+  return (size_t)(16 + 4 * KT) * HD * 2 + (size_t)TBL_MAX * 4;
 }
 template <int HD> size_t prefill_smem() { return (size_t)(64 + 4 * KT) * HD * 2; }
 
 template <int HD>
 int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, float* o_part, float* ml_part,
-           const __nv_bfloat16* cache, const int* qo_indptr, const int* positions, const int* tok_entry,
+           int* tile_counters, const __nv_bfloat16* cache, const int* qo_indptr, const int* positions, const int* tok_entry,
            const int* kv_indptr, const int* kv_indices, int n_entries, int n_tokens, int max_q_len, int Hq, int Hkv,
            int page_size, float scale, int window, int n_splits, int max_q_short, int run_decode, int run_prefill,
            cudaStream_t stream) {
@@ -474,17 +495,10 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
     dim3 grid(n_splits, Hkv, n_entries * row_tiles);
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidConfiguration;
     attn_decode_kernel<HD><<<grid, NTHREADS, decode_smem<HD>(), stream>>>(
-        q, q_row_stride, out, o_part, ml_part, cache, qo_indptr, positions, kv_indptr, kv_indices, Hq, Hkv, page_size,
-        scale_log2, window, n_splits, row_tiles, max_q_short);
-    int err = (int)cudaGetLastError();
+        q, q_row_stride, out, o_part, ml_part, tile_counters, cache, qo_indptr, positions, kv_indptr, kv_indices, Hq,
+        Hkv, page_size, scale_log2, window, n_splits, row_tiles, max_q_short);
+    const int err = (int)cudaGetLastError();
     if (err) return err;
-    if (n_splits > 1) {
-      const int warps = 4;
-      attn_merge_kernel<HD><<<(n_tokens * Hq + warps - 1) / warps, warps * 32, 0, stream>>>(
-          o_part, ml_part, out, qo_indptr, tok_entry, n_tokens, Hq, n_splits, max_q_short);
-      err = (int)cudaGetLastError();
-      if (err) return err;
-    }
   }
   if (run_prefill) {
     dim3 grid((max_q_len * G + 63) / 64, Hkv, n_entries);
@@ -499,18 +513,20 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
 }  // namespace
 
 // Requests with q_len <= max_q_short go through the split-key kernel (if run_decode), the others through the
-// 64-row kernel (if run_prefill).  n_splits > 1 needs scratch: o_part float32 [n_tokens * Hq * n_splits * hd],
-// ml_part float32 [n_tokens * Hq * n_splits * 2].  Returns cudaErrorInvalidValue for an unsupported head_dim.
+// 64-row kernel (if run_prefill).  n_splits (<= 64) > 1 needs scratch: o_part float32 [n_tokens * Hq * n_splits * hd],
+// ml_part float32 [n_tokens * Hq * n_splits * 2] and tile_counters int32 [n_entries * Hkv * row tiles], which must
+// be zero before the first launch and is left zero by every launch.  Returns cudaErrorInvalidValue for an
+// unsupported head_dim.
 BSPEC_API int bspec_attention_bf16(const void* q, long long q_row_stride, void* out, float* o_part, float* ml_part,
-                                   const void* cache, const int* qo_indptr, const int* positions,
+                                   int* tile_counters, const void* cache, const int* qo_indptr, const int* positions,
                                    const int* tok_entry, const int* kv_indptr, const int* kv_indices, int n_entries,
                                    int n_tokens, int max_q_len, int Hq, int Hkv, int hd, int page_size, float scale,
                                    int window, int n_splits, int max_q_short, int run_decode, int run_prefill,
                                    cudaStream_t stream) {
   if (n_entries <= 0 || n_tokens <= 0) return 0;
-  if (Hq % Hkv != 0 || n_splits < 1) return (int)cudaErrorInvalidValue;
+  if (Hq % Hkv != 0 || n_splits < 1 || n_splits > 64) return (int)cudaErrorInvalidValue;
 #define GO(HDV)                                                                                                    \
-  return launch<HDV>((const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, o_part, ml_part,                  \
+  return launch<HDV>((const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, o_part, ml_part, tile_counters,   \
                      (const __nv_bfloat16*)cache, qo_indptr, positions, tok_entry, kv_indptr, kv_indices, n_entries, \
                      n_tokens, max_q_len, Hq, Hkv, page_size, scale, window, n_splits, max_q_short, run_decode,      \
                      run_prefill, stream)

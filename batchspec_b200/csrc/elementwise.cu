@@ -32,6 +32,69 @@ BSPEC_API int bspec_embed(const int* ids, const void* table, int table_dtype, fl
 // ---------------------------------------------------------------- add + RMSNorm
 // resid[t,:] += delta[t,:] (if delta);  out[t,:] = cast(resid * rsqrt(mean(resid^2)+eps)) * w
 // The product with w is taken after the cast to the output type, in that type.
+// One block per row.  Each thread owns elements 4*(threadIdx.x + k*blockDim.x) .. +3 for k < VPT and keeps them in
+// registers between the sum of squares and the scaling (one pass over memory); rows wider than
+// 4 * VPT * blockDim.x, or whose width is not a multiple of 4, take the two-pass kernel below.
+template <typename T> struct Vec4 { T v[4]; };
+template <typename T> __device__ __forceinline__ void load4(const T* p, float (&f)[4]);
+template <> __device__ __forceinline__ void load4<float>(const float* p, float (&f)[4]) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+template <> __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&f)[4]) {
+  const uint2 v = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&v.x), b = *reinterpret_cast<const __nv_bfloat162*>(&v.y);
+  f[0] = __low2float(a); f[1] = __high2float(a); f[2] = __low2float(b); f[3] = __high2float(b);
+}
+template <typename T> __device__ __forceinline__ void store4(T* p, const float (&f)[4]);
+template <> __device__ __forceinline__ void store4<float>(float* p, const float (&f)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, const float (&f)[4]) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+  uint2 v;
+  v.x = *reinterpret_cast<const uint32_t*>(&a);
+  v.y = *reinterpret_cast<const uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = v;
+}
+
+template <typename TD, typename TO, typename TW, int VPT>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
+                                       const TW* __restrict__ weight, TO* __restrict__ out, int d, float eps) {
+  __shared__ float scratch[32];
+  const size_t base = (size_t)blockIdx.x * d;
+  float x[VPT][4];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = 4 * (threadIdx.x + k * blockDim.x);
+    if (i < d) {
+      load4<float>(resid + base + i, x[k]);
+      if (delta != nullptr) {
+        float dl[4];
+        load4<TD>(delta + base + i, dl);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) x[k][j] += dl[j];
+        store4<float>(resid + base + i, x[k]);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) ss += x[k][j] * x[k][j];
+    }
+  }
+  const float r = rsqrtf(block_sum(ss, scratch) / (float)d + eps);
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = 4 * (threadIdx.x + k * blockDim.x);
+    if (i < d) {
+      float w[4], y[4];
+      load4<TW>(weight + i, w);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) y[j] = to_f32(from_f32<TO>(to_f32(from_f32<TO>(x[k][j] * r)) * w[j]));
+      store4<TO>(out + base + i, y);
+    }
+  }
+}
+
 template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                    const void* __restrict__ weight, int w_dtype, TO* __restrict__ out, int d,
@@ -56,9 +119,32 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
   }
 }
 
+template <typename TD, typename TO, typename TW>
+static void launch_add_rmsnorm_vec(float* resid, const void* delta, const void* weight, void* out, int n, int d,
+                                   float eps, cudaStream_t stream) {
+  const int quads = d / 4;
+  int threads = quads >= 1024 ? 1024 : ((quads + 31) / 32) * 32;
+  if (threads < 32) threads = 32;
+  const int vpt = (quads + threads - 1) / threads;
+#define LV(V) add_rmsnorm_vec_kernel<TD, TO, TW, V><<<n, threads, 0, stream>>>(resid, (const TD*)delta, (const TW*)weight, (TO*)out, d, eps)
+  if (vpt <= 1) LV(1); else if (vpt <= 2) LV(2); else LV(4);
+#undef LV
+}
+
 BSPEC_API int bspec_add_rmsnorm(float* resid, const void* delta, int delta_dtype, const void* weight, int w_dtype,
                                 void* out, int out_dtype, int n, int d, float eps, cudaStream_t stream) {
   if (n <= 0) return 0;
+  const bool same = delta_dtype == out_dtype;
+  if (same && d % 4 == 0 && d <= 4 * 4 * 1024) {
+    if (out_dtype == BSPEC_F32) {
+      if (w_dtype == BSPEC_F32) launch_add_rmsnorm_vec<float, float, float>(resid, delta, weight, out, n, d, eps, stream);
+      else launch_add_rmsnorm_vec<float, float, __nv_bfloat16>(resid, delta, weight, out, n, d, eps, stream);
+    } else {
+      if (w_dtype == BSPEC_F32) launch_add_rmsnorm_vec<__nv_bfloat16, __nv_bfloat16, float>(resid, delta, weight, out, n, d, eps, stream);
+      else launch_add_rmsnorm_vec<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(resid, delta, weight, out, n, d, eps, stream);
+    }
+    return BSPEC_LAUNCH_CHECK();
+  }
   const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
 #define L(TD, TO) add_rmsnorm_kernel<TD, TO><<<n, threads, 0, stream>>>(resid, (const TD*)delta, weight, w_dtype, (TO*)out, d, eps)
   if (delta_dtype == BSPEC_F32 && out_dtype == BSPEC_F32) L(float, float);
@@ -124,6 +210,8 @@ BSPEC_API int bspec_silu_mul(const void* u, void* m, int dtype, int n, int inter
 // Cache layer layout: [pages][2 (k, v)][Hkv][page_size][hd].
 // Pairing: half-split (j, j + rot/2) or interleaved (2j, 2j+1); dims >= rot pass through.
 // angle = float(position) * inv_freq[j], all float32.
+constexpr int ROPE_HEADS_PER_BLOCK = 4;
+
 template <typename T>
 __global__ void rope_kv_append_kernel(T* __restrict__ qkv, int Hq, int Hkv, int hd, const float* __restrict__ inv_freq,
                                       int rot, int interleaved, const int* __restrict__ positions,
@@ -132,19 +220,24 @@ __global__ void rope_kv_append_kernel(T* __restrict__ qkv, int Hq, int Hkv, int 
                                       int write_kv) {
   extern __shared__ float cs[];  // [rot/2] cos, [rot/2] sin
   const int t = blockIdx.x;
+  const int slot0 = blockIdx.y * ROPE_HEADS_PER_BLOCK;          // head slots: q heads, then k heads, then v heads
+  const int n_slots = Hq + 2 * Hkv;
+  const int slot1 = min(n_slots, slot0 + ROPE_HEADS_PER_BLOCK);
   const int pos = positions[t];
   const int half = rot / 2;
-  for (int j = threadIdx.x; j < half; j += blockDim.x) {
-    float s, c;
-    sincosf((float)pos * inv_freq[j], &s, &c);
-    cs[j] = c;
-    cs[half + j] = s;
+  if (slot0 < Hq + Hkv) {
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+      float s, c;
+      sincosf((float)pos * inv_freq[j], &s, &c);
+      cs[j] = c;
+      cs[half + j] = s;
+    }
   }
   __syncthreads();
-  T* row = qkv + (size_t)t * (Hq + 2 * Hkv) * hd;
+  T* row = qkv + (size_t)t * n_slots * hd;
   T* kdst = nullptr;
   T* vdst = nullptr;
-  if (write_kv) {
+  if (write_kv && slot1 > Hq) {
     const int e = tok_entry[t];
     const int page = kv_indices[kv_indptr[e] + pos / page_size];
     const int r = pos % page_size;
@@ -153,10 +246,17 @@ __global__ void rope_kv_append_kernel(T* __restrict__ qkv, int Hq, int Hkv, int 
     vdst = kdst + page_elems;
   }
   const int hp = hd / 2;  // work items per head: one per pair of dims
-  // q and k heads: each work item handles dims (a, b)
-  for (int w = threadIdx.x; w < (Hq + Hkv) * hp; w += blockDim.x) {
-    const int h = w / hp, j = w - h * hp;
+  for (int w = threadIdx.x; w < (slot1 - slot0) * hp; w += blockDim.x) {
+    const int h = slot0 + w / hp, j = w % hp;
     T* x = row + (size_t)h * hd;
+    if (h >= Hq + Hkv) {                       // a v head: copy two elements
+      if (write_kv) {
+        T* vd = vdst + (size_t)(h - Hq - Hkv) * page_size * hd;
+        vd[2 * j] = x[2 * j];
+        vd[2 * j + 1] = x[2 * j + 1];
+      }
+      continue;
+    }
     int a, b;
     bool rotate;
     if (j < half) {
@@ -170,8 +270,8 @@ __global__ void rope_kv_append_kernel(T* __restrict__ qkv, int Hq, int Hkv, int 
     }
     float xa = to_f32(x[a]), xb = to_f32(x[b]);
     if (rotate) {
-      const float c = cs[j], s = cs[half + j];
-      const float ra = xa * c - xb * s, rb = xa * s + xb * c;
+      const float c = cs[j], sn = cs[half + j];
+      const float ra = xa * c - xb * sn, rb = xa * sn + xb * c;
       xa = ra;
       xb = rb;
     }
@@ -184,13 +284,6 @@ __global__ void rope_kv_append_kernel(T* __restrict__ qkv, int Hq, int Hkv, int 
       kd[b] = yb;
     }
   }
-  if (write_kv) {
-    const T* v = row + (size_t)(Hq + Hkv) * hd;
-    for (int w = threadIdx.x; w < Hkv * hd; w += blockDim.x) {
-      const int h = w / hd, dcol = w - h * hd;
-      vdst[(size_t)h * page_size * hd + dcol] = v[w];
-    }
-  }
 }
 
 BSPEC_API int bspec_rope_kv_append(void* qkv, int dtype, int n, int Hq, int Hkv, int hd, const float* inv_freq, int rot,
@@ -198,14 +291,16 @@ BSPEC_API int bspec_rope_kv_append(void* qkv, int dtype, int n, int Hq, int Hkv,
                                    const int* kv_indices, void* cache, int page_size, int write_kv,
                                    cudaStream_t stream) {
   if (n <= 0) return 0;
-  const int threads = 256;
+  const int threads = 128;
   const size_t smem = (size_t)(rot > 0 ? rot : 0) * sizeof(float);
+  dim3 grid(n, (Hq + 2 * Hkv + ROPE_HEADS_PER_BLOCK - 1) / ROPE_HEADS_PER_BLOCK);
+  if (grid.y > 65535) return (int)cudaErrorInvalidConfiguration;
   if (dtype == BSPEC_F32)
-    rope_kv_append_kernel<float><<<n, threads, smem, stream>>>((float*)qkv, Hq, Hkv, hd, inv_freq, rot, interleaved,
-                                                              positions, tok_entry, kv_indptr, kv_indices,
-                                                              (float*)cache, page_size, write_kv);
+    rope_kv_append_kernel<float><<<grid, threads, smem, stream>>>((float*)qkv, Hq, Hkv, hd, inv_freq, rot, interleaved,
+                                                                 positions, tok_entry, kv_indptr, kv_indices,
+                                                                 (float*)cache, page_size, write_kv);
   else
-    rope_kv_append_kernel<__nv_bfloat16><<<n, threads, smem, stream>>>(
+    rope_kv_append_kernel<__nv_bfloat16><<<grid, threads, smem, stream>>>(
         (__nv_bfloat16*)qkv, Hq, Hkv, hd, inv_freq, rot, interleaved, positions, tok_entry, kv_indptr, kv_indices,
         (__nv_bfloat16*)cache, page_size, write_kv);
   return BSPEC_LAUNCH_CHECK();

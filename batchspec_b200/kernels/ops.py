@@ -48,12 +48,13 @@ _SIGNATURES = {
     "bspec_attention_generic": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "bspec_attention_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                              c_int, c_int, c_int, c_int, c_void_p],
     "bspec_sgemm_tn": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p],
-    "bspec_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p],
+    "bspec_pick_slices": [c_int],
+    "bspec_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "bspec_sample": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ulonglong, c_void_p,
-                     c_void_p],
+                     c_void_p, c_void_p, c_void_p, c_void_p],
 }
 
 
@@ -194,16 +195,39 @@ FORCE_GENERIC_ATTENTION = False      # tests set this to compare the tensor-core
 _SM_COUNT = 148
 
 
+_DECODE_CTAS_PER_SM = 3           # the split-key kernel's shared memory lets three CTAs share an SM
+_tile_counters = {}               # device -> zeroed int32 buffers kept alive (graphs hold their addresses)
+
+
 def attention_splits(n_entries: int, n_kv_heads: int, group: int, max_q_len: int, max_kv_len: int) -> int:
-    """How many ways the split-key kernel cuts each request's keys: enough CTAs to
-    fill the device, never chunks shorter than 128 keys.  1 when the step also
-    holds long portions (they go to the 64-row kernel and already fill it)."""
+    """How many ways the split-key kernel cuts each request's keys.  If chunks of
+    at least 128 keys give no more CTAs than fit on the device at once, use them
+    all; otherwise chunks of at least 256 keys, with the count that wastes the
+    least of the last wave.  1 when the step also holds long portions (they go to
+    the 64-row kernel, which fills the device by itself)."""
     short = max(1, 16 // group)
     if max_q_len > short:
         return 1
     row_tiles = -(-(max_q_len * group) // 16)
-    ctas = max(1, n_entries * n_kv_heads * row_tiles)
-    return max(1, min(-(-(_SM_COUNT * 4) // ctas), -(-max_kv_len // 128), 64))
+    base = max(1, n_entries * n_kv_heads * row_tiles)
+    slots = _SM_COUNT * _DECODE_CTAS_PER_SM
+    fine = min(64, max(1, -(-max_kv_len // 128)))
+    if base * fine <= slots:
+        return fine
+    best, best_eff = 1, 0.0
+    for s in range(1, min(64, max(1, -(-max_kv_len // 256))) + 1):
+        total = base * s
+        eff = total / (-(-total // slots) * slots)
+        if eff > best_eff + 1e-9 or (abs(eff - best_eff) <= 1e-9 and s > best):
+            best, best_eff = s, eff
+    return best
+
+
+def _counters(device, n: int) -> torch.Tensor:
+    bufs = _tile_counters.setdefault(device, [])
+    if not bufs or bufs[-1].numel() < n:
+        bufs.append(torch.zeros(max(n, 1 << 16), dtype=torch.int32, device=device))
+    return bufs[-1]
 
 
 def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, ctx, tables, n_heads: int,
@@ -221,20 +245,23 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, c
         short = max(1, 16 // group)
         n_splits = ctx.extras.get("attn_splits") or attention_splits(ctx.n_entries, n_kv_heads, group, ctx.max_q_len,
                                                                      ctx.max_kv_len)
-        o_part = ml_part = None
+        o_part = ml_part = counters = None
         if n_splits > 1:
             o_part = torch.empty((ctx.n_tokens * n_heads * n_splits * head_dim,), dtype=torch.float32, device=qkv.device)
             ml_part = torch.empty((ctx.n_tokens * n_heads * n_splits * 2,), dtype=torch.float32, device=qkv.device)
+            row_tiles = -(-(min(ctx.max_q_len, short) * group) // 16)
+            counters = _counters(qkv.device, ctx.n_entries * n_kv_heads * row_tiles)
         run_decode = int(ctx.extras.get("min_q_len", 1) <= short)
         run_prefill = int(ctx.max_q_len > short)
         _check(lib.bspec_attention_bf16(
-            qkv.data_ptr(), qkv.stride(0), out.data_ptr(), _ptr(o_part), _ptr(ml_part), cache.data_ptr(),
+            qkv.data_ptr(), qkv.stride(0), out.data_ptr(), _ptr(o_part), _ptr(ml_part), _ptr(counters),
+            cache.data_ptr(),
             ctx.qo_indptr.data_ptr(), ctx.positions.data_ptr(), ctx.tok_entry.data_ptr(), tables.kv_indptr.data_ptr(),
             tables.kv_indices.data_ptr(), ctx.n_entries, ctx.n_tokens, ctx.max_q_len, n_heads, n_kv_heads, head_dim,
             tables.page_size, float(scale), int(window), n_splits, short, run_decode, run_prefill, _stream()),
             "attention_bf16")
         global _launches
-        _launches += (1 if n_splits > 1 and run_decode else 0) + (1 if run_decode and run_prefill else 0)
+        _launches += 1 if run_decode and run_prefill else 0
         return
     _check(lib.bspec_attention_generic(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), cache.data_ptr(), _dtype_code(qkv.dtype),
@@ -265,12 +292,24 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
 
 # ---------------------------------------------------------------------------- sampling
 
+def _pick_scratch(logits: torch.Tensor):
+    rows, vocab = logits.shape
+    nb = load_library().bspec_pick_slices(vocab)
+    part_v = torch.empty((rows * nb,), dtype=torch.float32, device=logits.device)
+    part_i = torch.empty((rows * nb,), dtype=torch.int32, device=logits.device)
+    return part_v, part_i
+
+
 def argmax(logits: torch.Tensor) -> torch.Tensor:
     _require_cuda(logits)
     assert logits.dtype == torch.float32 and logits.is_contiguous()
     out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
-    _check(load_library().bspec_argmax(logits.data_ptr(), logits.shape[0], logits.shape[1], out.data_ptr(), _stream()),
-           "argmax")
+    if logits.shape[0] == 0:
+        return out
+    part_v, part_i = _pick_scratch(logits)
+    _check(load_library().bspec_argmax(logits.data_ptr(), logits.shape[0], logits.shape[1], part_v.data_ptr(),
+                                       part_i.data_ptr(), out.data_ptr(), _stream()), "argmax")
+    count_launches(1)
     return out
 
 
@@ -285,7 +324,13 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     assert temperature.dtype == torch.float32 and top_k.dtype == torch.int32 and top_p.dtype == torch.float32
     assert stream_id.dtype == torch.int64 and counter.dtype == torch.int64
     out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    if rows == 0:
+        return out
+    part_v, part_i = _pick_scratch(logits)
+    threshold = torch.empty((rows,), dtype=torch.int32, device=logits.device)
     _check(load_library().bspec_sample(logits.data_ptr(), rows, logits.shape[1], temperature.data_ptr(),
                                        top_k.data_ptr(), top_p.data_ptr(), stream_id.data_ptr(), counter.data_ptr(),
-                                       int(seed) & 0xFFFFFFFFFFFFFFFF, out.data_ptr(), _stream()), "sample")
+                                       int(seed) & 0xFFFFFFFFFFFFFFFF, threshold.data_ptr(), part_v.data_ptr(),
+                                       part_i.data_ptr(), out.data_ptr(), _stream()), "sample")
+    count_launches(2)
     return out
