@@ -1,0 +1,382 @@
+// bfloat16 matrix product on the 5th-generation tensor cores of sm_100a:
+//   C[M, N] = X[M, K] * W[N, K]^T      (X, W row-major with K contiguous; C bfloat16 or float32)
+//
+// One CTA computes one 128 x BN accumulator tile held in tensor memory (TMEM):
+//   warp 0   one elected thread issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of the two operand
+//            tiles of every 64-wide K block into a ring of shared-memory stages, signalled by mbarriers;
+//   warp 1   allocates TMEM; one elected thread issues tcgen05.mma (kind::f16, 128 x BN x 16) four times per
+//            stage straight from shared memory and releases the stage with tcgen05.commit;
+//   warps 2-5 read the accumulator back with tcgen05.ld (each warp its own 32 TMEM lanes) and store C.
+//
+// Two arrangements share the kernel:
+//   tokens on the accumulator's rows   (M large):  rows = 128 tokens, columns = BN outputs.
+//   weights on the accumulator's rows  (M small):  rows = 128 outputs, columns = BN >= M tokens (rows of X past M
+//            are zero-filled by TMA), so a decode step streams every weight once at full tile efficiency.  K may
+//            be cut into `splits` slices run by different CTAs; the slices are joined, in slice order, by the
+//            CTA that finishes last for the tile (a counter per tile that this CTA resets), through scratch.
+//
+// Every wait on an mbarrier is bounded: when it runs out the CTA records a code in `status`, stops issuing work,
+// gives its TMEM back and returns.
+#include "common.cuh"
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+namespace {
+
+constexpr int BK = 64;                 // K elements per stage (one 128-byte swizzle span of bf16)
+constexpr int TM = 128;                // accumulator rows (UMMA M)
+constexpr int GEMM_THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+
+__device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(s32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (and raises the CTA's abort flag) when the limit is hit or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                          int code) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (i > 4096) __nanosleep(64);
+  }
+  *abort_flag = 1;
+  atomicCAS(status, 0, code);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(s32(dst)), "l"(map), "r"(s32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum) : "memory");
+}
+// 16 consecutive accumulator columns of this thread's TMEM lane
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(const void* tile) {
+  const uint64_t addr = (uint64_t)((s32(tile) & 0x3FFFFu) >> 4);
+  return addr | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major, M = 128, N = bn.
+__device__ __forceinline__ uint32_t instr_desc(int bn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
+}
+
+struct GemmParams {
+  void* C;               // [M, N] bf16 or f32
+  float* scratch;        // [tiles][splits][BN][128] float32 (weights-on-rows with splits > 1)
+  int* counters;         // [tiles], zero before and after every launch
+  int* status;           // 0, or the first error code
+  int M, N, K;
+  int out_f32;
+  int swap;              // 1: weights on the accumulator rows
+  int bn;                // accumulator columns
+  int splits;
+  int kblocks_per_split;
+  int stages;
+};
+
+__device__ __forceinline__ void store_out(void* C, int out_f32, size_t idx, float v) {
+  if (out_f32) reinterpret_cast<float*>(C)[idx] = v;
+  else reinterpret_cast<__nv_bfloat16*>(C)[idx] = __float2bfloat16_rn(v);
+}
+
+__global__ void __launch_bounds__(GEMM_THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  const int a_bytes = TM * BK * 2, b_bytes = p.bn * BK * 2;
+  const int stage_bytes = a_bytes + ((b_bytes + 1023) & ~1023);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)p.stages * stage_bytes);
+  uint64_t* empty = full + p.stages;
+  uint64_t* acc_full = empty + p.stages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* last_flag = const_cast<int*>(abort_flag) + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_a = blockIdx.x;            // 128-row tile of the operand on the accumulator rows
+  const int tile_b = blockIdx.y;            // bn-row tile of the other operand
+  const int split = blockIdx.z;
+  const int kb_total = (p.K + BK - 1) / BK;
+  const int kb0 = split * p.kblocks_per_split;
+  const int nkb = min(p.kblocks_per_split, kb_total - kb0);      // >= 1 by construction on the host
+  uint32_t tmem_cols = 32;
+  while ((int)tmem_cols < p.bn) tmem_cols <<= 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    *last_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"(tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int armed = 0;
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % p.stages;
+        const uint32_t ph = (uint32_t)(i / p.stages) & 1u;
+        if (!mbar_wait(empty + s, ph ^ 1u, abort_flag, p.status, 1)) break;
+        unsigned char* a_dst = smem + (size_t)s * stage_bytes;
+        mbar_expect_tx(full + s, (uint32_t)(a_bytes + b_bytes));
+        tma_load_2d(a_dst, &map_a, full + s, (kb0 + i) * BK, tile_a * TM);
+        tma_load_2d(a_dst + a_bytes, &map_b, full + s, (kb0 + i) * BK, tile_b * p.bn);
+        armed = i + 1;
+      }
+      if (*abort_flag) {
+        // let copies that are still in flight land before the CTA's shared memory is given up
+        for (int i = max(0, armed - p.stages); i < armed; ++i) {
+          const int s = i % p.stages;
+          const uint32_t ph = (uint32_t)(i / p.stages) & 1u;
+          for (uint32_t t = 0; t < (1u << 16) && !mbar_try_wait(full + s, ph); ++t) __nanosleep(32);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc(p.bn);
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % p.stages;
+        const uint32_t ph = (uint32_t)(i / p.stages) & 1u;
+        ok = mbar_wait(full + s, ph, abort_flag, p.status, 2);
+        if (!ok) break;
+        tc_fence_after();
+        unsigned char* a_src = smem + (size_t)s * stage_bytes;
+        const uint64_t adesc = smem_desc(a_src), bdesc = smem_desc(a_src + a_bytes);
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k)       // 16 bf16 = 32 bytes = 2 descriptor address units per step
+          tc_mma(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        tc_commit(empty + s);                    // the stage is free once these MMAs have read it
+      }
+      if (ok) tc_commit(acc_full);               // the accumulator is complete once all MMAs are done
+    }
+  } else {
+    // epilogue warps: TMEM lanes 32*(warp%4) .. +31  <->  accumulator rows
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;                       // accumulator row of this thread
+    const bool ok = mbar_wait(acc_full, 0, abort_flag, p.status, 3);
+    tc_fence_after();
+    if (ok) {
+      const int ra = tile_a * TM + row;                     // global row of the operand on the accumulator rows
+      for (int c0 = 0; c0 < p.bn; c0 += 16) {
+        uint32_t v[16];
+        tc_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
+        tc_wait_ld();
+        if (!p.swap) {
+          // rows = tokens (ra < M), columns = outputs
+          if (ra < p.M) {
+            const int n0 = tile_b * p.bn + c0;
+            const size_t base = (size_t)ra * p.N + n0;
+            if (!p.out_f32 && n0 + 16 <= p.N && (p.N % 8) == 0) {
+              uint32_t w[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                w[j] = *reinterpret_cast<uint32_t*>(&h);
+              }
+              uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + base);
+              dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+              dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (n0 + j < p.N) store_out(p.C, p.out_f32, base + j, __uint_as_float(v[j]));
+            }
+          }
+        } else if (p.splits == 1) {
+          // rows = outputs (ra < N), columns = tokens: consecutive lanes write consecutive outputs of one token
+          if (ra < p.N) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int tok = tile_b * p.bn + c0 + j;
+              if (tok < p.M) store_out(p.C, p.out_f32, (size_t)tok * p.N + ra, __uint_as_float(v[j]));
+            }
+          }
+        } else {
+          float* dst = p.scratch + (((size_t)(tile_a * gridDim.y + tile_b) * p.splits + split) * p.bn + c0) * TM + row;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) dst[(size_t)j * TM] = __uint_as_float(v[j]);
+        }
+      }
+    }
+    if (p.swap && p.splits > 1) {
+      // join the K slices: the last CTA of the tile adds them in slice order
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");        // the four epilogue warps only
+      const int tile_id = tile_a * gridDim.y + tile_b;
+      if (threadIdx.x == 64) *last_flag = (atomicAdd(&p.counters[tile_id], 1) == p.splits - 1);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*last_flag) {
+        __threadfence();
+        const int ra = tile_a * TM + row;
+        if (ra < p.N && !*abort_flag) {
+          const float* src = p.scratch + ((size_t)tile_id * p.splits) * p.bn * TM + row;
+          for (int j = 0; j < p.bn; ++j) {
+            const int tok = tile_b * p.bn + j;
+            if (tok >= p.M) break;
+            float acc = 0.f;
+            for (int s = 0; s < p.splits; ++s) acc += __ldcg(src + ((size_t)s * p.bn + j) * TM);
+            store_out(p.C, p.out_f32, (size_t)tok * p.N + ra, acc);
+          }
+        }
+        if (threadIdx.x == 64) p.counters[tile_id] = 0;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------- host side
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  }
+  return fn;
+}
+
+// rows x K bf16 matrix, K contiguous; box = box_rows x 64 elements; 128-byte swizzle; out-of-range reads give zeros
+bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+  auto fn = encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+size_t smem_bytes(int bn, int stages) {
+  const int a_bytes = TM * BK * 2, b_bytes = bn * BK * 2;
+  const int stage_bytes = a_bytes + ((b_bytes + 1023) & ~1023);
+  return 1024 + (size_t)stages * stage_bytes + (size_t)(2 * stages + 1) * 8 + 64;
+}
+}  // namespace
+
+// Plan for a product of these sizes: writes {swap, bn, splits, stages, tiles} to plan[5] and returns the number of
+// float32 scratch elements the launch needs (0 when splits == 1), or -1 if the sizes are not supported
+// (K not a multiple of 8).  `sm_count` is the number of SMs to fill.
+BSPEC_API long long bspec_gemm_tc_plan(int M, int N, int K, int sm_count, int* plan) {
+  if (K % 8 != 0 || M <= 0 || N <= 0 || K <= 0) return -1;
+  const int kb_total = (K + BK - 1) / BK;
+  int swap, bn, splits = 1;
+  int smem_budget;
+  if (M <= 128) {
+    swap = 1;
+    bn = 16;
+    while (bn < M) bn <<= 1;
+    const int tiles = (N + TM - 1) / TM;
+    // two CTAs share an SM: cut K so that the CTAs about fill those slots, at least 8 K blocks per slice
+    splits = (2 * sm_count) / tiles;
+    if (splits < 1) splits = 1;
+    if (splits > kb_total / 8) splits = kb_total / 8 > 0 ? kb_total / 8 : 1;
+    if (splits > 16) splits = 16;
+    smem_budget = 108 * 1024;
+  } else {
+    swap = 0;
+    bn = N >= 256 ? 256 : (N > 64 ? 128 : 64);
+    smem_budget = 200 * 1024;
+  }
+  int per = (kb_total + splits - 1) / splits;
+  splits = (kb_total + per - 1) / per;                   // no empty slice
+  const int a_bytes = TM * BK * 2, b_bytes = bn * BK * 2;
+  const int stage_bytes = a_bytes + ((b_bytes + 1023) & ~1023);
+  int stages = smem_budget / stage_bytes;
+  if (stages > 8) stages = 8;
+  if (stages > per + 1) stages = per + 1;
+  if (stages < 2) stages = 2;
+  const int tiles_a = swap ? (N + TM - 1) / TM : (M + TM - 1) / TM;
+  const int tiles_b = swap ? (M + bn - 1) / bn : (N + bn - 1) / bn;
+  plan[0] = swap; plan[1] = bn; plan[2] = splits; plan[3] = stages; plan[4] = tiles_a * tiles_b;
+  return splits > 1 ? (long long)tiles_a * tiles_b * splits * bn * TM : 0;
+}
+
+// C = X W^T.  scratch / counters as bspec_gemm_tc_plan says (counters: one int per tile, zeroed once by the caller).
+BSPEC_API int bspec_gemm_tc(const void* X, const void* W, void* C, int M, int N, int K, int out_f32, float* scratch,
+                            int* counters, int* status, int sm_count, cudaStream_t stream) {
+  int plan[5];
+  if (bspec_gemm_tc_plan(M, N, K, sm_count, plan) < 0) return (int)cudaErrorInvalidValue;
+  GemmParams p;
+  p.C = C; p.scratch = scratch; p.counters = counters; p.status = status;
+  p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32;
+  p.swap = plan[0]; p.bn = plan[1]; p.splits = plan[2]; p.stages = plan[3];
+  const int kb_total = (K + BK - 1) / BK;
+  p.kblocks_per_split = (kb_total + p.splits - 1) / p.splits;
+  CUtensorMap map_a, map_b;
+  const void* a_ptr = p.swap ? W : X;
+  const void* b_ptr = p.swap ? X : W;
+  const int a_rows = p.swap ? N : M, b_rows = p.swap ? M : N;
+  if (!make_map(&map_a, a_ptr, a_rows, K, TM) || !make_map(&map_b, b_ptr, b_rows, K, p.bn))
+    return (int)cudaErrorInvalidValue;
+  const size_t smem = smem_bytes(p.bn, p.stages);
+  static size_t smem_set = 0;
+  if (smem > smem_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    smem_set = smem;
+  }
+  dim3 grid((a_rows + TM - 1) / TM, (b_rows + p.bn - 1) / p.bn, p.splits);
+  if (grid.y > 65535) return (int)cudaErrorInvalidConfiguration;
+  gemm_tc_kernel<<<grid, GEMM_THREADS, smem, stream>>>(map_a, map_b, p);
+  return BSPEC_LAUNCH_CHECK();
+}

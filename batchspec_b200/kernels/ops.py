@@ -12,6 +12,7 @@ mode can slip in.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
 from typing import Optional
@@ -50,6 +51,9 @@ _SIGNATURES = {
     "bspec_attention_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                              c_int, c_int, c_int, c_int, c_void_p],
+    "bspec_gemm_tc_plan": [c_int, c_int, c_int, c_int, c_void_p],
+    "bspec_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                      c_void_p],
     "bspec_sgemm_tn": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p],
     "bspec_pick_slices": [c_int],
     "bspec_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -72,7 +76,7 @@ def load_library():
         for name, argtypes in _SIGNATURES.items():
             fn = getattr(lib, name)
             fn.argtypes = argtypes
-            fn.restype = c_int
+            fn.restype = c_longlong if name == "bspec_gemm_tc_plan" else c_int
         _lib = lib
     return _lib
 
@@ -272,6 +276,50 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, c
 
 # ---------------------------------------------------------------------------- matrix products
 
+# Which bfloat16 products run on this package's tcgen05 kernel: "auto" (those with at most TC_GEMM_MAX_M rows,
+# i.e. decode-sized steps, where it streams the weights faster than the vendor library), "all", or "none".
+TC_GEMM = os.environ.get("BSPEC_TC_GEMM", "auto")
+TC_GEMM_MAX_M = 128
+_status = {}
+
+
+def _status_word(device) -> torch.Tensor:
+    if device not in _status:
+        _status[device] = torch.zeros((1,), dtype=torch.int32, device=device)
+    return _status[device]
+
+
+def check_status() -> None:
+    """Raise if a kernel of this package gave up on a bounded wait (synchronises)."""
+    for dev, t in _status.items():
+        code = int(t.item())
+        if code:
+            t.zero_()
+            raise KernelError(f"a tcgen05 GEMM on {dev} gave up waiting (code {code}: 1 = stage never freed, "
+                              f"2 = operands never arrived, 3 = accumulator never completed)")
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """x [M, K] @ w[N, K]^T on the tcgen05 kernel (bfloat16 operands, float32 accumulation)."""
+    lib = load_library()
+    M, K = x.shape
+    N = w.shape[0]
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
+    plan = (c_int * 5)()
+    n_scratch = lib.bspec_gemm_tc_plan(M, N, K, _SM_COUNT, plan)
+    if n_scratch < 0:
+        raise KernelError(f"gemm_tc: sizes M={M} N={N} K={K} are not supported (K must be a multiple of 8)")
+    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    scratch = counters = None
+    if n_scratch > 0:
+        scratch = torch.empty((n_scratch,), dtype=torch.float32, device=x.device)
+        counters = _counters(x.device, plan[4])
+    _check(lib.bspec_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, int(out_dtype == torch.float32),
+                             _ptr(scratch), _ptr(counters), _status_word(x.device).data_ptr(), _SM_COUNT, _stream()),
+           "gemm_tc")
+    return out
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """x [M, K] @ w[N, K]^T -> [M, N] in ``out_dtype`` (default: x's dtype)."""
     _require_cuda(x, w)
@@ -285,6 +333,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
         _check(load_library().bspec_sgemm_tn(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, x.stride(0),
                                              w.stride(0), N, _stream()), "sgemm_tn")
         return out
+    if (K % 8 == 0 and M > 0 and x.is_contiguous() and w.is_contiguous()
+            and (TC_GEMM == "all" or (TC_GEMM == "auto" and M <= TC_GEMM_MAX_M))):
+        return gemm_tc(x, w, out_dtype)
     if out_dtype == x.dtype:
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=out_dtype)
