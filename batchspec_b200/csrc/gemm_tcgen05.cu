@@ -12,8 +12,9 @@
 //   tokens on the accumulator's rows   (M large):  rows = 128 tokens, columns = BN outputs.
 //   weights on the accumulator's rows  (M small):  rows = 128 outputs, columns = BN >= M tokens (rows of X past M
 //            are zero-filled by TMA), so a decode step streams every weight once at full tile efficiency.  K may
-//            be cut into `splits` slices run by different CTAs; the slices are joined, in slice order, by the
-//            CTA that finishes last for the tile (a counter per tile that this CTA resets), through scratch.
+//            be cut into `splits` <= 8 slices run by the CTAs of one thread-block cluster; each CTA leaves its
+//            partial tile in its own shared memory and, after a cluster barrier, adds up its share of the tokens
+//            over all slices, in slice order, reading the peers through distributed shared memory.
 //
 // Every wait on an mbarrier is bounded: when it runs out the CTA records a code in `status`, stops issuing work,
 // gives its TMEM back and returns.
@@ -99,8 +100,6 @@ __device__ __forceinline__ uint32_t instr_desc(int bn) {
 
 struct GemmParams {
   void* C;               // [M, N] bf16 or f32
-  float* scratch;        // [tiles][splits][BN][128] float32 (weights-on-rows with splits > 1)
-  int* counters;         // [tiles], zero before and after every launch
   int* status;           // 0, or the first error code
   int M, N, K;
   int out_f32;
@@ -127,7 +126,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   uint64_t* acc_full = empty + p.stages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* last_flag = const_cast<int*>(abort_flag) + 1;
+  float* part = reinterpret_cast<float*>(smem);      // [bn][128] partial tile of this K slice (reuses the stages)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile_a = blockIdx.x;            // 128-row tile of the operand on the accumulator rows
@@ -146,7 +145,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     mbar_init(acc_full, 1);
     *abort_flag = 0;
-    *last_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -242,35 +240,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
           }
         } else {
-          float* dst = p.scratch + (((size_t)(tile_a * gridDim.y + tile_b) * p.splits + split) * p.bn + c0) * TM + row;
+          // every MMA has completed (acc_full), so the stages are no longer read: keep the partial tile there
 #pragma unroll
-          for (int j = 0; j < 16; ++j) dst[(size_t)j * TM] = __uint_as_float(v[j]);
+          for (int j = 0; j < 16; ++j) part[(size_t)(c0 + j) * TM + row] = __uint_as_float(v[j]);
         }
       }
     }
-    if (p.swap && p.splits > 1) {
-      // join the K slices: the last CTA of the tile adds them in slice order
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");        // the four epilogue warps only
-      const int tile_id = tile_a * gridDim.y + tile_b;
-      if (threadIdx.x == 64) *last_flag = (atomicAdd(&p.counters[tile_id], 1) == p.splits - 1);
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (*last_flag) {
-        __threadfence();
-        const int ra = tile_a * TM + row;
-        if (ra < p.N && !*abort_flag) {
-          const float* src = p.scratch + ((size_t)tile_id * p.splits) * p.bn * TM + row;
-          for (int j = 0; j < p.bn; ++j) {
-            const int tok = tile_b * p.bn + j;
-            if (tok >= p.M) break;
-            float acc = 0.f;
-            for (int s = 0; s < p.splits; ++s) acc += __ldcg(src + ((size_t)s * p.bn + j) * TM);
-            store_out(p.C, p.out_f32, (size_t)tok * p.N + ra, acc);
+  }
+  if (p.swap && p.splits > 1) {
+    // join the K slices inside the cluster: CTA r adds tokens r, r + splits, ... over all slices in slice order
+    tc_fence_before();
+    __syncthreads();
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (warp >= 2 && !*abort_flag) {
+      const int row = (warp & 3) * 32 + lane;
+      const int ra = tile_a * TM + row;
+      if (ra < p.N) {
+        for (int j = split; j < p.bn; j += p.splits) {
+          const int tok = tile_b * p.bn + j;
+          if (tok >= p.M) break;
+          const uint32_t local = s32(part + (size_t)j * TM + row);
+          float acc = 0.f;
+          for (int s = 0; s < p.splits; ++s) {
+            uint32_t remote;
+            float v;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(s));
+            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+            acc += v;
           }
+          store_out(p.C, p.out_f32, (size_t)tok * p.N + ra, acc);
         }
-        if (threadIdx.x == 64) p.counters[tile_id] = 0;
       }
     }
+    // nobody leaves while a peer may still read its shared memory
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
@@ -313,9 +316,8 @@ size_t smem_bytes(int bn, int stages) {
 }
 }  // namespace
 
-// Plan for a product of these sizes: writes {swap, bn, splits, stages, tiles} to plan[5] and returns the number of
-// float32 scratch elements the launch needs (0 when splits == 1), or -1 if the sizes are not supported
-// (K not a multiple of 8).  `sm_count` is the number of SMs to fill.
+// Plan for a product of these sizes: writes {swap, bn, splits, stages, tiles} to plan[5]; returns 0, or -1 if the
+// sizes are not supported (K not a multiple of 8).  `sm_count` is the number of SMs to fill.
 BSPEC_API long long bspec_gemm_tc_plan(int M, int N, int K, int sm_count, int* plan) {
   if (K % 8 != 0 || M <= 0 || N <= 0 || K <= 0) return -1;
   const int kb_total = (K + BK - 1) / BK;
@@ -330,7 +332,7 @@ BSPEC_API long long bspec_gemm_tc_plan(int M, int N, int K, int sm_count, int* p
     splits = (2 * sm_count) / tiles;
     if (splits < 1) splits = 1;
     if (splits > kb_total / 8) splits = kb_total / 8 > 0 ? kb_total / 8 : 1;
-    if (splits > 16) splits = 16;
+    if (splits > 8) splits = 8;                           // one portable cluster
     smem_budget = 108 * 1024;
   } else {
     swap = 0;
@@ -348,16 +350,16 @@ BSPEC_API long long bspec_gemm_tc_plan(int M, int N, int K, int sm_count, int* p
   const int tiles_a = swap ? (N + TM - 1) / TM : (M + TM - 1) / TM;
   const int tiles_b = swap ? (M + bn - 1) / bn : (N + bn - 1) / bn;
   plan[0] = swap; plan[1] = bn; plan[2] = splits; plan[3] = stages; plan[4] = tiles_a * tiles_b;
-  return splits > 1 ? (long long)tiles_a * tiles_b * splits * bn * TM : 0;
+  return 0;
 }
 
-// C = X W^T.  scratch / counters as bspec_gemm_tc_plan says (counters: one int per tile, zeroed once by the caller).
-BSPEC_API int bspec_gemm_tc(const void* X, const void* W, void* C, int M, int N, int K, int out_f32, float* scratch,
-                            int* counters, int* status, int sm_count, cudaStream_t stream) {
+// C = X W^T.  `status`: one int on the device, 0 unless a bounded wait ran out.
+BSPEC_API int bspec_gemm_tc(const void* X, const void* W, void* C, int M, int N, int K, int out_f32, int* status,
+                            int sm_count, cudaStream_t stream) {
   int plan[5];
   if (bspec_gemm_tc_plan(M, N, K, sm_count, plan) < 0) return (int)cudaErrorInvalidValue;
   GemmParams p;
-  p.C = C; p.scratch = scratch; p.counters = counters; p.status = status;
+  p.C = C; p.status = status;
   p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32;
   p.swap = plan[0]; p.bn = plan[1]; p.splits = plan[2]; p.stages = plan[3];
   const int kb_total = (K + BK - 1) / BK;
@@ -377,6 +379,19 @@ BSPEC_API int bspec_gemm_tc(const void* X, const void* W, void* C, int M, int N,
   }
   dim3 grid((a_rows + TM - 1) / TM, (b_rows + p.bn - 1) / p.bn, p.splits);
   if (grid.y > 65535) return (int)cudaErrorInvalidConfiguration;
-  gemm_tc_kernel<<<grid, GEMM_THREADS, smem, stream>>>(map_a, map_b, p);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = p.splits;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel, map_a, map_b, p);
+  if (e != cudaSuccess) return (int)e;
   return BSPEC_LAUNCH_CHECK();
 }

@@ -1,0 +1,165 @@
+"""Times single kernels of this package at the sizes of a model configuration.
+
+    python -m batchspec_b200.kernels.microbench [--config llama-3-8b] [--what gemm attention small] [--m 1 8 64 2048]
+
+CUDA events around each launch, after warm-up, with a read of a buffer four times
+the L2 between timed launches, median of the repeats.  Prints, per kernel
+and size, the time, the bytes it has to move (or the flops) and the fraction of
+the peak (``MEASURED_PEAKS.json`` at the repository root if present, else the
+stated fallback).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+from pathlib import Path
+from types import SimpleNamespace
+
+import torch
+
+from ..config import get_config
+from . import ops
+
+FALLBACK = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)
+
+
+def peaks():
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    out = dict(FALLBACK, source="fallback")
+    if p.is_file():
+        try:
+            d = json.loads(p.read_text())
+            for k in FALLBACK:
+                if isinstance(d.get(k), (int, float)) and d[k] > 0:
+                    out[k] = float(d[k])
+            out["source"] = "measured"
+        except Exception:
+            pass
+    return out
+
+
+class Timer:
+    def __init__(self, device, flush_mb=512):
+        # reading a buffer four times the L2 evicts what the last launch left without filling the L2 with dirty lines
+        self.flush = torch.zeros(flush_mb << 18, dtype=torch.float32, device=device)
+
+    def time(self, fn, warmup=3, iters=10) -> float:
+        """Median milliseconds of ``fn()`` with a cold L2."""
+        for _ in range(warmup):
+            fn()
+        ts = []
+        for _ in range(iters):
+            self.flush.sum()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            e.synchronize()
+            ts.append(s.elapsed_time(e))
+        return statistics.median(ts)
+
+
+def bench_gemms(cfg, ms, timer, pk, dev):
+    d, I, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    q, kv = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
+    shapes = [("qkv", q + 2 * kv, d), ("o", d, q), ("gate_up", 2 * I, d), ("down", d, I), ("lm_head", V, d)]
+    print(f"{'gemm':8s} {'M':>5s} {'N':>7s} {'K':>6s} | {'tcgen05 ms':>10s} {'GB/s':>7s} {'TF/s':>7s} | {'library ms':>10s} {'GB/s':>7s} {'TF/s':>7s} | frac(tc) of {pk['source']} peak")
+    for name, N, K in shapes:
+        w = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
+        for M in ms:
+            if name == "lm_head" and M > 256:
+                continue
+            x = torch.randn(M, K, device=dev).bfloat16()
+            out_dtype = torch.float32 if name == "lm_head" else torch.bfloat16
+            t_tc = timer.time(lambda: ops.gemm_tc(x, w, out_dtype))
+            t_lib = timer.time(lambda: torch.mm(x, w.t()) if out_dtype == torch.bfloat16 else torch.mm(x, w.t(), out_dtype=out_dtype))
+            ops.check_status()
+            byts = 2 * (N * K + M * K) + M * N * (4 if out_dtype == torch.float32 else 2)
+            flops = 2.0 * M * N * K
+            gb = lambda t: byts / t / 1e6
+            tf = lambda t: flops / t / 1e9
+            frac = max(gb(t_tc) / pk["hbm_gbs"], tf(t_tc) / pk["bf16_tflops"])
+            print(f"{name:8s} {M:5d} {N:7d} {K:6d} | {t_tc:10.4f} {gb(t_tc):7.0f} {tf(t_tc):7.1f} | {t_lib:10.4f} {gb(t_lib):7.0f} {tf(t_lib):7.1f} | {frac:.3f}")
+
+
+def bench_attention(cfg, timer, pk, dev, page=16):
+    Hq, Hkv, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    print(f"{'attention':10s} {'batch':>5s} {'q_len':>5s} {'kv_len':>6s} | {'ms':>8s} {'GB/s':>7s} {'TF/s':>7s} | frac of {pk['source']} peak")
+    for batch, q_len, kv_len in [(1, 1, 2304), (8, 1, 2304), (64, 1, 2304), (8, 1, 30000), (1, 2048, 2048), (4, 512, 4096)]:
+        pages_per = -(-kv_len // page)
+        n_pages = batch * pages_per
+        cache = (torch.randn(n_pages, 2, Hkv, page, hd, device=dev) * 0.5).bfloat16()
+        n = batch * q_len
+        qkv = torch.randn(n, (Hq + 2 * Hkv) * hd, device=dev).bfloat16()
+        out = torch.empty(n, Hq * hd, device=dev, dtype=torch.bfloat16)
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+        ctx = SimpleNamespace(
+            qo_indptr=i32([i * q_len for i in range(batch + 1)]),
+            positions=i32([kv_len - q_len + j for _ in range(batch) for j in range(q_len)]),
+            tok_entry=i32([b for b in range(batch) for _ in range(q_len)]), n_entries=batch, n_tokens=n,
+            max_q_len=q_len, max_kv_len=kv_len, extras={"min_q_len": q_len})
+        tables = SimpleNamespace(kv_indptr=i32([i * pages_per for i in range(batch + 1)]),
+                                 kv_indices=torch.randperm(n_pages, device=dev).to(torch.int32), page_size=page)
+        t = timer.time(lambda: ops.paged_attention(qkv, out, cache, ctx, tables, Hq, Hkv, hd, hd ** -0.5, 0))
+        kv_bytes = batch * kv_len * 2 * Hkv * hd * 2
+        pairs = batch * (q_len * (kv_len - q_len) + q_len * (q_len + 1) / 2)
+        flops = 4.0 * pairs * Hq * hd
+        frac = max(kv_bytes / t / 1e6 / pk["hbm_gbs"], flops / t / 1e9 / pk["bf16_tflops"])
+        print(f"{'paged':10s} {batch:5d} {q_len:5d} {kv_len:6d} | {t:8.4f} {kv_bytes / t / 1e6:7.0f} {flops / t / 1e9:7.1f} | {frac:.3f}")
+
+
+def bench_small(cfg, ms, timer, pk, dev):
+    d, I = cfg.hidden_size, cfg.intermediate_size
+    Hq, Hkv, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    print(f"{'kernel':16s} {'rows':>5s} | {'ms':>8s} {'GB/s':>7s}")
+    for M in ms:
+        resid = torch.randn(M, d, device=dev)
+        delta = torch.randn(M, d, device=dev).bfloat16()
+        w = torch.ones(d, device=dev, dtype=torch.bfloat16)
+        out = torch.empty(M, d, device=dev, dtype=torch.bfloat16)
+        t = timer.time(lambda: ops.add_rmsnorm(resid, delta, w, 1e-5, out))
+        print(f"{'add_rmsnorm':16s} {M:5d} | {t:8.4f} {M * d * 12 / t / 1e6:7.0f}")
+        u = torch.randn(M, 2 * I, device=dev).bfloat16()
+        m = torch.empty(M, I, device=dev, dtype=torch.bfloat16)
+        t = timer.time(lambda: ops.silu_mul(u, m))
+        print(f"{'silu_mul':16s} {M:5d} | {t:8.4f} {M * I * 6 / t / 1e6:7.0f}")
+        qkv = torch.randn(M, (Hq + 2 * Hkv) * hd, device=dev).bfloat16()
+        inv = torch.rand(hd // 2, device=dev)
+        pos = torch.arange(M, device=dev, dtype=torch.int32)
+        ent = torch.zeros(M, device=dev, dtype=torch.int32)
+        n_pages = -(-M // 16)
+        cache = torch.empty(n_pages, 2, Hkv, 16, hd, device=dev, dtype=torch.bfloat16)
+        indptr = torch.tensor([0, n_pages], device=dev, dtype=torch.int32)
+        idx = torch.arange(n_pages, device=dev, dtype=torch.int32)
+        t = timer.time(lambda: ops.rope_kv_append(qkv, Hq, Hkv, hd, inv, hd, False, pos, ent, indptr, idx, cache, 16))
+        print(f"{'rope_kv_append':16s} {M:5d} | {t:8.4f} {M * (Hq + 2 * Hkv) * hd * 2 * 2 / t / 1e6:7.0f}")
+    logits = torch.randn(64, cfg.vocab_size, device=dev)
+    for rows in (1, 8, 64):
+        t = timer.time(lambda: ops.argmax(logits[:rows]))
+        print(f"{'argmax':16s} {rows:5d} | {t:8.4f} {rows * cfg.vocab_size * 4 / t / 1e6:7.0f}")
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--config", default="llama-3-8b")
+    ap.add_argument("--what", nargs="+", default=["gemm", "attention", "small"], choices=["gemm", "attention", "small"])
+    ap.add_argument("--m", nargs="+", type=int, default=[1, 8, 64, 2048])
+    a = ap.parse_args()
+    dev = torch.device("cuda:0")
+    ops.load_library()
+    cfg = get_config(a.config)
+    pk = peaks()
+    timer = Timer(dev)
+    print(f"peaks ({pk['source']}): {pk['hbm_gbs']:.0f} GB/s, {pk['bf16_tflops']:.0f} TFLOP/s bf16")
+    with torch.inference_mode():
+        if "gemm" in a.what:
+            bench_gemms(cfg, a.m, timer, pk, dev)
+        if "attention" in a.what:
+            bench_attention(cfg, timer, pk, dev)
+        if "small" in a.what:
+            bench_small(cfg, [m for m in a.m if m <= 2048], timer, pk, dev)
+
+
+if __name__ == "__main__":
+    main()

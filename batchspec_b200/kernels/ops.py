@@ -52,8 +52,7 @@ _SIGNATURES = {
                              c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                              c_int, c_int, c_int, c_int, c_void_p],
     "bspec_gemm_tc_plan": [c_int, c_int, c_int, c_int, c_void_p],
-    "bspec_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                      c_void_p],
+    "bspec_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
     "bspec_sgemm_tn": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p],
     "bspec_pick_slices": [c_int],
     "bspec_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -305,18 +304,11 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.T
     M, K = x.shape
     N = w.shape[0]
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
-    plan = (c_int * 5)()
-    n_scratch = lib.bspec_gemm_tc_plan(M, N, K, _SM_COUNT, plan)
-    if n_scratch < 0:
+    if K % 8 != 0 or M <= 0:
         raise KernelError(f"gemm_tc: sizes M={M} N={N} K={K} are not supported (K must be a multiple of 8)")
     out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-    scratch = counters = None
-    if n_scratch > 0:
-        scratch = torch.empty((n_scratch,), dtype=torch.float32, device=x.device)
-        counters = _counters(x.device, plan[4])
     _check(lib.bspec_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, int(out_dtype == torch.float32),
-                             _ptr(scratch), _ptr(counters), _status_word(x.device).data_ptr(), _SM_COUNT, _stream()),
-           "gemm_tc")
+                             _status_word(x.device).data_ptr(), _SM_COUNT, _stream()), "gemm_tc")
     return out
 
 
