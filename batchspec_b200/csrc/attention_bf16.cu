@@ -200,6 +200,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride, 
                    const int* __restrict__ positions, const int* __restrict__ kv_indptr,
                    const int* __restrict__ kv_indices, int Hq, int Hkv, int page_size, float scale_log2, int window,
                    int n_splits, int row_tiles, int max_q_short) {
+  bspec::pdl_prologue();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);           // [16][HD]
   __nv_bfloat16* KV = Qs + 16 * HD;                                        // 2 stages x (K [KT][HD], V [KT][HD])
@@ -380,6 +381,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
                     const int* __restrict__ positions, const int* __restrict__ kv_indptr,
                     const int* __restrict__ kv_indices, int Hq, int Hkv, int page_size, float scale_log2, int window,
                     int min_q_long) {
+  bspec::pdl_prologue();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);           // [64][HD]
   __nv_bfloat16* KV = Qs + 64 * HD;                                        // 2 stages x (K, V)
@@ -494,7 +496,7 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
     const int row_tiles = (short_q * G + 15) / 16;
     dim3 grid(n_splits, Hkv, n_entries * row_tiles);
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidConfiguration;
-    attn_decode_kernel<HD><<<grid, NTHREADS, decode_smem<HD>(), stream>>>(
+    BSPEC_LAUNCH((attn_decode_kernel<HD>), grid, NTHREADS, decode_smem<HD>(), stream, 
         q, q_row_stride, out, o_part, ml_part, tile_counters, cache, qo_indptr, positions, kv_indptr, kv_indices, Hq,
         Hkv, page_size, scale_log2, window, n_splits, row_tiles, max_q_short);
     const int err = (int)cudaGetLastError();
@@ -503,7 +505,7 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
   if (run_prefill) {
     dim3 grid((max_q_len * G + 63) / 64, Hkv, n_entries);
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidConfiguration;
-    attn_prefill_kernel<HD><<<grid, NTHREADS, prefill_smem<HD>(), stream>>>(
+    BSPEC_LAUNCH((attn_prefill_kernel<HD>), grid, NTHREADS, prefill_smem<HD>(), stream, 
         q, q_row_stride, out, cache, qo_indptr, positions, kv_indptr, kv_indices, Hq, Hkv, page_size, scale_log2,
         window, max_q_short + 1);
     return (int)cudaGetLastError();

@@ -22,6 +22,7 @@ attn_generic_kernel(const T* __restrict__ q, long long q_row_stride, T* __restri
                     const int* __restrict__ positions, const int* __restrict__ kv_indptr,
                     const int* __restrict__ kv_indices, int Hq, int Hkv, int hd, int page_size, float scale,
                     int window) {
+  bspec::pdl_prologue();
   __shared__ float qs[WARPS][MAX_HD];
   const int e = blockIdx.y, h = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -103,11 +104,11 @@ BSPEC_API int bspec_attention_generic(const void* q, long long q_row_stride, voi
   dim3 grid((max_q_len + WARPS - 1) / WARPS, n_entries, Hq);
   if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidConfiguration;
   if (dtype == BSPEC_F32)
-    attn_generic_kernel<float><<<grid, WARPS * 32, 0, stream>>>(
+    BSPEC_LAUNCH((attn_generic_kernel<float>), grid, WARPS * 32, 0, stream, 
         (const float*)q, q_row_stride, (float*)out, (const float*)cache, qo_indptr, positions, kv_indptr, kv_indices,
         Hq, Hkv, hd, page_size, scale, window);
   else
-    attn_generic_kernel<__nv_bfloat16><<<grid, WARPS * 32, 0, stream>>>(
+    BSPEC_LAUNCH((attn_generic_kernel<__nv_bfloat16>), grid, WARPS * 32, 0, stream, 
         (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)cache, qo_indptr, positions,
         kv_indptr, kv_indices, Hq, Hkv, hd, page_size, scale, window);
   return BSPEC_LAUNCH_CHECK();

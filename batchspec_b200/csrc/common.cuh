@@ -52,6 +52,40 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return t;
 }
 
+// Programmatic dependent launch: a kernel lets its successor start (be scheduled, run its prologue, prefetch
+// constant data) as soon as all of its own CTAs have begun, and waits for its predecessor's completion and memory
+// before it touches anything the predecessor wrote or may still read.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_prologue() {
+  pdl_launch_dependents();
+  pdl_wait();
+}
+
+inline bool& pdl_enabled() {
+  static bool on = true;
+  return on;
+}
+
+// Launch with the programmatic-stream-serialization attribute (when enabled) and, optionally, a cluster along z.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace bspec
 
+#define BSPEC_LAUNCH(kernel, grid, block, smem, stream, ...) \
+  (void)bspec::launch(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, __VA_ARGS__)
 #define BSPEC_LAUNCH_CHECK() (int)cudaGetLastError()

@@ -10,6 +10,7 @@ using namespace bspec;
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out,
                              int d, int vocab, float scale) {
+  bspec::pdl_prologue();
   const int t = blockIdx.x;
   int id = ids[t];
   const bool ok = id >= 0 && id < vocab;
@@ -23,9 +24,9 @@ BSPEC_API int bspec_embed(const int* ids, const void* table, int table_dtype, fl
   if (n <= 0) return 0;
   const int threads = d >= 1024 ? 256 : 128;
   if (table_dtype == BSPEC_F32)
-    embed_kernel<float><<<n, threads, 0, stream>>>(ids, (const float*)table, out, d, vocab, scale);
+    BSPEC_LAUNCH((embed_kernel<float>), n, threads, 0, stream, ids, (const float*)table, out, d, vocab, scale);
   else
-    embed_kernel<__nv_bfloat16><<<n, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, d, vocab, scale);
+    BSPEC_LAUNCH((embed_kernel<__nv_bfloat16>), n, threads, 0, stream, ids, (const __nv_bfloat16*)table, out, d, vocab, scale);
   return BSPEC_LAUNCH_CHECK();
 }
 
@@ -61,6 +62,7 @@ template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16*
 template <typename TD, typename TO, typename TW, int VPT>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                        const TW* __restrict__ weight, TO* __restrict__ out, int d, float eps) {
+  bspec::pdl_prologue();
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * d;
   float x[VPT][4];
@@ -99,6 +101,7 @@ template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                    const void* __restrict__ weight, int w_dtype, TO* __restrict__ out, int d,
                                    float eps) {
+  bspec::pdl_prologue();
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * d;
   float ss = 0.f;
@@ -126,7 +129,7 @@ static void launch_add_rmsnorm_vec(float* resid, const void* delta, const void* 
   int threads = quads >= 1024 ? 1024 : ((quads + 31) / 32) * 32;
   if (threads < 32) threads = 32;
   const int vpt = (quads + threads - 1) / threads;
-#define LV(V) add_rmsnorm_vec_kernel<TD, TO, TW, V><<<n, threads, 0, stream>>>(resid, (const TD*)delta, (const TW*)weight, (TO*)out, d, eps)
+#define LV(V) BSPEC_LAUNCH((add_rmsnorm_vec_kernel<TD, TO, TW, V>), n, threads, 0, stream, resid, (const TD*)delta, (const TW*)weight, (TO*)out, d, eps)
   if (vpt <= 1) LV(1); else if (vpt <= 2) LV(2); else LV(4);
 #undef LV
 }
@@ -146,7 +149,7 @@ BSPEC_API int bspec_add_rmsnorm(float* resid, const void* delta, int delta_dtype
     return BSPEC_LAUNCH_CHECK();
   }
   const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
-#define L(TD, TO) add_rmsnorm_kernel<TD, TO><<<n, threads, 0, stream>>>(resid, (const TD*)delta, weight, w_dtype, (TO*)out, d, eps)
+#define L(TD, TO) BSPEC_LAUNCH((add_rmsnorm_kernel<TD, TO>), n, threads, 0, stream, resid, (const TD*)delta, weight, w_dtype, (TO*)out, d, eps)
   if (delta_dtype == BSPEC_F32 && out_dtype == BSPEC_F32) L(float, float);
   else if (delta_dtype == BSPEC_BF16 && out_dtype == BSPEC_BF16) L(__nv_bfloat16, __nv_bfloat16);
   else if (delta_dtype == BSPEC_F32 && out_dtype == BSPEC_BF16) L(float, __nv_bfloat16);
@@ -159,6 +162,7 @@ BSPEC_API int bspec_add_rmsnorm(float* resid, const void* delta, int delta_dtype
 template <typename TD>
 __global__ void gather_rows_add_kernel(const float* __restrict__ resid, const TD* __restrict__ pending,
                                        const int* __restrict__ rows, float* __restrict__ out, int d) {
+  bspec::pdl_prologue();
   const size_t src = (size_t)rows[blockIdx.x] * d, dst = (size_t)blockIdx.x * d;
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     float v = resid[src + i];
@@ -171,9 +175,9 @@ BSPEC_API int bspec_gather_rows_add(const float* resid, const void* pending, int
                                     float* out, int n_out, int d, cudaStream_t stream) {
   if (n_out <= 0) return 0;
   if (pending_dtype == BSPEC_F32)
-    gather_rows_add_kernel<float><<<n_out, 256, 0, stream>>>(resid, (const float*)pending, rows, out, d);
+    BSPEC_LAUNCH((gather_rows_add_kernel<float>), n_out, 256, 0, stream, resid, (const float*)pending, rows, out, d);
   else
-    gather_rows_add_kernel<__nv_bfloat16><<<n_out, 256, 0, stream>>>(resid, (const __nv_bfloat16*)pending, rows, out, d);
+    BSPEC_LAUNCH((gather_rows_add_kernel<__nv_bfloat16>), n_out, 256, 0, stream, resid, (const __nv_bfloat16*)pending, rows, out, d);
   return BSPEC_LAUNCH_CHECK();
 }
 
@@ -181,6 +185,7 @@ BSPEC_API int bspec_gather_rows_add(const float* resid, const void* pending, int
 // u [n, 2I] = [gate | up]  ->  m [n, I]
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ u, T* __restrict__ m, int inter, size_t total) {
+  bspec::pdl_prologue();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t row = idx / inter, col = idx - row * inter;
@@ -198,9 +203,9 @@ BSPEC_API int bspec_silu_mul(const void* u, void* m, int dtype, int n, int inter
   size_t want = (total + threads - 1) / threads;
   const int blocks = (int)(want > 148 * 32 ? 148 * 32 : want);
   if (dtype == BSPEC_F32)
-    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)u, (float*)m, inter, total);
+    BSPEC_LAUNCH((silu_mul_kernel<float>), blocks, threads, 0, stream, (const float*)u, (float*)m, inter, total);
   else
-    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)u, (__nv_bfloat16*)m, inter, total);
+    BSPEC_LAUNCH((silu_mul_kernel<__nv_bfloat16>), blocks, threads, 0, stream, (const __nv_bfloat16*)u, (__nv_bfloat16*)m, inter, total);
   return BSPEC_LAUNCH_CHECK();
 }
 
@@ -218,6 +223,7 @@ __global__ void rope_kv_append_kernel(T* __restrict__ qkv, int Hq, int Hkv, int 
                                       const int* __restrict__ tok_entry, const int* __restrict__ kv_indptr,
                                       const int* __restrict__ kv_indices, T* __restrict__ cache, int page_size,
                                       int write_kv) {
+  bspec::pdl_prologue();
   extern __shared__ float cs[];  // [rot/2] cos, [rot/2] sin
   const int t = blockIdx.x;
   const int slot0 = blockIdx.y * ROPE_HEADS_PER_BLOCK;          // head slots: q heads, then k heads, then v heads
@@ -296,11 +302,11 @@ BSPEC_API int bspec_rope_kv_append(void* qkv, int dtype, int n, int Hq, int Hkv,
   dim3 grid(n, (Hq + 2 * Hkv + ROPE_HEADS_PER_BLOCK - 1) / ROPE_HEADS_PER_BLOCK);
   if (grid.y > 65535) return (int)cudaErrorInvalidConfiguration;
   if (dtype == BSPEC_F32)
-    rope_kv_append_kernel<float><<<grid, threads, smem, stream>>>((float*)qkv, Hq, Hkv, hd, inv_freq, rot, interleaved,
+    BSPEC_LAUNCH((rope_kv_append_kernel<float>), grid, threads, smem, stream, (float*)qkv, Hq, Hkv, hd, inv_freq, rot, interleaved,
                                                                  positions, tok_entry, kv_indptr, kv_indices,
                                                                  (float*)cache, page_size, write_kv);
   else
-    rope_kv_append_kernel<__nv_bfloat16><<<grid, threads, smem, stream>>>(
+    BSPEC_LAUNCH((rope_kv_append_kernel<__nv_bfloat16>), grid, threads, smem, stream, 
         (__nv_bfloat16*)qkv, Hq, Hkv, hd, inv_freq, rot, interleaved, positions, tok_entry, kv_indptr, kv_indices,
         (__nv_bfloat16*)cache, page_size, write_kv);
   return BSPEC_LAUNCH_CHECK();
@@ -311,6 +317,7 @@ template <typename T>
 __global__ void rope_inplace_kernel(T* __restrict__ x, long long row_stride, int H, int hd,
                                     const float* __restrict__ inv_freq, int rot, int interleaved,
                                     const int* __restrict__ positions) {
+  bspec::pdl_prologue();
   extern __shared__ float cs[];
   const int t = blockIdx.x, half = rot / 2;
   const int pos = positions[t];
@@ -338,8 +345,8 @@ BSPEC_API int bspec_rope_inplace(void* x, int dtype, int n, long long row_stride
   if (n <= 0 || rot <= 0) return 0;
   const size_t smem = (size_t)rot * sizeof(float);
   if (dtype == BSPEC_F32)
-    rope_inplace_kernel<float><<<n, 128, smem, stream>>>((float*)x, row_stride, H, hd, inv_freq, rot, interleaved, positions);
+    BSPEC_LAUNCH((rope_inplace_kernel<float>), n, 128, smem, stream, (float*)x, row_stride, H, hd, inv_freq, rot, interleaved, positions);
   else
-    rope_inplace_kernel<__nv_bfloat16><<<n, 128, smem, stream>>>((__nv_bfloat16*)x, row_stride, H, hd, inv_freq, rot, interleaved, positions);
+    BSPEC_LAUNCH((rope_inplace_kernel<__nv_bfloat16>), n, 128, smem, stream, (__nv_bfloat16*)x, row_stride, H, hd, inv_freq, rot, interleaved, positions);
   return BSPEC_LAUNCH_CHECK();
 }

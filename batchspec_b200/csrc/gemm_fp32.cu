@@ -10,6 +10,7 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 __global__ void __launch_bounds__(256)
 sgemm_tn_kernel(const float* __restrict__ A, const float* __restrict__ W, float* __restrict__ C, int M, int N, int K,
                 long long lda, long long ldw, long long ldc) {
+  bspec::pdl_prologue();
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -64,6 +65,6 @@ BSPEC_API int bspec_sgemm_tn(const float* A, const float* W, float* C, int M, in
   if (M <= 0 || N <= 0) return 0;
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (grid.y > 65535) return (int)cudaErrorInvalidConfiguration;
-  sgemm_tn_kernel<<<grid, 256, 0, stream>>>(A, W, C, M, N, K, lda, ldw, ldc);
+  BSPEC_LAUNCH((sgemm_tn_kernel), grid, 256, 0, stream, A, W, C, M, N, K, lda, ldw, ldc);
   return BSPEC_LAUNCH_CHECK();
 }

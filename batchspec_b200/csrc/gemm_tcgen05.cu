@@ -128,6 +128,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* part = reinterpret_cast<float*>(smem);      // [bn][128] partial tile of this K slice (reuses the stages)
 
+  bspec::pdl_launch_dependents();           // the next kernel may start its own prologue and weight prefetch
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile_a = blockIdx.x;            // 128-row tile of the operand on the accumulator rows
   const int tile_b = blockIdx.y;            // bn-row tile of the other operand
@@ -159,7 +160,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (warp == 0) {
     if (lane == 0) {
       int armed = 0;
-      for (int i = 0; i < nkb; ++i) {
+      // The weights do not depend on the kernel before this one: fetch them for the first stages at once, and
+      // only then wait for that kernel to finish before touching the activations it wrote.
+      const int pre = min(nkb, p.stages);
+      for (int i = 0; i < pre; ++i) {
+        unsigned char* a_dst = smem + (size_t)i * stage_bytes;
+        mbar_expect_tx(full + i, (uint32_t)(a_bytes + b_bytes));
+        if (p.swap) tma_load_2d(a_dst, &map_a, full + i, (kb0 + i) * BK, tile_a * TM);
+        else tma_load_2d(a_dst + a_bytes, &map_b, full + i, (kb0 + i) * BK, tile_b * p.bn);
+      }
+      bspec::pdl_wait();
+      for (int i = 0; i < pre; ++i) {
+        unsigned char* a_dst = smem + (size_t)i * stage_bytes;
+        if (p.swap) tma_load_2d(a_dst + a_bytes, &map_b, full + i, (kb0 + i) * BK, tile_b * p.bn);
+        else tma_load_2d(a_dst, &map_a, full + i, (kb0 + i) * BK, tile_a * TM);
+      }
+      armed = pre;
+      for (int i = pre; i < nkb; ++i) {
         const int s = i % p.stages;
         const uint32_t ph = (uint32_t)(i / p.stages) & 1u;
         if (!mbar_wait(empty + s, ph ^ 1u, abort_flag, p.status, 1)) break;
@@ -203,6 +220,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int row = quad * 32 + lane;                       // accumulator row of this thread
     const bool ok = mbar_wait(acc_full, 0, abort_flag, p.status, 3);
     tc_fence_after();
+    bspec::pdl_wait();                                      // C may reuse memory the kernel before still reads
     if (ok) {
       const int ra = tile_a * TM + row;                     // global row of the operand on the accumulator rows
       for (int c0 = 0; c0 < p.bn; c0 += 16) {
@@ -384,14 +402,19 @@ BSPEC_API int bspec_gemm_tc(const void* X, const void* W, void* C, int M, int N,
   cfg.blockDim = dim3(GEMM_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = p.splits;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = bspec::pdl_enabled() ? 2 : 1;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel, map_a, map_b, p);
   if (e != cudaSuccess) return (int)e;
   return BSPEC_LAUNCH_CHECK();
 }
+
+// Switch programmatic dependent launch on (default) or off for every kernel of this library.
+BSPEC_API void bspec_set_pdl(int on) { bspec::pdl_enabled() = on != 0; }

@@ -78,6 +78,7 @@ __device__ int block_count(int v, int* iscratch) {
 __global__ void __launch_bounds__(THREADS)
 threshold_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
                  const int* __restrict__ top_k, const float* __restrict__ top_p, uint32_t* __restrict__ threshold) {
+  bspec::pdl_prologue();
   __shared__ float fscratch[32];
   __shared__ int iscratch[32];
   const int r = blockIdx.x;
@@ -145,6 +146,7 @@ pick_partial_kernel(const float* __restrict__ logits, int vocab, const float* __
                     const uint32_t* __restrict__ threshold, const long long* __restrict__ stream_id,
                     const long long* __restrict__ counter, unsigned long long seed, float* __restrict__ part_v,
                     int* __restrict__ part_i) {
+  bspec::pdl_prologue();
   __shared__ ArgBest scratch[32];
   const int r = blockIdx.y, nb = gridDim.x;
   const float* row = logits + (size_t)r * vocab;
@@ -176,6 +178,7 @@ pick_partial_kernel(const float* __restrict__ logits, int vocab, const float* __
 // Stage 3 (one warp per row): best of the slices.
 __global__ void pick_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i, int nb,
                                   int* __restrict__ out) {
+  bspec::pdl_prologue();
   const int r = blockIdx.x;
   ArgBest b{-INFINITY, 0x7fffffff};
   for (int i = threadIdx.x; i < nb; i += 32) b = better(b, ArgBest{part_v[r * nb + i], part_i[r * nb + i]});
@@ -199,9 +202,9 @@ BSPEC_API int bspec_argmax(const float* logits, int rows, int vocab, float* part
   if (rows <= 0) return 0;
   if (rows > 65535) return (int)cudaErrorInvalidConfiguration;
   const int nb = bspec_pick_slices(vocab);
-  pick_partial_kernel<<<dim3(nb, rows), PICK_THREADS, 0, stream>>>(logits, vocab, nullptr, nullptr, nullptr, nullptr,
+  BSPEC_LAUNCH((pick_partial_kernel), dim3(nb, rows), PICK_THREADS, 0, stream, logits, vocab, nullptr, nullptr, nullptr, nullptr,
                                                                     0ull, part_v, part_i);
-  pick_final_kernel<<<rows, 32, 0, stream>>>(part_v, part_i, nb, out);
+  BSPEC_LAUNCH((pick_final_kernel), rows, 32, 0, stream, part_v, part_i, nb, out);
   return BSPEC_LAUNCH_CHECK();
 }
 
@@ -213,9 +216,9 @@ BSPEC_API int bspec_sample(const float* logits, int rows, int vocab, const float
   if (rows <= 0) return 0;
   if (rows > 65535) return (int)cudaErrorInvalidConfiguration;
   const int nb = bspec_pick_slices(vocab);
-  threshold_kernel<<<rows, THREADS, 0, stream>>>(logits, vocab, temperature, top_k, top_p, threshold);
-  pick_partial_kernel<<<dim3(nb, rows), PICK_THREADS, 0, stream>>>(logits, vocab, temperature, threshold, stream_id,
+  BSPEC_LAUNCH((threshold_kernel), rows, THREADS, 0, stream, logits, vocab, temperature, top_k, top_p, threshold);
+  BSPEC_LAUNCH((pick_partial_kernel), dim3(nb, rows), PICK_THREADS, 0, stream, logits, vocab, temperature, threshold, stream_id,
                                                                     counter, seed, part_v, part_i);
-  pick_final_kernel<<<rows, 32, 0, stream>>>(part_v, part_i, nb, out);
+  BSPEC_LAUNCH((pick_final_kernel), rows, 32, 0, stream, part_v, part_i, nb, out);
   return BSPEC_LAUNCH_CHECK();
 }

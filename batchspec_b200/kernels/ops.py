@@ -77,7 +77,17 @@ def load_library():
             fn.argtypes = argtypes
             fn.restype = c_longlong if name == "bspec_gemm_tc_plan" else c_int
         _lib = lib
+        if os.environ.get("BSPEC_PDL", "1") == "0":
+            set_pdl(False)
     return _lib
+
+
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launch for every kernel of the library (on by default)."""
+    lib = load_library()
+    lib.bspec_set_pdl.argtypes = [c_int]
+    lib.bspec_set_pdl.restype = None
+    lib.bspec_set_pdl(int(bool(on)))
 
 
 def library_file() -> str:
