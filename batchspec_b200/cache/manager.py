@@ -10,7 +10,8 @@ empty), finished requests' pages go back to the list and are handed out again, a
 a windowed group also gives back pages that the window has passed (their table
 entries become -1; no kernel reads them).
 
-Nothing is zeroed on reuse: kernels never read past a request's length.
+The pool is zeroed once when it is made and never again: what a kernel loads past a request's length is
+masked, it only has to be finite.
 """
 from __future__ import annotations
 
@@ -147,7 +148,9 @@ class CacheManager:
             self.groups[g].runs.append(e)
         if allocate:
             for grp in self.groups:
-                grp.pages = torch.empty((len(grp.runs), grp.pool.num_pages, 2, self.page_size * grp.entry_elems),
+                # zeroed once: kernels may load (and mask) rows of a page that no token has been written to yet,
+                # and those must not hold NaN or infinity
+                grp.pages = torch.zeros((len(grp.runs), grp.pool.num_pages, 2, self.page_size * grp.entry_elems),
                                         dtype=dtype, device=device)
         self.state_tensors: List[Optional[torch.Tensor]] = []
         self.layer_caches: List[Optional[LayerCache]] = []

@@ -17,6 +17,7 @@
 // Both skip requests that belong to the other kernel, so a mixed step launches
 // both.  Cache layer layout: [pages][2 (k, v)][Hkv][page_size][HD].
 #include "common.cuh"
+#include "tma.cuh"
 #include <math.h>
 using namespace bspec;
 
@@ -56,6 +57,14 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // element offset of (row, col) in a [rows][HD] bf16 tile whose 16-byte chunks are XOR-swizzled by the row
 template <int HD> __device__ __forceinline__ int swz(int row, int col) {
   return row * HD + ((((col >> 3) ^ (row & 7))) << 3) + (col & 7);
+}
+
+// the same for a K/V tile written by TMA with its 128-byte swizzle: HD/64 sub-tiles of [KT rows][64 columns]
+template <int HD> __device__ __forceinline__ int tswz(int row, int col) {
+  return (col >> 6) * (KT * 64) + row * 64 + ((((col & 63) >> 3) ^ (row & 7)) << 3) + (col & 7);
+}
+template <int HD, bool TMA_TILE> __device__ __forceinline__ int kv_off(int row, int col) {
+  return TMA_TILE ? tswz<HD>(row, col) : swz<HD>(row, col);
 }
 
 struct TileGeom {
@@ -105,7 +114,7 @@ __device__ __forceinline__ void load_q_tile(__nv_bfloat16* Qs, const __nv_bfloat
 
 // One warp: scores of its 16 rows against 16 keys (kb .. kb+15 of the tile), online softmax, P*V.
 // qf: A fragments of the rows for every 16-dim step.  Row state (m, l) per thread for rows lane/4 and lane/4+8.
-template <int HD>
+template <int HD, bool TMA_TILE = false>
 __device__ __forceinline__ void block16(const uint32_t (&qf)[HD / 16][4], const __nv_bfloat16* Ks,
                                         const __nv_bfloat16* Vs, int kb, int key0, int row_lim0, int row_lim1,
                                         int row_lo0, int row_lo1, int k_end, float scale_log2, float (&m)[2],
@@ -120,7 +129,7 @@ __device__ __forceinline__ void block16(const uint32_t (&qf)[HD / 16][4], const 
 #pragma unroll
   for (int ks = 0; ks < HD / 16; ++ks) {
     uint32_t b[4];
-    ldmatrix_x4(b, Ks + swz<HD>(kb + 8 * (mat >> 1) + r8, 16 * ks + 8 * (mat & 1)));
+    ldmatrix_x4(b, Ks + kv_off<HD, TMA_TILE>(kb + 8 * (mat >> 1) + r8, 16 * ks + 8 * (mat & 1)));
     mma_bf16(s[0], qf[ks], b[0], b[1]);
     mma_bf16(s[1], qf[ks], b[2], b[3]);
   }
@@ -170,7 +179,7 @@ __device__ __forceinline__ void block16(const uint32_t (&qf)[HD / 16][4], const 
       o[nd + 1][i] *= corr[i >> 1];
     }
     uint32_t b[4];
-    ldmatrix_x4_trans(b, Vs + swz<HD>(kb + 8 * (mat & 1) + r8, 8 * (nd + (mat >> 1))));
+    ldmatrix_x4_trans(b, Vs + kv_off<HD, TMA_TILE>(kb + 8 * (mat & 1) + r8, 8 * (nd + (mat >> 1))));
     mma_bf16(o[nd], pf, b[0], b[1]);
     mma_bf16(o[nd + 1], pf, b[2], b[3]);
   }
@@ -187,6 +196,110 @@ __device__ __forceinline__ bool tile_geometry(TileGeom& t, const int* qo_indptr,
   t.G = Hq / Hkv;
   t.rows_total = t.q_len * t.G;
   return true;
+}
+
+// The end of a split-key CTA, run by its 128 consumer threads: combine the 4 warps through shared memory
+// (`scratch_smem`: at least 4*16*HD + 128 floats, no longer used for K/V), write the result (one split) or the
+// partial result; with several splits the CTA that gets here last for the tile joins them in split order.
+__device__ __forceinline__ void bar_consumers() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <int HD>
+__device__ __forceinline__ void decode_finish(float* scratch_smem, int* s_last, float (&m)[2], float (&l)[2],
+                                              float (&o)[HD / 8][4], const TileGeom& t, int row0, int g, int e, int rt,
+                                              int split, int n_splits, int row_tiles, int Hq, int Hkv,
+                                              __nv_bfloat16* __restrict__ out, float* __restrict__ o_part,
+                                              float* __restrict__ ml_part, int* __restrict__ tile_counters) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+  // combine the 4 warps through shared memory (reusing the K/V stages)
+  float* Os = scratch_smem;                                 // [4][16][HD]
+  float* Ms = Os + 4 * 16 * HD;                             // [4][16]
+  float* Ls = Ms + 4 * 16;                                  // [4][16]
+#pragma unroll
+  for (int nd = 0; nd < HD / 8; ++nd)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = (lane >> 2) + 8 * (i >> 1), col = 8 * nd + 2 * (lane & 3) + (i & 1);
+      Os[(warp * 16 + row) * HD + col] = o[nd][i];
+    }
+  if ((lane & 3) == 0) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      Ms[warp * 16 + (lane >> 2) + 8 * r] = m[r];
+      Ls[warp * 16 + (lane >> 2) + 8 * r] = l[r];
+    }
+  }
+  bar_consumers();
+  const int nrows = min(16, t.rows_total - row0);
+  for (int idx = threadIdx.x; idx < nrows * HD; idx += NTHREADS) {
+    const int row = idx / HD, col = idx - row * HD;
+    float mt = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mt = fmaxf(mt, Ms[w * 16 + row]);
+    float lt = 0.f, acc = 0.f;
+    if (mt != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float f = exp2f(Ms[w * 16 + row] - mt);
+        lt += Ls[w * 16 + row] * f;
+        acc += Os[(w * 16 + row) * HD + col] * f;
+      }
+    }
+    const int r = row0 + row, qi = r / t.G, h = g * t.G + (r - qi * t.G);
+    const size_t th = (size_t)(t.q_begin + qi) * Hq + h;
+    if (n_splits == 1) {
+      out[th * HD + col] = __float2bfloat16_rn(lt > 0.f ? acc / lt : 0.f);
+    } else {
+      o_part[(th * n_splits + split) * HD + col] = acc;
+      if (col == 0) {
+        ml_part[(th * n_splits + split) * 2] = mt;
+        ml_part[(th * n_splits + split) * 2 + 1] = lt;
+      }
+    }
+  }
+  if (n_splits == 1) return;
+  // The CTA that gets here last for this tile joins the splits (in split order, so the result does not depend
+  // on which CTA it is) and resets the counter for the next launch.
+  __threadfence();
+  bar_consumers();
+  const int tile_id = (e * Hkv + g) * row_tiles + rt;
+  if (threadIdx.x == 0) *s_last = (atomicAdd(&tile_counters[tile_id], 1) == n_splits - 1);
+  bar_consumers();
+  if (!*s_last) return;
+  __threadfence();
+  float* Wt = Os;                                           // [n_splits <= 64][16] weights exp2(m_s - m)
+  float* Inv = Os + 64 * 16;                                // [16]
+  for (int row = threadIdx.x; row < nrows; row += NTHREADS) {
+    const int r = row0 + row, qi = r / t.G, h = g * t.G + (r - qi * t.G);
+    const size_t th = (size_t)(t.q_begin + qi) * Hq + h;
+    float mt = -INFINITY;
+    for (int sp = 0; sp < n_splits; ++sp) mt = fmaxf(mt, __ldcg(ml_part + (th * n_splits + sp) * 2));
+    float lt = 0.f;
+    for (int sp = 0; sp < n_splits; ++sp) {
+      const float ms = __ldcg(ml_part + (th * n_splits + sp) * 2);
+      const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - mt);
+      Wt[sp * 16 + row] = f;
+      lt += __ldcg(ml_part + (th * n_splits + sp) * 2 + 1) * f;
+    }
+    Inv[row] = lt > 0.f ? 1.f / lt : 0.f;
+  }
+  bar_consumers();
+  for (int idx = threadIdx.x; idx < nrows * HD; idx += NTHREADS) {
+    const int row = idx / HD, col = idx - row * HD;
+    const int r = row0 + row, qi = r / t.G, h = g * t.G + (r - qi * t.G);
+    const size_t th = (size_t)(t.q_begin + qi) * Hq + h;
+    float acc = 0.f;
+    for (int sp = 0; sp < n_splits; ++sp) {
+      const float f = Wt[sp * 16 + row];
+      if (f != 0.f) acc += __ldcg(o_part + (th * n_splits + sp) * HD + col) * f;
+    }
+    out[th * HD + col] = __float2bfloat16_rn(acc * Inv[row]);
+  }
+  if (threadIdx.x == 0) tile_counters[tile_id] = 0;
 }
 
 // ------------------------------------------------------------------------------------ decode (split keys)
@@ -281,96 +394,154 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride, 
       __syncthreads();
     }
   }
+  decode_finish<HD>(reinterpret_cast<float*>(KV), &s_last, m, l, o, t, row0, g, e, rt, split, n_splits, row_tiles, Hq,
+                    Hkv, out, o_part, ml_part, tile_counters);
+}
+
+// ------------------------------------------------------------------------------------ decode, K/V through TMA
+// The same split-key work as attn_decode_kernel, for page sizes 8 / 16 / 32 / 64: a fifth warp feeds a ring of
+// K/V stages with TMA tensor copies (one box per page and 64-column half, 128-byte swizzle, completion on an
+// mbarrier), so the four consumer warps spend no instructions on addresses.  A tile always loads whole pages;
+// pages outside the split's range are replaced by its nearest needed page (their keys are masked anyway), so
+// shared memory never holds bytes that were not read from the cache.  The cache must not hold NaN or infinity in
+// rows that were never written (the pool is allocated zeroed).
+constexpr int TMA_STAGES = 3;
+constexpr int DECODE_TMA_THREADS = 160;
+
+template <int HD>
+__global__ void __launch_bounds__(DECODE_TMA_THREADS)
+attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bfloat16* __restrict__ q,
+                       long long q_row_stride, __nv_bfloat16* __restrict__ out, float* __restrict__ o_part,
+                       float* __restrict__ ml_part, int* __restrict__ tile_counters, int* __restrict__ status,
+                       const int* __restrict__ qo_indptr, const int* __restrict__ positions,
+                       const int* __restrict__ kv_indptr, const int* __restrict__ kv_indices, int Hq, int Hkv,
+                       int page_size, float scale_log2, int window, int n_splits, int row_tiles, int max_q_short) {
+  bspec::pdl_prologue();
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  constexpr int TILE_ELEMS = KT * HD;                                        // one K (or V) tile
+  __nv_bfloat16* KV = reinterpret_cast<__nv_bfloat16*>(smem);                // TMA_STAGES x (K tile, V tile)
+  __nv_bfloat16* Qs = KV + TMA_STAGES * 2 * TILE_ELEMS;                      // [16][HD]
+  uint64_t* full = reinterpret_cast<uint64_t*>(Qs + 16 * HD);
+  uint64_t* empty = full + TMA_STAGES;
+  int* tbl = reinterpret_cast<int*>(empty + TMA_STAGES);                     // [TBL_MAX]
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tbl + TBL_MAX);
+  int* s_last = const_cast<int*>(abort_flag) + 1;
+
+  const int split = blockIdx.x, g = blockIdx.y;
+  const int e = blockIdx.z / row_tiles, rt = blockIdx.z - e * row_tiles;
+  TileGeom t;
+  if (!tile_geometry(t, qo_indptr, positions, e, g, Hq, Hkv)) return;
+  if (t.q_len > max_q_short) return;
+  const int row0 = rt * 16;
+  if (row0 >= t.rows_total) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qi_lo = row0 / t.G, qi_hi = min(t.q_len - 1, (row0 + 15) / t.G);
+  const int hi_key = t.pos0 + qi_hi;
+  const int lo_key = window > 0 ? max(0, t.pos0 + qi_lo - window + 1) : 0;
+  const int lo_al = (lo_key / KT) * KT;
+  const int n_keys = hi_key + 1 - lo_al;
+  const int chunk = ((((n_keys + n_splits - 1) / n_splits) + KT - 1) / KT) * KT;
+  const int k_begin = lo_al + split * chunk;
+  const int k_end = min(hi_key + 1, k_begin + chunk);
+  const int n_tiles = k_begin < k_end ? (k_end - k_begin + KT - 1) / KT : 0;
+  const int* table = kv_indices + kv_indptr[e];
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TMA_STAGES; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 4);          // one arrival per consumer warp
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+
+  if (warp == 4) {
+    // ---- producer: one lane issues every copy
+    if (n_tiles > 0) {
+      const int first_pg = max(k_begin, lo_key) / page_size, last_pg = (k_end - 1) / page_size;
+      const int n_pg = last_pg - first_pg + 1;
+      const bool in_smem = n_pg <= TBL_MAX;
+      if (in_smem) {
+        for (int i = lane; i < n_pg; i += 32) tbl[i] = table[first_pg + i];
+        __syncwarp();
+      }
+      if (lane == 0) {
+        const int pages_per_tile = KT / page_size;
+        constexpr uint32_t tile_bytes = 2u * TILE_ELEMS * 2u;
+        for (int it = 0; it < n_tiles; ++it) {
+          const int s = it % TMA_STAGES;
+          const uint32_t ph = (uint32_t)(it / TMA_STAGES) & 1u;
+          if (!mbar_wait(empty + s, ph ^ 1u, abort_flag, status, 11)) break;
+          __nv_bfloat16* Ks = KV + (size_t)s * 2 * TILE_ELEMS;
+          mbar_expect_tx(full + s, tile_bytes);
+          const int key0 = k_begin + it * KT;
+          for (int pp = 0; pp < pages_per_tile; ++pp) {
+            int pg = (key0 + pp * page_size) / page_size;
+            pg = min(max(pg, first_pg), last_pg);
+            const int page = in_smem ? tbl[pg - first_pg] : table[pg];
+            const int row_k = ((page * 2) * Hkv + g) * page_size;           // first cache row of this page's K
+            const int row_v = row_k + Hkv * page_size;
+#pragma unroll
+            for (int c = 0; c < HD / 64; ++c) {
+              tma_load_2d(Ks + c * (KT * 64) + pp * page_size * 64, &kv_map, full + s, c * 64, row_k);
+              tma_load_2d(Ks + TILE_ELEMS + c * (KT * 64) + pp * page_size * 64, &kv_map, full + s, c * 64, row_v);
+            }
+          }
+        }
+      }
+    }
+    return;
+  }
+
+  // ---- consumers (threads 0..127)
+  int lim[2], lo[2];
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
-    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
-    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    const int row = row0 + (lane >> 2) + 8 * r;
+    const int qi = row / t.G;
+    lim[r] = row < t.rows_total ? t.pos0 + qi : -1;
+    lo[r] = window > 0 ? max(0, t.pos0 + qi - window + 1) : 0;
   }
-  // combine the 4 warps through shared memory (reusing the K/V stages)
-  float* Os = reinterpret_cast<float*>(KV);                 // [4][16][HD]
-  float* Ms = Os + 4 * 16 * HD;                             // [4][16]
-  float* Ls = Ms + 4 * 16;                                  // [4][16]
+  if (n_tiles > 0) {
+    load_q_tile<HD>(Qs, q, q_row_stride, t, row0, 16);
+    bar_consumers();
+    uint32_t qf[HD / 16][4];
+    {
+      const int mat = lane >> 3, r8 = lane & 7;
 #pragma unroll
-  for (int nd = 0; nd < HD / 8; ++nd)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int row = (lane >> 2) + 8 * (i >> 1), col = 8 * nd + 2 * (lane & 3) + (i & 1);
-      Os[(warp * 16 + row) * HD + col] = o[nd][i];
+      for (int ks = 0; ks < HD / 16; ++ks)
+        ldmatrix_x4(qf[ks], Qs + swz<HD>(8 * (mat & 1) + r8, 16 * ks + 8 * (mat >> 1)));
     }
-  if ((lane & 3) == 0) {
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      Ms[warp * 16 + (lane >> 2) + 8 * r] = m[r];
-      Ls[warp * 16 + (lane >> 2) + 8 * r] = l[r];
-    }
-  }
-  __syncthreads();
-  const int nrows = min(16, t.rows_total - row0);
-  for (int idx = threadIdx.x; idx < nrows * HD; idx += NTHREADS) {
-    const int row = idx / HD, col = idx - row * HD;
-    float mt = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) mt = fmaxf(mt, Ms[w * 16 + row]);
-    float lt = 0.f, acc = 0.f;
-    if (mt != -INFINITY) {
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const float f = exp2f(Ms[w * 16 + row] - mt);
-        lt += Ls[w * 16 + row] * f;
-        acc += Os[(w * 16 + row) * HD + col] * f;
-      }
-    }
-    const int r = row0 + row, qi = r / t.G, h = g * t.G + (r - qi * t.G);
-    const size_t th = (size_t)(t.q_begin + qi) * Hq + h;
-    if (n_splits == 1) {
-      out[th * HD + col] = __float2bfloat16_rn(lt > 0.f ? acc / lt : 0.f);
-    } else {
-      o_part[(th * n_splits + split) * HD + col] = acc;
-      if (col == 0) {
-        ml_part[(th * n_splits + split) * 2] = mt;
-        ml_part[(th * n_splits + split) * 2 + 1] = lt;
-      }
+    for (int it = 0; it < n_tiles; ++it) {
+      const int s = it % TMA_STAGES;
+      const uint32_t ph = (uint32_t)(it / TMA_STAGES) & 1u;
+      if (!mbar_wait(full + s, ph, abort_flag, status, 12)) break;
+      const __nv_bfloat16* Ks = KV + (size_t)s * 2 * TILE_ELEMS;
+      const int key0 = k_begin + it * KT;
+      if (key0 + 16 * warp < k_end)
+        block16<HD, true>(qf, Ks, Ks + TILE_ELEMS, 16 * warp, key0, lim[0], lim[1], lo[0], lo[1], k_end, scale_log2,
+                          m, l, o);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty + s);
     }
   }
-  if (n_splits == 1) return;
-  // The CTA that gets here last for this tile joins the splits (in split order, so the result does not depend
-  // on which CTA it is) and resets the counter for the next launch.
-  __threadfence();
-  __syncthreads();
-  const int tile_id = (e * Hkv + g) * row_tiles + rt;
-  if (threadIdx.x == 0) s_last = (atomicAdd(&tile_counters[tile_id], 1) == n_splits - 1);
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-  float* Wt = Os;                                           // [n_splits <= 64][16] weights exp2(m_s - m)
-  float* Inv = Os + 64 * 16;                                // [16]
-  for (int row = threadIdx.x; row < nrows; row += NTHREADS) {
-    const int r = row0 + row, qi = r / t.G, h = g * t.G + (r - qi * t.G);
-    const size_t th = (size_t)(t.q_begin + qi) * Hq + h;
-    float mt = -INFINITY;
-    for (int sp = 0; sp < n_splits; ++sp) mt = fmaxf(mt, __ldcg(ml_part + (th * n_splits + sp) * 2));
-    float lt = 0.f;
-    for (int sp = 0; sp < n_splits; ++sp) {
-      const float ms = __ldcg(ml_part + (th * n_splits + sp) * 2);
-      const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - mt);
-      Wt[sp * 16 + row] = f;
-      lt += __ldcg(ml_part + (th * n_splits + sp) * 2 + 1) * f;
-    }
-    Inv[row] = lt > 0.f ? 1.f / lt : 0.f;
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < nrows * HD; idx += NTHREADS) {
-    const int row = idx / HD, col = idx - row * HD;
-    const int r = row0 + row, qi = r / t.G, h = g * t.G + (r - qi * t.G);
-    const size_t th = (size_t)(t.q_begin + qi) * Hq + h;
-    float acc = 0.f;
-    for (int sp = 0; sp < n_splits; ++sp) {
-      const float f = Wt[sp * 16 + row];
-      if (f != 0.f) acc += __ldcg(o_part + (th * n_splits + sp) * HD + col) * f;
-    }
-    out[th * HD + col] = __float2bfloat16_rn(acc * Inv[row]);
-  }
-  if (threadIdx.x == 0) tile_counters[tile_id] = 0;
+  bar_consumers();                        // every warp is done with the stages (or gave up)
+  if (*abort_flag) return;
+  decode_finish<HD>(reinterpret_cast<float*>(KV), s_last, m, l, o, t, row0, g, e, rt, split, n_splits, row_tiles, Hq,
+                    Hkv, out, o_part, ml_part, tile_counters);
+}
+
+template <int HD> size_t decode_tma_smem() {
+  return 1024 + (size_t)TMA_STAGES * 2 * KT * HD * 2 + (size_t)16 * HD * 2 + 2 * TMA_STAGES * 8 + (size_t)TBL_MAX * 4 + 64;
 }
 
 // ------------------------------------------------------------------------------------ prefill (64 rows per CTA)
@@ -479,7 +650,7 @@ template <int HD> size_t prefill_smem() { return (size_t)(64 + 4 * KT) * HD * 2;
 
 template <int HD>
 int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, float* o_part, float* ml_part,
-           int* tile_counters, const __nv_bfloat16* cache, const int* qo_indptr, const int* positions, const int* tok_entry,
+           int* tile_counters, int* status, long long kv_rows, const __nv_bfloat16* cache, const int* qo_indptr, const int* positions, const int* tok_entry,
            const int* kv_indptr, const int* kv_indices, int n_entries, int n_tokens, int max_q_len, int Hq, int Hkv,
            int page_size, float scale, int window, int n_splits, int max_q_short, int run_decode, int run_prefill,
            cudaStream_t stream) {
@@ -488,6 +659,7 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
   static bool attr_set = false;
   if (!attr_set) {
     cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem<HD>());
+    cudaFuncSetAttribute(attn_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_tma_smem<HD>());
     cudaFuncSetAttribute(attn_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_smem<HD>());
     attr_set = true;
   }
@@ -496,9 +668,20 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
     const int row_tiles = (short_q * G + 15) / 16;
     dim3 grid(n_splits, Hkv, n_entries * row_tiles);
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidConfiguration;
-    BSPEC_LAUNCH((attn_decode_kernel<HD>), grid, NTHREADS, decode_smem<HD>(), stream, 
-        q, q_row_stride, out, o_part, ml_part, tile_counters, cache, qo_indptr, positions, kv_indptr, kv_indices, Hq,
-        Hkv, page_size, scale_log2, window, n_splits, row_tiles, max_q_short);
+    bool launched = false;
+    if (kv_rows > 0 && status != nullptr && page_size % 8 == 0 && KT % page_size == 0) {
+      CUtensorMap kv_map;
+      if (make_map_2d_bf16(&kv_map, cache, kv_rows, HD, page_size, 64)) {
+        BSPEC_LAUNCH((attn_decode_tma_kernel<HD>), grid, DECODE_TMA_THREADS, decode_tma_smem<HD>(), stream, kv_map, q,
+                     q_row_stride, out, o_part, ml_part, tile_counters, status, qo_indptr, positions, kv_indptr,
+                     kv_indices, Hq, Hkv, page_size, scale_log2, window, n_splits, row_tiles, max_q_short);
+        launched = true;
+      }
+    }
+    if (!launched)
+      BSPEC_LAUNCH((attn_decode_kernel<HD>), grid, NTHREADS, decode_smem<HD>(), stream,
+                   q, q_row_stride, out, o_part, ml_part, tile_counters, cache, qo_indptr, positions, kv_indptr,
+                   kv_indices, Hq, Hkv, page_size, scale_log2, window, n_splits, row_tiles, max_q_short);
     const int err = (int)cudaGetLastError();
     if (err) return err;
   }
@@ -519,8 +702,10 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
 // ml_part float32 [n_tokens * Hq * n_splits * 2] and tile_counters int32 [n_entries * Hkv * row tiles], which must
 // be zero before the first launch and is left zero by every launch.  Returns cudaErrorInvalidValue for an
 // unsupported head_dim.
+// status: one int on the device (0 unless a bounded wait ran out); n_pages: pages of this cache layer (lets the
+// split-key kernel load K/V through TMA; 0 keeps it on plain asynchronous copies).
 BSPEC_API int bspec_attention_bf16(const void* q, long long q_row_stride, void* out, float* o_part, float* ml_part,
-                                   int* tile_counters, const void* cache, const int* qo_indptr, const int* positions,
+                                   int* tile_counters, int* status, long long n_pages, const void* cache, const int* qo_indptr, const int* positions,
                                    const int* tok_entry, const int* kv_indptr, const int* kv_indices, int n_entries,
                                    int n_tokens, int max_q_len, int Hq, int Hkv, int hd, int page_size, float scale,
                                    int window, int n_splits, int max_q_short, int run_decode, int run_prefill,
@@ -529,7 +714,7 @@ BSPEC_API int bspec_attention_bf16(const void* q, long long q_row_stride, void* 
   if (Hq % Hkv != 0 || n_splits < 1 || n_splits > 64) return (int)cudaErrorInvalidValue;
 #define GO(HDV)                                                                                                    \
   return launch<HDV>((const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, o_part, ml_part, tile_counters,   \
-                     (const __nv_bfloat16*)cache, qo_indptr, positions, tok_entry, kv_indptr, kv_indices, n_entries, \
+                     status, n_pages * 2 * Hkv * page_size, (const __nv_bfloat16*)cache, qo_indptr, positions, tok_entry, kv_indptr, kv_indices, n_entries, \
                      n_tokens, max_q_len, Hq, Hkv, page_size, scale, window, n_splits, max_q_short, run_decode,      \
                      run_prefill, stream)
   if (hd == 64) GO(64);

@@ -19,51 +19,15 @@
 // Every wait on an mbarrier is bounded: when it runs out the CTA records a code in `status`, stops issuing work,
 // gives its TMEM back and returns.
 #include "common.cuh"
-#include <cuda.h>
-#include <cudaTypedefs.h>
+#include "tma.cuh"
+
+using namespace bspec;
 
 namespace {
 
 constexpr int BK = 64;                 // K elements per stage (one 128-byte swizzle span of bf16)
 constexpr int TM = 128;                // accumulator rows (UMMA M)
 constexpr int GEMM_THREADS = 192;
-constexpr uint32_t WAIT_LIMIT = 1u << 24;
-
-__device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(s32(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false (and raises the CTA's abort flag) when the limit is hit or another role aborted.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                          int code) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (i > 4096) __nanosleep(64);
-  }
-  *abort_flag = 1;
-  atomicCAS(status, 0, code);
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(s32(dst)), "l"(map), "r"(s32(bar)), "r"(x), "r"(y) : "memory");
-}
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -302,31 +266,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------------------- host side
-PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
-  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
-  if (fn == nullptr) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
-  }
-  return fn;
-}
-
-// rows x K bf16 matrix, K contiguous; box = box_rows x 64 elements; 128-byte swizzle; out-of-range reads give zeros
-bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
-  auto fn = encode_fn();
-  if (fn == nullptr) return false;
-  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  cuuint32_t elem[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 size_t smem_bytes(int bn, int stages) {
   const int a_bytes = TM * BK * 2, b_bytes = bn * BK * 2;
   const int stage_bytes = a_bytes + ((b_bytes + 1023) & ~1023);
@@ -346,11 +285,21 @@ BSPEC_API long long bspec_gemm_tc_plan(int M, int N, int K, int sm_count, int* p
     bn = 16;
     while (bn < M) bn <<= 1;
     const int tiles = (N + TM - 1) / TM;
-    // two CTAs share an SM: cut K so that the CTAs about fill those slots, at least 8 K blocks per slice
-    splits = (2 * sm_count) / tiles;
-    if (splits < 1) splits = 1;
-    if (splits > kb_total / 8) splits = kb_total / 8 > 0 ? kb_total / 8 : 1;
-    if (splits > 8) splits = 8;                           // one portable cluster
+    // Two CTAs share an SM.  Cut K into the number of slices (one cluster, at most 8 CTAs, at least 4 K blocks
+    // each) that leaves the fewest of those slots idle in the last wave; among equals, the fewest slices.
+    const int slots = 2 * sm_count;
+    double best = -1.0;
+    for (int s = 1; s <= 8 && s * 4 <= (kb_total > 4 ? kb_total : 4); ++s) {
+      const int per_s = (kb_total + s - 1) / s;
+      const int real = (kb_total + per_s - 1) / per_s;
+      if (real != s) continue;
+      const long long ctas = (long long)tiles * s;
+      const double eff = (double)ctas / (double)(((ctas + slots - 1) / slots) * slots);
+      if (eff > best + 1e-9) {
+        best = eff;
+        splits = s;
+      }
+    }
     smem_budget = 108 * 1024;
   } else {
     swap = 0;
@@ -386,7 +335,7 @@ BSPEC_API int bspec_gemm_tc(const void* X, const void* W, void* C, int M, int N,
   const void* a_ptr = p.swap ? W : X;
   const void* b_ptr = p.swap ? X : W;
   const int a_rows = p.swap ? N : M, b_rows = p.swap ? M : N;
-  if (!make_map(&map_a, a_ptr, a_rows, K, TM) || !make_map(&map_b, b_ptr, b_rows, K, p.bn))
+  if (!make_map_2d_bf16(&map_a, a_ptr, a_rows, K, TM, BK) || !make_map_2d_bf16(&map_b, b_ptr, b_rows, K, p.bn, BK))
     return (int)cudaErrorInvalidValue;
   const size_t smem = smem_bytes(p.bn, p.stages);
   static size_t smem_set = 0;

@@ -83,10 +83,13 @@ def bench_gemms(cfg, ms, timer, pk, dev):
             print(f"{name:8s} {M:5d} {N:7d} {K:6d} | {t_tc:10.4f} {gb(t_tc):7.0f} {tf(t_tc):7.1f} | {t_lib:10.4f} {gb(t_lib):7.0f} {tf(t_lib):7.1f} | {frac:.3f}")
 
 
-def bench_attention(cfg, timer, pk, dev, page=16):
+ATTENTION_CASES = [(1, 1, 2304), (8, 1, 2304), (64, 1, 2304), (8, 1, 30000), (1, 2048, 2048), (4, 512, 4096)]
+
+
+def bench_attention(cfg, timer, pk, dev, page=16, cases=None):
     Hq, Hkv, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
     print(f"{'attention':10s} {'batch':>5s} {'q_len':>5s} {'kv_len':>6s} | {'ms':>8s} {'GB/s':>7s} {'TF/s':>7s} | frac of {pk['source']} peak")
-    for batch, q_len, kv_len in [(1, 1, 2304), (8, 1, 2304), (64, 1, 2304), (8, 1, 30000), (1, 2048, 2048), (4, 512, 4096)]:
+    for batch, q_len, kv_len in cases or ATTENTION_CASES:
         pages_per = -(-kv_len // page)
         n_pages = batch * pages_per
         cache = (torch.randn(n_pages, 2, Hkv, page, hd, device=dev) * 0.5).bfloat16()
@@ -145,6 +148,8 @@ def main():
     ap.add_argument("--config", default="llama-3-8b")
     ap.add_argument("--what", nargs="+", default=["gemm", "attention", "small"], choices=["gemm", "attention", "small"])
     ap.add_argument("--m", nargs="+", type=int, default=[1, 8, 64, 2048])
+    ap.add_argument("--attn-case", nargs=3, type=int, action="append", metavar=("BATCH", "Q_LEN", "KV_LEN"),
+                    help="attention case(s) to time instead of the built-in list")
     a = ap.parse_args()
     dev = torch.device("cuda:0")
     ops.load_library()
@@ -156,7 +161,7 @@ def main():
         if "gemm" in a.what:
             bench_gemms(cfg, a.m, timer, pk, dev)
         if "attention" in a.what:
-            bench_attention(cfg, timer, pk, dev)
+            bench_attention(cfg, timer, pk, dev, cases=[tuple(c) for c in a.attn_case] if a.attn_case else None)
         if "small" in a.what:
             bench_small(cfg, [m for m in a.m if m <= 2048], timer, pk, dev)
 

@@ -48,8 +48,8 @@ _SIGNATURES = {
     "bspec_rope_inplace": [c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "bspec_attention_generic": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
-    "bspec_attention_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+    "bspec_attention_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong,
+                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                              c_int, c_int, c_int, c_int, c_void_p],
     "bspec_gemm_tc_plan": [c_int, c_int, c_int, c_int, c_void_p],
     "bspec_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
@@ -204,15 +204,16 @@ def rope_inplace(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tenso
 
 # ---------------------------------------------------------------------------- attention
 
+USE_TMA_ATTENTION = os.environ.get("BSPEC_TMA_ATTENTION", "1") != "0"
 FORCE_GENERIC_ATTENTION = False      # tests set this to compare the tensor-core kernels with the generic one
 _SM_COUNT = 148
 
 
-_DECODE_CTAS_PER_SM = 3           # the split-key kernel's shared memory lets three CTAs share an SM
 _tile_counters = {}               # device -> zeroed int32 buffers kept alive (graphs hold their addresses)
 
 
-def attention_splits(n_entries: int, n_kv_heads: int, group: int, max_q_len: int, max_kv_len: int) -> int:
+def attention_splits(n_entries: int, n_kv_heads: int, group: int, max_q_len: int, max_kv_len: int,
+                     ctas_per_sm: int = 3) -> int:
     """How many ways the split-key kernel cuts each request's keys.  If chunks of
     at least 128 keys give no more CTAs than fit on the device at once, use them
     all; otherwise chunks of at least 256 keys, with the count that wastes the
@@ -223,7 +224,7 @@ def attention_splits(n_entries: int, n_kv_heads: int, group: int, max_q_len: int
         return 1
     row_tiles = -(-(max_q_len * group) // 16)
     base = max(1, n_entries * n_kv_heads * row_tiles)
-    slots = _SM_COUNT * _DECODE_CTAS_PER_SM
+    slots = _SM_COUNT * ctas_per_sm
     fine = min(64, max(1, -(-max_kv_len // 128)))
     if base * fine <= slots:
         return fine
@@ -256,8 +257,10 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, c
     if qkv.dtype == torch.bfloat16 and head_dim in (64, 128, 256) and not FORCE_GENERIC_ATTENTION:
         group = n_heads // n_kv_heads
         short = max(1, 16 // group)
+        # the TMA-fed split-key kernel (page sizes 8..64) fits two CTAs per SM, the plain one three
+        tma = USE_TMA_ATTENTION and tables.page_size % 8 == 0 and 64 % tables.page_size == 0
         n_splits = ctx.extras.get("attn_splits") or attention_splits(ctx.n_entries, n_kv_heads, group, ctx.max_q_len,
-                                                                     ctx.max_kv_len)
+                                                                     ctx.max_kv_len, 2 if tma else 3)
         o_part = ml_part = counters = None
         if n_splits > 1:
             o_part = torch.empty((ctx.n_tokens * n_heads * n_splits * head_dim,), dtype=torch.float32, device=qkv.device)
@@ -268,7 +271,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, c
         run_prefill = int(ctx.max_q_len > short)
         _check(lib.bspec_attention_bf16(
             qkv.data_ptr(), qkv.stride(0), out.data_ptr(), _ptr(o_part), _ptr(ml_part), _ptr(counters),
-            cache.data_ptr(),
+            _status_word(qkv.device).data_ptr(), cache.shape[0] if tma else 0, cache.data_ptr(),
             ctx.qo_indptr.data_ptr(), ctx.positions.data_ptr(), ctx.tok_entry.data_ptr(), tables.kv_indptr.data_ptr(),
             tables.kv_indices.data_ptr(), ctx.n_entries, ctx.n_tokens, ctx.max_q_len, n_heads, n_kv_heads, head_dim,
             tables.page_size, float(scale), int(window), n_splits, short, run_decode, run_prefill, _stream()),
@@ -304,8 +307,12 @@ def check_status() -> None:
         code = int(t.item())
         if code:
             t.zero_()
-            raise KernelError(f"a tcgen05 GEMM on {dev} gave up waiting (code {code}: 1 = stage never freed, "
-                              f"2 = operands never arrived, 3 = accumulator never completed)")
+            for bufs in _tile_counters.values():
+                for b in bufs:
+                    b.zero_()
+            raise KernelError(f"a kernel on {dev} gave up a bounded wait (code {code}: GEMM 1 = stage never freed, "
+                              f"2 = operands never arrived, 3 = accumulator never completed; attention 11 = stage "
+                              f"never freed, 12 = keys never arrived)")
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
