@@ -285,21 +285,13 @@ BSPEC_API long long bspec_gemm_tc_plan(int M, int N, int K, int sm_count, int* p
     bn = 16;
     while (bn < M) bn <<= 1;
     const int tiles = (N + TM - 1) / TM;
-    // Two CTAs share an SM.  Cut K into the number of slices (one cluster, at most 8 CTAs, at least 4 K blocks
-    // each) that leaves the fewest of those slots idle in the last wave; among equals, the fewest slices.
-    const int slots = 2 * sm_count;
-    double best = -1.0;
-    for (int s = 1; s <= 8 && s * 4 <= (kb_total > 4 ? kb_total : 4); ++s) {
-      const int per_s = (kb_total + s - 1) / s;
-      const int real = (kb_total + per_s - 1) / per_s;
-      if (real != s) continue;
-      const long long ctas = (long long)tiles * s;
-      const double eff = (double)ctas / (double)(((ctas + slots - 1) / slots) * slots);
-      if (eff > best + 1e-9) {
-        best = eff;
-        splits = s;
-      }
-    }
+    // Two CTAs share an SM: cut K into slices (the CTAs of one cluster, at most 8) so that the CTAs about fill
+    // those slots, keeping at least 8 K blocks per slice.  Measured on B200: more, shorter slices lose more to the
+    // per-CTA prologue and epilogue than they gain in balance.
+    splits = (2 * sm_count) / tiles;
+    if (splits < 1) splits = 1;
+    if (splits > kb_total / 8) splits = kb_total / 8 > 0 ? kb_total / 8 : 1;
+    if (splits > 8) splits = 8;
     smem_budget = 108 * 1024;
   } else {
     swap = 0;

@@ -214,11 +214,12 @@ _tile_counters = {}               # device -> zeroed int32 buffers kept alive (g
 
 def attention_splits(n_entries: int, n_kv_heads: int, group: int, max_q_len: int, max_kv_len: int,
                      ctas_per_sm: int = 3) -> int:
-    """How many ways the split-key kernel cuts each request's keys.  If chunks of
-    at least 128 keys give no more CTAs than fit on the device at once, use them
-    all; otherwise chunks of at least 256 keys, with the count that wastes the
-    least of the last wave.  1 when the step also holds long portions (they go to
-    the 64-row kernel, which fills the device by itself)."""
+    """How many ways the split-key kernel cuts each request's keys.  Every CTA pays a prologue and, with more
+    than one split, a join, so long chunks are preferred: if chunks of at least 128 keys give no more CTAs than
+    fit on the device at once, use them all (small batches: fill the SMs); otherwise chunks of at least 512
+    keys, one split if that already keeps four fifths of the last wave busy, else the count that wastes the
+    least of it.  1 when the step also holds long portions (they go to the 64-row kernel, which fills the
+    device by itself)."""
     short = max(1, 16 // group)
     if max_q_len > short:
         return 1
@@ -228,12 +229,13 @@ def attention_splits(n_entries: int, n_kv_heads: int, group: int, max_q_len: int
     fine = min(64, max(1, -(-max_kv_len // 128)))
     if base * fine <= slots:
         return fine
-    best, best_eff = 1, 0.0
-    for s in range(1, min(64, max(1, -(-max_kv_len // 256))) + 1):
-        total = base * s
-        eff = total / (-(-total // slots) * slots)
-        if eff > best_eff + 1e-9 or (abs(eff - best_eff) <= 1e-9 and s > best):
-            best, best_eff = s, eff
+    eff = lambda s: (base * s) / (-(-(base * s) // slots) * slots)
+    if eff(1) >= 0.8:
+        return 1
+    best, best_eff = 1, eff(1)
+    for s in range(2, min(64, max(1, max_kv_len // 512)) + 1):
+        if eff(s) > best_eff + 1e-9:
+            best, best_eff = s, eff(s)
     return best
 
 
