@@ -723,3 +723,90 @@ BSPEC_API int bspec_attention_bf16(const void* q, long long q_row_stride, void* 
 #undef GO
   return (int)cudaErrorInvalidValue;
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// The same split-key decode attention for callers that cannot allocate: see attention_noalloc.h.
+#include "attention_noalloc.h"
+#include <mutex>
+#include <stdio.h>
+
+namespace {
+// Scratch of the no-allocation entry point: [partial results | counters].  In host code this name is only a handle
+// for cudaGetSymbolAddress; the kernels get the device address looked up below.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[BSPEC_NOALLOC_SCRATCH_BYTES];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+void* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+std::mutex g_noalloc_mutex;
+
+int noalloc_refuse(int code, char* message, int message_len, const char* text) {
+  if (message != nullptr && message_len > 0) snprintf(message, (size_t)message_len, "%s", text);
+  return code;
+}
+}  // namespace
+
+BSPEC_API int bspec_attention_decode_noalloc(const void* q, long long q_row_stride, void* out, const void* cache,
+                                             const int* qo_indptr, const int* positions, const int* tok_entry,
+                                             const int* kv_indptr, const int* kv_indices, int n_entries, int n_tokens,
+                                             int max_q_len, int Hq, int Hkv, int head_dim, int page_size, float scale,
+                                             int window, int n_splits, cudaStream_t stream, char* message,
+                                             int message_len) {
+  char text[256];
+  if (n_entries <= 0 || n_tokens <= 0) return BSPEC_NOALLOC_OK;
+  if (Hkv <= 0 || Hq % Hkv != 0 || (head_dim != 64 && head_dim != 128 && head_dim != 256) || n_splits < 1 ||
+      n_splits > 64 || page_size < 1)
+    return noalloc_refuse(BSPEC_NOALLOC_BAD_ARGUMENT, message, message_len,
+                          "attention_decode_noalloc: head_dim must be 64/128/256, Hq a multiple of Hkv, 1 <= n_splits <= 64");
+  const int G = Hq / Hkv;
+  const int max_q_short = 16 / G > 1 ? 16 / G : 1;
+  if (max_q_len > max_q_short) {
+    snprintf(text, sizeof(text), "attention_decode_noalloc: serves requests of at most %d new tokens at this group size, got %d",
+             max_q_short, max_q_len);
+    return noalloc_refuse(BSPEC_NOALLOC_BAD_ARGUMENT, message, message_len, text);
+  }
+  const int row_tiles = (max_q_len * G + 15) / 16;
+  const unsigned long long need_floats = (unsigned long long)n_tokens * Hq * n_splits * (head_dim + 2);
+  const unsigned long long need_counters = (unsigned long long)n_entries * Hkv * row_tiles;
+  if (n_splits > 1 && (need_floats > BSPEC_NOALLOC_MAX_PARTIAL_FLOATS || need_counters > BSPEC_NOALLOC_MAX_COUNTERS)) {
+    snprintf(text, sizeof(text),
+             "attention_decode_noalloc: needs %llu scratch floats and %llu counters, the built-in array holds %u and %u",
+             need_floats, need_counters, BSPEC_NOALLOC_MAX_PARTIAL_FLOATS, BSPEC_NOALLOC_MAX_COUNTERS);
+    return noalloc_refuse(BSPEC_NOALLOC_TOO_LARGE, message, message_len, text);
+  }
+  // Once per device, with that device current: the device address of the array.
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES)
+    return noalloc_refuse(BSPEC_NOALLOC_SETUP_FAILED, message, message_len, "attention_decode_noalloc: no current device");
+  void* base = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+      if (e != cudaSuccess || p == nullptr) {
+        snprintf(text, sizeof(text), "attention_decode_noalloc: cudaGetSymbolAddress failed on device %d: %s", dev,
+                 cudaGetErrorString(e));
+        return noalloc_refuse(BSPEC_NOALLOC_SETUP_FAILED, message, message_len, text);
+      }
+      g_noalloc_ptr[dev] = p;
+    }
+    base = g_noalloc_ptr[dev];
+  }
+  float* o_part = reinterpret_cast<float*>(base);
+  float* ml_part = o_part + (size_t)n_tokens * Hq * n_splits * head_dim;
+  int* counters = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(base) + (size_t)BSPEC_NOALLOC_MAX_PARTIAL_FLOATS * 4);
+  if (n_splits > 1) {
+    // the counters must start at zero whatever an earlier (possibly failed) call left behind
+    const cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)need_counters * sizeof(int), stream);
+    if (e != cudaSuccess) return (int)e;
+  }
+#define GO(HDV)                                                                                                     \
+  return launch<HDV>((const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, o_part, ml_part, counters, nullptr, \
+                     0, (const __nv_bfloat16*)cache, qo_indptr, positions, tok_entry, kv_indptr, kv_indices,        \
+                     n_entries, n_tokens, max_q_len, Hq, Hkv, page_size, scale, window, n_splits, max_q_short, 1, 0, \
+                     stream)
+  if (head_dim == 64) GO(64);
+  if (head_dim == 128) GO(128);
+  GO(256);
+#undef GO
+}
