@@ -416,7 +416,10 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
                        const int* __restrict__ qo_indptr, const int* __restrict__ positions,
                        const int* __restrict__ kv_indptr, const int* __restrict__ kv_indices, int Hq, int Hkv,
                        int page_size, float scale_log2, int window, int n_splits, int row_tiles, int max_q_short) {
-  bspec::pdl_prologue();
+  // The step's metadata (lengths, positions, block tables) was uploaded before the step's first kernel, and every
+  // cached key below the first new token was written by earlier steps: the producer may fetch those tiles while
+  // the kernel before this one (which writes q and the new tokens' keys and values) is still running.
+  bspec::pdl_launch_dependents();
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
   constexpr int TILE_ELEMS = KT * HD;                                        // one K (or V) tile
@@ -477,9 +480,14 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
       if (lane == 0) {
         const int pages_per_tile = KT / page_size;
         constexpr uint32_t tile_bytes = 2u * TILE_ELEMS * 2u;
+        bool waited = false;
         for (int it = 0; it < n_tiles; ++it) {
           const int s = it % TMA_STAGES;
           const uint32_t ph = (uint32_t)(it / TMA_STAGES) & 1u;
+          if (!waited && (it >= TMA_STAGES || k_begin + (it + 1) * KT > t.pos0)) {
+            bspec::pdl_wait();             // this tile holds new keys, or a stage must first be released by consumers
+            waited = true;
+          }
           if (!mbar_wait(empty + s, ph ^ 1u, abort_flag, status, 11)) break;
           __nv_bfloat16* Ks = KV + (size_t)s * 2 * TILE_ELEMS;
           mbar_expect_tx(full + s, tile_bytes);
@@ -503,6 +511,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
   }
 
   // ---- consumers (threads 0..127)
+  bspec::pdl_wait();
   int lim[2], lo[2];
 #pragma unroll
   for (int r = 0; r < 2; ++r) {

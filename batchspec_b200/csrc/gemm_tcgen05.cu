@@ -72,6 +72,7 @@ struct GemmParams {
   int splits;
   int kblocks_per_split;
   int stages;
+  int prefetch_kb;       // K blocks of weights (beyond the stages) to pull into the L2 before waiting on the predecessor
 };
 
 __device__ __forceinline__ void store_out(void* C, int out_f32, size_t idx, float v) {
@@ -132,6 +133,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         mbar_expect_tx(full + i, (uint32_t)(a_bytes + b_bytes));
         if (p.swap) tma_load_2d(a_dst, &map_a, full + i, (kb0 + i) * BK, tile_a * TM);
         else tma_load_2d(a_dst + a_bytes, &map_b, full + i, (kb0 + i) * BK, tile_b * p.bn);
+      }
+      const int pf_end = min(nkb, pre + p.prefetch_kb);
+      for (int i = pre; i < pf_end; ++i) {
+        if (p.swap) tma_prefetch_2d(&map_a, (kb0 + i) * BK, tile_a * TM);
+        else tma_prefetch_2d(&map_b, (kb0 + i) * BK, tile_b * p.bn);
       }
       bspec::pdl_wait();
       for (int i = 0; i < pre; ++i) {
@@ -323,6 +329,14 @@ BSPEC_API int bspec_gemm_tc(const void* X, const void* W, void* C, int M, int N,
   p.swap = plan[0]; p.bn = plan[1]; p.splits = plan[2]; p.stages = plan[3];
   const int kb_total = (K + BK - 1) / BK;
   p.kblocks_per_split = (kb_total + p.splits - 1) / p.splits;
+  {
+    // weights this launch may park in the L2 ahead of time: at most 48 MB (the L2 has 126 MB)
+    const long long ctas = (long long)plan[4] * p.splits;
+    const long long per_kb = ctas * (p.swap ? TM : p.bn) * BK * 2;
+    long long pf = per_kb > 0 ? (48ll << 20) / per_kb : 0;
+    if (pf > p.kblocks_per_split) pf = p.kblocks_per_split;
+    p.prefetch_kb = bspec::pdl_enabled() ? (int)pf : 0;
+  }
   CUtensorMap map_a, map_b;
   const void* a_ptr = p.swap ? W : X;
   const void* b_ptr = p.swap ? X : W;
