@@ -553,6 +553,249 @@ template <int HD> size_t decode_tma_smem() {
   return 1024 + (size_t)TMA_STAGES * 2 * KT * HD * 2 + (size_t)16 * HD * 2 + 2 * TMA_STAGES * 8 + (size_t)TBL_MAX * 4 + 64;
 }
 
+// ------------------------------------------------------------------------------------ prefill, 128 rows, TMA
+// One warp: scores of its 16 rows against all 64 keys of a tile, one online-softmax step, P*V.
+template <int HD, bool TMA_TILE>
+__device__ __forceinline__ void block64(const uint32_t (&qf)[HD / 16][4], const __nv_bfloat16* Ks,
+                                        const __nv_bfloat16* Vs, int key0, int row_lim0, int row_lim1, int row_lo0,
+                                        int row_lo1, int k_end, bool need_mask, float scale_log2, float (&m)[2],
+                                        float (&l)[2], float (&o)[HD / 8][4]) {
+  const int lane = threadIdx.x & 31;
+  const int mat = lane >> 3, r8 = lane & 7;
+  float s[8][4];
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s[nt][i] = 0.f;
+#pragma unroll
+  for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+    for (int np = 0; np < 4; ++np) {
+      uint32_t b[4];
+      ldmatrix_x4(b, Ks + kv_off<HD, TMA_TILE>(16 * np + 8 * (mat >> 1) + r8, 16 * ks + 8 * (mat & 1)));
+      mma_bf16(s[2 * np], qf[ks], b[0], b[1]);
+      mma_bf16(s[2 * np + 1], qf[ks], b[2], b[3]);
+    }
+  }
+  float mx[2] = {-INFINITY, -INFINITY};
+  if (need_mask) {
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int key = key0 + 8 * nt + 2 * (lane & 3) + (i & 1);
+        const int lim = (i >> 1) ? row_lim1 : row_lim0, lo = (i >> 1) ? row_lo1 : row_lo0;
+        const bool ok = key <= lim && key >= lo && key < k_end;
+        s[nt][i] = ok ? s[nt][i] * scale_log2 : -INFINITY;
+        mx[i >> 1] = fmaxf(mx[i >> 1], s[nt][i]);
+      }
+  } else {
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        s[nt][i] *= scale_log2;
+        mx[i >> 1] = fmaxf(mx[i >> 1], s[nt][i]);
+      }
+  }
+  float corr[2], msafe[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+    const float mn = fmaxf(m[r], mx[r]);
+    msafe[r] = (mn == -INFINITY) ? 0.f : mn;
+    corr[r] = exp2f(m[r] - msafe[r]);
+    m[r] = mn;
+    l[r] *= corr[r];
+  }
+  uint32_t pf[4][4];
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      s[nt][i] = exp2f(s[nt][i] - msafe[i >> 1]);
+      l[i >> 1] += s[nt][i];
+    }
+    pf[nt >> 1][2 * (nt & 1)] = pack_bf16(s[nt][0], s[nt][1]);
+    pf[nt >> 1][2 * (nt & 1) + 1] = pack_bf16(s[nt][2], s[nt][3]);
+  }
+#pragma unroll
+  for (int nd = 0; nd < HD / 8; ++nd)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[nd][i] *= corr[i >> 1];
+#pragma unroll
+  for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+    for (int nd = 0; nd < HD / 8; nd += 2) {
+      uint32_t b[4];
+      ldmatrix_x4_trans(b, Vs + kv_off<HD, TMA_TILE>(16 * kk + 8 * (mat & 1) + r8, 8 * (nd + (mat >> 1))));
+      mma_bf16(o[nd], pf[kk], b[0], b[1]);
+      mma_bf16(o[nd + 1], pf[kk], b[2], b[3]);
+    }
+  }
+}
+
+// A CTA owns 128 rows (8 consumer warps x 16) of one (request, kv head) and walks the visible keys in 64-key
+// tiles that a ninth warp fetches with TMA (page sizes 8 / 16 / 32 / 64) into a ring of stages.  Tiles wholly
+// below every row's limit skip the mask; each warp stops at its own last visible tile.
+constexpr int PREFILL_ROWS = 128;
+constexpr int PREFILL_TMA_THREADS = 288;
+constexpr int PREFILL_STAGES = 4;     // one CTA per SM (registers): a deep ring hides the load latency instead
+
+template <int HD>
+__global__ void __launch_bounds__(PREFILL_TMA_THREADS)
+attn_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bfloat16* __restrict__ q,
+                        long long q_row_stride, __nv_bfloat16* __restrict__ out, int* __restrict__ status,
+                        const int* __restrict__ qo_indptr, const int* __restrict__ positions,
+                        const int* __restrict__ kv_indptr, const int* __restrict__ kv_indices, int Hq, int Hkv,
+                        int page_size, float scale_log2, int window, int min_q_long) {
+  bspec::pdl_prologue();
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  constexpr int TILE_ELEMS = KT * HD;
+  __nv_bfloat16* KV = reinterpret_cast<__nv_bfloat16*>(smem);                 // PREFILL_STAGES x (K tile, V tile)
+  __nv_bfloat16* Qs = KV + PREFILL_STAGES * 2 * TILE_ELEMS;                   // [128][HD]
+  uint64_t* full = reinterpret_cast<uint64_t*>(Qs + PREFILL_ROWS * HD);
+  uint64_t* empty = full + PREFILL_STAGES;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + PREFILL_STAGES);
+
+  const int g = blockIdx.y, e = blockIdx.z;
+  TileGeom t;
+  if (!tile_geometry(t, qo_indptr, positions, e, g, Hq, Hkv)) return;
+  if (t.q_len < min_q_long) return;
+  const int n_row_tiles = (t.rows_total + PREFILL_ROWS - 1) / PREFILL_ROWS;
+  if ((int)blockIdx.x >= n_row_tiles) return;
+  const int row0 = (n_row_tiles - 1 - blockIdx.x) * PREFILL_ROWS;             // late (heavy) tiles first
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qi_lo = row0 / t.G, qi_hi = min(t.q_len - 1, (row0 + PREFILL_ROWS - 1) / t.G);
+  const int hi_key = t.pos0 + qi_hi;
+  const int lo_key = window > 0 ? max(0, t.pos0 + qi_lo - window + 1) : 0;
+  const int k_begin = (lo_key / KT) * KT, k_end = hi_key + 1;
+  const int n_tiles = (k_end - k_begin + KT - 1) / KT;
+  const int* table = kv_indices + kv_indptr[e];
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PREFILL_STAGES; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 8);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp == 8) {
+    if (lane == 0) {
+      const int first_pg = lo_key / page_size, last_pg = (k_end - 1) / page_size;
+      const int pages_per_tile = KT / page_size;
+      constexpr uint32_t tile_bytes = 2u * TILE_ELEMS * 2u;
+      for (int it = 0; it < n_tiles; ++it) {
+        const int s = it % PREFILL_STAGES;
+        const uint32_t ph = (uint32_t)(it / PREFILL_STAGES) & 1u;
+        if (!mbar_wait(empty + s, ph ^ 1u, abort_flag, status, 21)) break;
+        __nv_bfloat16* Ks = KV + (size_t)s * 2 * TILE_ELEMS;
+        mbar_expect_tx(full + s, tile_bytes);
+        const int key0 = k_begin + it * KT;
+        for (int pp = 0; pp < pages_per_tile; ++pp) {
+          int pg = (key0 + pp * page_size) / page_size;
+          pg = min(max(pg, first_pg), last_pg);
+          const int page = table[pg];
+          const int row_k = ((page * 2) * Hkv + g) * page_size;
+          const int row_v = row_k + Hkv * page_size;
+#pragma unroll
+          for (int c = 0; c < HD / 64; ++c) {
+            tma_load_2d(Ks + c * (KT * 64) + pp * page_size * 64, &kv_map, full + s, c * 64, row_k);
+            tma_load_2d(Ks + TILE_ELEMS + c * (KT * 64) + pp * page_size * 64, &kv_map, full + s, c * 64, row_v);
+          }
+        }
+      }
+    }
+    return;
+  }
+
+  // ---- consumers: warps 0..7
+  const int wrow0 = row0 + 16 * warp;
+  int lim[2], lo[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = wrow0 + (lane >> 2) + 8 * r;
+    const int qi = row / t.G;
+    lim[r] = row < t.rows_total ? t.pos0 + qi : -1;
+    lo[r] = window > 0 ? max(0, t.pos0 + qi - window + 1) : 0;
+  }
+  const bool warp_live = wrow0 < t.rows_total;
+  const int warp_hi = t.pos0 + min(t.q_len - 1, (wrow0 + 15) / t.G);          // last key any row of the warp sees
+  const int warp_full = t.pos0 + wrow0 / t.G;                                 // keys <= this are seen by all its rows
+  const int warp_lo = window > 0 ? t.pos0 + min(t.q_len - 1, (wrow0 + 15) / t.G) - window + 1 : 0;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+
+  // Q tile: 256 consumer threads load 128 rows
+  {
+    constexpr int CH = HD / 8;
+    for (int idx = threadIdx.x; idx < PREFILL_ROWS * CH; idx += 256) {
+      const int row = idx / CH, ch = idx - row * CH;
+      const int r = row0 + row;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (r < t.rows_total) {
+        const int qi = r / t.G, h = g * t.G + (r - qi * t.G);
+        v = *reinterpret_cast<const uint4*>(q + (size_t)(t.q_begin + qi) * q_row_stride + (size_t)h * HD + ch * 8);
+      }
+      *reinterpret_cast<uint4*>(Qs + row * HD + ((ch ^ (row & 7)) << 3)) = v;
+    }
+  }
+  asm volatile("bar.sync 1, 256;" ::: "memory");
+  uint32_t qf[HD / 16][4];
+  {
+    const int mat = lane >> 3, r8 = lane & 7;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks)
+      ldmatrix_x4(qf[ks], Qs + swz<HD>(16 * warp + 8 * (mat & 1) + r8, 16 * ks + 8 * (mat >> 1)));
+  }
+  for (int it = 0; it < n_tiles; ++it) {
+    const int s = it % PREFILL_STAGES;
+    const uint32_t ph = (uint32_t)(it / PREFILL_STAGES) & 1u;
+    if (!mbar_wait(full + s, ph, abort_flag, status, 22)) break;
+    const __nv_bfloat16* Ks = KV + (size_t)s * 2 * TILE_ELEMS;
+    const int key0 = k_begin + it * KT;
+    if (warp_live && key0 <= warp_hi) {
+      const bool need_mask = key0 + KT - 1 > warp_full || key0 < warp_lo || key0 + KT > k_end;
+      block64<HD, true>(qf, Ks, Ks + TILE_ELEMS, key0, lim[0], lim[1], lo[0], lo[1], k_end, need_mask, scale_log2, m,
+                        l, o);
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty + s);
+  }
+  if (*abort_flag || !warp_live) return;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = wrow0 + (lane >> 2) + 8 * r;
+    if (row >= t.rows_total) continue;
+    const int qi = row / t.G, h = g * t.G + (row - qi * t.G);
+    const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+    __nv_bfloat16* op = out + ((size_t)(t.q_begin + qi) * Hq + h) * HD;
+#pragma unroll
+    for (int nd = 0; nd < HD / 8; ++nd) {
+      const int col = 8 * nd + 2 * (lane & 3);
+      *reinterpret_cast<__nv_bfloat162*>(op + col) = __floats2bfloat162_rn(o[nd][2 * r] * inv, o[nd][2 * r + 1] * inv);
+    }
+  }
+}
+
+template <int HD> size_t prefill_tma_smem() {
+  return 1024 + (size_t)PREFILL_STAGES * 2 * KT * HD * 2 + (size_t)PREFILL_ROWS * HD * 2 + 2 * PREFILL_STAGES * 8 + 64;
+}
+
 // ------------------------------------------------------------------------------------ prefill (64 rows per CTA)
 template <int HD>
 __global__ void __launch_bounds__(NTHREADS)
@@ -670,6 +913,9 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
     cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem<HD>());
     cudaFuncSetAttribute(attn_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_tma_smem<HD>());
     cudaFuncSetAttribute(attn_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_smem<HD>());
+    if constexpr (HD <= 128)
+      cudaFuncSetAttribute(attn_prefill_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)prefill_tma_smem<HD>());
     attr_set = true;
   }
   if (run_decode) {
@@ -695,11 +941,26 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
     if (err) return err;
   }
   if (run_prefill) {
-    dim3 grid((max_q_len * G + 63) / 64, Hkv, n_entries);
-    if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidConfiguration;
-    BSPEC_LAUNCH((attn_prefill_kernel<HD>), grid, NTHREADS, prefill_smem<HD>(), stream, 
-        q, q_row_stride, out, cache, qo_indptr, positions, kv_indptr, kv_indices, Hq, Hkv, page_size, scale_log2,
-        window, max_q_short + 1);
+    if (Hkv > 65535 || n_entries > 65535) return (int)cudaErrorInvalidConfiguration;
+    bool launched = false;
+    if constexpr (HD <= 128) {
+     if (kv_rows > 0 && status != nullptr && page_size % 8 == 0 && KT % page_size == 0) {
+      CUtensorMap kv_map;
+      if (make_map_2d_bf16(&kv_map, cache, kv_rows, HD, page_size, 64)) {
+        dim3 grid((max_q_len * G + PREFILL_ROWS - 1) / PREFILL_ROWS, Hkv, n_entries);
+        BSPEC_LAUNCH((attn_prefill_tma_kernel<HD>), grid, PREFILL_TMA_THREADS, prefill_tma_smem<HD>(), stream, kv_map,
+                     q, q_row_stride, out, status, qo_indptr, positions, kv_indptr, kv_indices, Hq, Hkv, page_size,
+                     scale_log2, window, max_q_short + 1);
+        launched = true;
+      }
+     }
+    }
+    if (!launched) {
+      dim3 grid((max_q_len * G + 63) / 64, Hkv, n_entries);
+      BSPEC_LAUNCH((attn_prefill_kernel<HD>), grid, NTHREADS, prefill_smem<HD>(), stream,
+                   q, q_row_stride, out, cache, qo_indptr, positions, kv_indptr, kv_indices, Hq, Hkv, page_size,
+                   scale_log2, window, max_q_short + 1);
+    }
     return (int)cudaGetLastError();
   }
   return 0;

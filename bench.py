@@ -177,8 +177,9 @@ def run_e2e(eng, cfg, batch, steps, warmup, page_size=16):
     token ids out; returns decode tokens per second over the decode steps and the
     host<->device bytes per decode step."""
     from batchspec_b200.engine import Sequence
+    # token budget of one step = all prompts, so the requests prefill together and then decode in lockstep
     eng.setup_caches(max_batch_size=batch, max_seq_length=PROMPT_LEN + steps + 2, page_size=page_size,
-                     prefill_chunk_size=PROMPT_LEN, max_tokens_per_step=PROMPT_LEN)
+                     prefill_chunk_size=PROMPT_LEN, max_tokens_per_step=batch * PROMPT_LEN)
     eng.ignore_eos = True
     prompts = prompts_for(batch, cfg.vocab_size, 3)
     # warm-up: the same call on the same prompts, a few tokens (loads kernels, captures the decode graph)
