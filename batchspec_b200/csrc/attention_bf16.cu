@@ -313,7 +313,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride, 
                    const int* __restrict__ positions, const int* __restrict__ kv_indptr,
                    const int* __restrict__ kv_indices, int Hq, int Hkv, int page_size, float scale_log2, int window,
                    int n_splits, int row_tiles, int max_q_short) {
-  bspec::pdl_prologue();
+  bspec::pdl_prologue(8);
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);           // [16][HD]
   __nv_bfloat16* KV = Qs + 16 * HD;                                        // 2 stages x (K [KT][HD], V [KT][HD])
@@ -419,6 +419,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
   // The step's metadata (lengths, positions, block tables) was uploaded before the step's first kernel, and every
   // cached key below the first new token was written by earlier steps: the producer may fetch those tiles while
   // the kernel before this one (which writes q and the new tokens' keys and values) is still running.
+  const unsigned long long t_trace = bspec::g_trace_buf != nullptr ? bspec::global_timer() : 0ull;
   bspec::pdl_launch_dependents();
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
@@ -512,6 +513,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
 
   // ---- consumers (threads 0..127)
   bspec::pdl_wait();
+  bspec::trace_record(8, t_trace);
   int lim[2], lo[2];
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -650,7 +652,7 @@ attn_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_b
                         const int* __restrict__ qo_indptr, const int* __restrict__ positions,
                         const int* __restrict__ kv_indptr, const int* __restrict__ kv_indices, int Hq, int Hkv,
                         int page_size, float scale_log2, int window, int min_q_long) {
-  bspec::pdl_prologue();
+  bspec::pdl_prologue(9);
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
   constexpr int TILE_ELEMS = KT * HD;
@@ -804,7 +806,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
                     const int* __restrict__ positions, const int* __restrict__ kv_indptr,
                     const int* __restrict__ kv_indices, int Hq, int Hkv, int page_size, float scale_log2, int window,
                     int min_q_long) {
-  bspec::pdl_prologue();
+  bspec::pdl_prologue(9);
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);           // [64][HD]
   __nv_bfloat16* KV = Qs + 64 * HD;                                        // 2 stages x (K, V)
@@ -1080,3 +1082,5 @@ BSPEC_API int bspec_attention_decode_noalloc(const void* q, long long q_row_stri
   GO(256);
 #undef GO
 }
+
+BSPEC_DEFINE_TRACE_SETTER(bspec_trace_set_attention_bf16)

@@ -22,7 +22,7 @@ attn_generic_kernel(const T* __restrict__ q, long long q_row_stride, T* __restri
                     const int* __restrict__ positions, const int* __restrict__ kv_indptr,
                     const int* __restrict__ kv_indices, int Hq, int Hkv, int hd, int page_size, float scale,
                     int window) {
-  bspec::pdl_prologue();
+  bspec::pdl_prologue(7);
   __shared__ float qs[WARPS][MAX_HD];
   const int e = blockIdx.y, h = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -113,3 +113,5 @@ BSPEC_API int bspec_attention_generic(const void* q, long long q_row_stride, voi
         kv_indptr, kv_indices, Hq, Hkv, hd, page_size, scale, window);
   return BSPEC_LAUNCH_CHECK();
 }
+
+BSPEC_DEFINE_TRACE_SETTER(bspec_trace_set_attention_generic)

@@ -57,9 +57,32 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // before it touches anything the predecessor wrote or may still read.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_prologue() {
+// Optional timeline for tuning: when a trace buffer is set, thread 0 of block 0 of every kernel appends
+// {kernel id, time it started, time its wait on the predecessor returned} (nanoseconds of %globaltimer).
+// Each translation unit has its own copy of these two pointers; BSPEC_DEFINE_TRACE_SETTER exports its setter.
+static __device__ unsigned long long* g_trace_buf = nullptr;   // [capacity][3]
+static __device__ unsigned int* g_trace_cnt = nullptr;         // [2]: {next slot, capacity}
+
+__device__ __forceinline__ unsigned long long global_timer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void trace_record(int kid, unsigned long long t_start) {
+  if (g_trace_buf != nullptr && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+    const unsigned int slot = atomicAdd(g_trace_cnt, 1u);
+    if (slot < g_trace_cnt[1]) {
+      g_trace_buf[3 * slot] = (unsigned long long)kid;
+      g_trace_buf[3 * slot + 1] = t_start;
+      g_trace_buf[3 * slot + 2] = global_timer();
+    }
+  }
+}
+__device__ __forceinline__ void pdl_prologue(int kid = 0) {
+  const unsigned long long t0 = g_trace_buf != nullptr ? global_timer() : 0ull;
   pdl_launch_dependents();
   pdl_wait();
+  trace_record(kid, t0);
 }
 
 inline bool& pdl_enabled() {
@@ -89,3 +112,9 @@ inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
 #define BSPEC_LAUNCH(kernel, grid, block, smem, stream, ...) \
   (void)bspec::launch(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, __VA_ARGS__)
 #define BSPEC_LAUNCH_CHECK() (int)cudaGetLastError()
+#define BSPEC_DEFINE_TRACE_SETTER(name)                                                            \
+  BSPEC_API int name(unsigned long long* buf, unsigned int* cnt) {                                 \
+    cudaError_t e = cudaMemcpyToSymbol(bspec::g_trace_buf, &buf, sizeof(buf));                     \
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(bspec::g_trace_cnt, &cnt, sizeof(cnt));           \
+    return (int)e;                                                                                 \
+  }

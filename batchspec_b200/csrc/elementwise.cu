@@ -10,7 +10,7 @@ using namespace bspec;
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out,
                              int d, int vocab, float scale) {
-  bspec::pdl_prologue();
+  bspec::pdl_prologue(1);
   const int t = blockIdx.x;
   int id = ids[t];
   const bool ok = id >= 0 && id < vocab;
@@ -62,7 +62,7 @@ template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16*
 template <typename TD, typename TO, typename TW, int VPT>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                        const TW* __restrict__ weight, TO* __restrict__ out, int d, float eps) {
-  bspec::pdl_prologue();
+  bspec::pdl_prologue(2);
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * d;
   float x[VPT][4];
@@ -101,7 +101,7 @@ template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                    const void* __restrict__ weight, int w_dtype, TO* __restrict__ out, int d,
                                    float eps) {
-  bspec::pdl_prologue();
+  bspec::pdl_prologue(2);
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * d;
   float ss = 0.f;
@@ -162,7 +162,7 @@ BSPEC_API int bspec_add_rmsnorm(float* resid, const void* delta, int delta_dtype
 template <typename TD>
 __global__ void gather_rows_add_kernel(const float* __restrict__ resid, const TD* __restrict__ pending,
                                        const int* __restrict__ rows, float* __restrict__ out, int d) {
-  bspec::pdl_prologue();
+  bspec::pdl_prologue(3);
   const size_t src = (size_t)rows[blockIdx.x] * d, dst = (size_t)blockIdx.x * d;
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     float v = resid[src + i];
@@ -185,7 +185,7 @@ BSPEC_API int bspec_gather_rows_add(const float* resid, const void* pending, int
 // u [n, 2I] = [gate | up]  ->  m [n, I]
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ u, T* __restrict__ m, int inter, size_t total) {
-  bspec::pdl_prologue();
+  bspec::pdl_prologue(4);
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t row = idx / inter, col = idx - row * inter;
@@ -199,7 +199,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ u, T* __restrict__ m, int 
 // the same, eight bfloat16 per thread (I a multiple of 8)
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ u, __nv_bfloat16* __restrict__ m, int inter,
                                        size_t total8) {
-  bspec::pdl_prologue();
+  bspec::pdl_prologue(4);
   const int inter8 = inter / 8;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8;
        idx += (size_t)gridDim.x * blockDim.x) {
@@ -256,7 +256,7 @@ __global__ void rope_kv_append_kernel(T* __restrict__ qkv, int Hq, int Hkv, int 
                                       const int* __restrict__ tok_entry, const int* __restrict__ kv_indptr,
                                       const int* __restrict__ kv_indices, T* __restrict__ cache, int page_size,
                                       int write_kv) {
-  bspec::pdl_prologue();
+  bspec::pdl_prologue(5);
   extern __shared__ float cs[];  // [rot/2] cos, [rot/2] sin
   const int t = blockIdx.x;
   const int slot0 = blockIdx.y * ROPE_HEADS_PER_BLOCK;          // head slots: q heads, then k heads, then v heads
@@ -350,7 +350,7 @@ template <typename T>
 __global__ void rope_inplace_kernel(T* __restrict__ x, long long row_stride, int H, int hd,
                                     const float* __restrict__ inv_freq, int rot, int interleaved,
                                     const int* __restrict__ positions) {
-  bspec::pdl_prologue();
+  bspec::pdl_prologue(6);
   extern __shared__ float cs[];
   const int t = blockIdx.x, half = rot / 2;
   const int pos = positions[t];
@@ -383,3 +383,5 @@ BSPEC_API int bspec_rope_inplace(void* x, int dtype, int n, long long row_stride
     BSPEC_LAUNCH((rope_inplace_kernel<__nv_bfloat16>), n, 128, smem, stream, (__nv_bfloat16*)x, row_stride, H, hd, inv_freq, rot, interleaved, positions);
   return BSPEC_LAUNCH_CHECK();
 }
+
+BSPEC_DEFINE_TRACE_SETTER(bspec_trace_set_elementwise)

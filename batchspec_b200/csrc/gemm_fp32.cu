@@ -10,7 +10,7 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 __global__ void __launch_bounds__(256)
 sgemm_tn_kernel(const float* __restrict__ A, const float* __restrict__ W, float* __restrict__ C, int M, int N, int K,
                 long long lda, long long ldw, long long ldc) {
-  bspec::pdl_prologue();
+  bspec::pdl_prologue(10);
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -68,3 +68,5 @@ BSPEC_API int bspec_sgemm_tn(const float* A, const float* W, float* C, int M, in
   BSPEC_LAUNCH((sgemm_tn_kernel), grid, 256, 0, stream, A, W, C, M, N, K, lda, ldw, ldc);
   return BSPEC_LAUNCH_CHECK();
 }
+
+BSPEC_DEFINE_TRACE_SETTER(bspec_trace_set_gemm_fp32)

@@ -93,6 +93,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* part = reinterpret_cast<float*>(smem);      // [bn][128] partial tile of this K slice (reuses the stages)
 
+  const unsigned long long t_trace = bspec::g_trace_buf != nullptr ? bspec::global_timer() : 0ull;
   bspec::pdl_launch_dependents();           // the next kernel may start its own prologue and weight prefetch
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile_a = blockIdx.x;            // 128-row tile of the operand on the accumulator rows
@@ -140,6 +141,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         else tma_prefetch_2d(&map_b, (kb0 + i) * BK, tile_b * p.bn);
       }
       bspec::pdl_wait();
+      bspec::trace_record(20, t_trace);
       for (int i = 0; i < pre; ++i) {
         unsigned char* a_dst = smem + (size_t)i * stage_bytes;
         if (p.swap) tma_load_2d(a_dst + a_bytes, &map_b, full + i, (kb0 + i) * BK, tile_b * p.bn);
@@ -279,6 +281,10 @@ size_t smem_bytes(int bn, int stages) {
 }
 }  // namespace
 
+static int g_force_splits = 0;
+// For experiments: force the number of K slices of the weights-on-rows arrangement (0: choose automatically).
+BSPEC_API void bspec_gemm_tc_force_splits(int splits) { g_force_splits = splits > 8 ? 8 : splits; }
+
 // Plan for a product of these sizes: writes {swap, bn, splits, stages, tiles} to plan[5]; returns 0, or -1 if the
 // sizes are not supported (K not a multiple of 8).  `sm_count` is the number of SMs to fill.
 BSPEC_API long long bspec_gemm_tc_plan(int M, int N, int K, int sm_count, int* plan) {
@@ -298,6 +304,7 @@ BSPEC_API long long bspec_gemm_tc_plan(int M, int N, int K, int sm_count, int* p
     if (splits < 1) splits = 1;
     if (splits > kb_total / 8) splits = kb_total / 8 > 0 ? kb_total / 8 : 1;
     if (splits > 8) splits = 8;
+    if (g_force_splits > 0) splits = g_force_splits < kb_total ? g_force_splits : kb_total;
     smem_budget = 108 * 1024;
   } else {
     swap = 0;
@@ -373,3 +380,5 @@ BSPEC_API int bspec_gemm_tc(const void* X, const void* W, void* C, int M, int N,
 
 // Switch programmatic dependent launch on (default) or off for every kernel of this library.
 BSPEC_API void bspec_set_pdl(int on) { bspec::pdl_enabled() = on != 0; }
+
+BSPEC_DEFINE_TRACE_SETTER(bspec_trace_set_gemm_tcgen05)

@@ -78,7 +78,7 @@ __device__ int block_count(int v, int* iscratch) {
 __global__ void __launch_bounds__(THREADS)
 threshold_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
                  const int* __restrict__ top_k, const float* __restrict__ top_p, uint32_t* __restrict__ threshold) {
-  bspec::pdl_prologue();
+  bspec::pdl_prologue(11);
   __shared__ float fscratch[32];
   __shared__ int iscratch[32];
   const int r = blockIdx.x;
@@ -146,7 +146,7 @@ pick_partial_kernel(const float* __restrict__ logits, int vocab, const float* __
                     const uint32_t* __restrict__ threshold, const long long* __restrict__ stream_id,
                     const long long* __restrict__ counter, unsigned long long seed, float* __restrict__ part_v,
                     int* __restrict__ part_i) {
-  bspec::pdl_prologue();
+  bspec::pdl_prologue(12);
   __shared__ ArgBest scratch[32];
   const int r = blockIdx.y, nb = gridDim.x;
   const float* row = logits + (size_t)r * vocab;
@@ -178,7 +178,7 @@ pick_partial_kernel(const float* __restrict__ logits, int vocab, const float* __
 // Stage 3 (one warp per row): best of the slices.
 __global__ void pick_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i, int nb,
                                   int* __restrict__ out) {
-  bspec::pdl_prologue();
+  bspec::pdl_prologue(13);
   const int r = blockIdx.x;
   ArgBest b{-INFINITY, 0x7fffffff};
   for (int i = threadIdx.x; i < nb; i += 32) b = better(b, ArgBest{part_v[r * nb + i], part_i[r * nb + i]});
@@ -222,3 +222,5 @@ BSPEC_API int bspec_sample(const float* logits, int rows, int vocab, const float
   BSPEC_LAUNCH((pick_final_kernel), rows, 32, 0, stream, part_v, part_i, nb, out);
   return BSPEC_LAUNCH_CHECK();
 }
+
+BSPEC_DEFINE_TRACE_SETTER(bspec_trace_set_sampling)

@@ -79,6 +79,9 @@ def load_library():
         _lib = lib
         if os.environ.get("BSPEC_PDL", "1") == "0":
             set_pdl(False)
+        if os.environ.get("BSPEC_GEMM_SPLITS"):
+            lib.bspec_gemm_tc_force_splits.argtypes = [c_int]
+            lib.bspec_gemm_tc_force_splits(int(os.environ["BSPEC_GEMM_SPLITS"]))
     return _lib
 
 
@@ -88,6 +91,25 @@ def set_pdl(on: bool) -> None:
     lib.bspec_set_pdl.argtypes = [c_int]
     lib.bspec_set_pdl.restype = None
     lib.bspec_set_pdl(int(bool(on)))
+
+
+_TRACE_SETTERS = ["bspec_trace_set_elementwise", "bspec_trace_set_attention_generic", "bspec_trace_set_attention_bf16",
+                  "bspec_trace_set_gemm_fp32", "bspec_trace_set_sampling", "bspec_trace_set_gemm_tcgen05"]
+TRACE_KERNEL_NAMES = {1: "embed", 2: "add_rmsnorm", 3: "gather_rows_add", 4: "silu_mul", 5: "rope_kv_append",
+                      6: "rope_inplace", 7: "attn_generic", 8: "attn_decode", 9: "attn_prefill", 10: "sgemm",
+                      11: "sample_threshold", 12: "sample_pick", 13: "sample_final", 20: "gemm_tcgen05"}
+
+
+def set_trace(buf: Optional[torch.Tensor], count: Optional[torch.Tensor]) -> None:
+    """Tuning aid.  ``buf`` int64 [capacity, 3] and ``count`` int32 [2] = {0, capacity} on the device: from now on
+    block 0 of every kernel appends (kernel id, start ns, ns at which its wait on the predecessor returned).
+    ``None`` switches it off.  Set it before capturing a graph that should record."""
+    lib = load_library()
+    for name in _TRACE_SETTERS:
+        fn = getattr(lib, name)
+        fn.argtypes = [c_void_p, c_void_p]
+        fn.restype = c_int
+        _check(fn(_ptr(buf), _ptr(count)), name)
 
 
 def library_file() -> str:
