@@ -78,6 +78,17 @@ __device__ __forceinline__ void trace_record(int kid, unsigned long long t_start
     }
   }
 }
+// a free-form mark from the calling thread of block 0 (phases inside a kernel)
+__device__ __forceinline__ void trace_mark(int kid, unsigned long long t_from) {
+  if (g_trace_buf != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+    const unsigned int slot = atomicAdd(g_trace_cnt, 1u);
+    if (slot < g_trace_cnt[1]) {
+      g_trace_buf[3 * slot] = (unsigned long long)kid;
+      g_trace_buf[3 * slot + 1] = t_from;
+      g_trace_buf[3 * slot + 2] = global_timer();
+    }
+  }
+}
 __device__ __forceinline__ void pdl_prologue(int kid = 0) {
   const unsigned long long t0 = g_trace_buf != nullptr ? global_timer() : 0ull;
   pdl_launch_dependents();

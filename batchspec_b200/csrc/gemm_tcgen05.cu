@@ -192,6 +192,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int row = quad * 32 + lane;                       // accumulator row of this thread
     const bool ok = mbar_wait(acc_full, 0, abort_flag, p.status, 3);
     tc_fence_after();
+    if (threadIdx.x == 64) bspec::trace_mark(21, t_trace);      // accumulator complete
     bspec::pdl_wait();                                      // C may reuse memory the kernel before still reads
     if (ok) {
       const int ra = tile_a * TM + row;                     // global row of the operand on the accumulator rows
@@ -242,28 +243,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tc_fence_before();
     __syncthreads();
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (threadIdx.x == 64) bspec::trace_mark(22, t_trace);      // partial tiles of the cluster visible
     if (warp >= 2 && !*abort_flag) {
       const int row = (warp & 3) * 32 + lane;
       const int ra = tile_a * TM + row;
       if (ra < p.N) {
+        // addresses of this thread's row in every peer's partial tile
+        uint32_t peer[8];
+        const uint32_t mine = s32(part + row);
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+          if (s < p.splits) asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer[s]) : "r"(mine), "r"(s));
         for (int j = split; j < p.bn; j += p.splits) {
           const int tok = tile_b * p.bn + j;
           if (tok >= p.M) break;
-          const uint32_t local = s32(part + (size_t)j * TM + row);
+          const uint32_t off = (uint32_t)j * TM * 4u;
+          float v[8];
+#pragma unroll
+          for (int s = 0; s < 8; ++s)                      // all loads in flight before the first add
+            if (s < p.splits) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[s]) : "r"(peer[s] + off));
           float acc = 0.f;
-          for (int s = 0; s < p.splits; ++s) {
-            uint32_t remote;
-            float v;
-            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(s));
-            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-            acc += v;
-          }
+#pragma unroll
+          for (int s = 0; s < 8; ++s)
+            if (s < p.splits) acc += v[s];                 // slice order
           store_out(p.C, p.out_f32, (size_t)tok * p.N + ra, acc);
         }
       }
     }
+    if (threadIdx.x == 64) bspec::trace_mark(23, t_trace);      // joined and stored
     // nobody leaves while a peer may still read its shared memory
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (threadIdx.x == 64) bspec::trace_mark(24, t_trace);
   }
   tc_fence_before();
   __syncthreads();
@@ -304,6 +314,7 @@ BSPEC_API long long bspec_gemm_tc_plan(int M, int N, int K, int sm_count, int* p
     if (splits < 1) splits = 1;
     if (splits > kb_total / 8) splits = kb_total / 8 > 0 ? kb_total / 8 : 1;
     if (splits > 8) splits = 8;
+    while (splits & (splits - 1)) --splits;               // clusters of 1, 2, 4 or 8 schedule best (measured: 6 is slow)
     if (g_force_splits > 0) splits = g_force_splits < kb_total ? g_force_splits : kb_total;
     smem_budget = 108 * 1024;
   } else {
