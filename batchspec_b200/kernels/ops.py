@@ -53,6 +53,9 @@ _SIGNATURES = {
                              c_int, c_int, c_int, c_int, c_void_p],
     "bspec_gemm_tc_plan": [c_int, c_int, c_int, c_int, c_void_p],
     "bspec_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+    "bspec_attention_prefill_tc": [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                                   c_void_p],
     "bspec_sgemm_tn": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p],
     "bspec_pick_slices": [c_int],
     "bspec_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -93,11 +96,11 @@ def set_pdl(on: bool) -> None:
     lib.bspec_set_pdl(int(bool(on)))
 
 
-_TRACE_SETTERS = ["bspec_trace_set_elementwise", "bspec_trace_set_attention_generic", "bspec_trace_set_attention_bf16",
+_TRACE_SETTERS = ["bspec_trace_set_attention_tcgen05", "bspec_trace_set_elementwise", "bspec_trace_set_attention_generic", "bspec_trace_set_attention_bf16",
                   "bspec_trace_set_gemm_fp32", "bspec_trace_set_sampling", "bspec_trace_set_gemm_tcgen05"]
 TRACE_KERNEL_NAMES = {1: "embed", 2: "add_rmsnorm", 3: "gather_rows_add", 4: "silu_mul", 5: "rope_kv_append",
                       6: "rope_inplace", 7: "attn_generic", 8: "attn_decode", 9: "attn_prefill", 10: "sgemm",
-                      11: "sample_threshold", 12: "sample_pick", 13: "sample_final", 20: "gemm_tcgen05"}
+                      11: "sample_threshold", 12: "sample_pick", 13: "sample_final", 20: "gemm_tcgen05", 30: "attn_prefill_tc"}
 
 
 def set_trace(buf: Optional[torch.Tensor], count: Optional[torch.Tensor]) -> None:
@@ -227,6 +230,7 @@ def rope_inplace(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tenso
 # ---------------------------------------------------------------------------- attention
 
 USE_TMA_ATTENTION = os.environ.get("BSPEC_TMA_ATTENTION", "1") != "0"
+USE_TC_ATTENTION = os.environ.get("BSPEC_TC_ATTENTION", "1") != "0"    # tcgen05 kernel for long prompt portions
 FORCE_GENERIC_ATTENTION = False      # tests set this to compare the tensor-core kernels with the generic one
 _SM_COUNT = 148
 
@@ -293,6 +297,16 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, c
             counters = _counters(qkv.device, ctx.n_entries * n_kv_heads * row_tiles)
         run_decode = int(ctx.extras.get("min_q_len", 1) <= short)
         run_prefill = int(ctx.max_q_len > short)
+        if run_prefill and tma and USE_TC_ATTENTION and head_dim == 128:
+            # long portions on the tcgen05 kernel; what is left for the call below are the short requests
+            _check(lib.bspec_attention_prefill_tc(
+                qkv.data_ptr(), qkv.stride(0), out.data_ptr(), _status_word(qkv.device).data_ptr(), cache.shape[0],
+                cache.data_ptr(), ctx.qo_indptr.data_ptr(), ctx.positions.data_ptr(), tables.kv_indptr.data_ptr(),
+                tables.kv_indices.data_ptr(), ctx.n_entries, ctx.max_q_len, n_heads, n_kv_heads, head_dim,
+                tables.page_size, float(scale), int(window), short + 1, _stream()), "attention_prefill_tc")
+            run_prefill = 0
+            if not run_decode:
+                return
         _check(lib.bspec_attention_bf16(
             qkv.data_ptr(), qkv.stride(0), out.data_ptr(), _ptr(o_part), _ptr(ml_part), _ptr(counters),
             _status_word(qkv.device).data_ptr(), cache.shape[0] if tma else 0, cache.data_ptr(),

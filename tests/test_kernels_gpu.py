@@ -221,6 +221,11 @@ ATT_SHAPES = [
     (5, 5, 128, 32, [9, 200], [77, 200]),
     (4, 1, 256, 16, [1, 40], [150, 90]),
     (40, 2, 64, 16, [1, 2], [100, 65]),                # 20 query heads per kv head: more than one 16-row tile
+    (32, 8, 128, 16, [300], [300]),                    # head_dim 128, long portions: the tcgen05 kernel
+    (32, 8, 128, 16, [128, 257, 1], [1000, 257, 90]),
+    (8, 8, 128, 64, [100], [700]),
+    (16, 2, 128, 8, [33, 500], [33, 777]),
+    (6, 2, 128, 32, [129], [385]),                     # 3 query heads per kv head: rows do not align with tokens
 ]
 
 
