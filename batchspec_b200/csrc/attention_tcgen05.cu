@@ -62,6 +62,11 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&v)[32])
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float ex2(float x) {          // 2^x on the special-function unit; 2^-inf = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // K-major operand tile: rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
@@ -205,6 +210,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
             tc_mma(tmem_s[b], qdesc + off, kdesc + off, id_s, ks > 0 ? 1u : 0u);
           }
           tc_commit(s_full + b);
+          if (j < 6) bspec::trace_mark(130 + j, 0ull);                           // S_j issued
         }
         if (j >= 1) {
           // O += P_{j-1} V_{j-1}
@@ -219,6 +225,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
             const uint64_t b_off = (uint64_t)(kk * ((16 * 128) >> 4));                        // 16 keys = 16 rows of V
             tc_mma(tmem_o, pdesc + a_off, vdesc + b_off, id_o, (jj > 0 || kk > 0) ? 1u : 0u);
           }
+          if (jj < 6) bspec::trace_mark(140 + jj, 0ull);                         // PV_jj issued
           tc_commit(kv_empty + st);       // K_{j-1} and V_{j-1} are no longer read
           tc_commit(pv_done);             // O holds tiles 0..j-1, P may be overwritten
         }
@@ -249,60 +256,64 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
       __syncwarp();
       if (lane == 0) mbar_arrive(q_ready);
     }
-    float m = -INFINITY, l = 0.f;
+    // m_ref: the maximum the probabilities and O are currently scaled by.  It follows the true running maximum
+    // lazily: O and l are rescaled only when the maximum has grown by more than 8 (a factor 256, harmless in
+    // float32 and bfloat16), which after the first tiles is rare.
+    float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int b = j & 1;
+      const unsigned long long t_a = (bspec::g_trace_buf != nullptr && j < 6) ? bspec::global_timer() : 0ull;
       ok = mbar_wait(s_full + b, (uint32_t)(j >> 1) & 1u, abort_flag, status, 36);
       if (!ok) break;
       tc_fence_after();
+      if (threadIdx.x == 64 && j < 6) bspec::trace_mark(100 + j, t_a);          // waited for S_j
       const int key0 = k_begin + j * KT;
       const bool need_mask = key0 + KT - 1 > lim || key0 < lo || key0 + KT > k_end;
-      // pass 1: row maximum
+      // the whole S row into registers, then the S buffer is free for tile j + 2
+      uint32_t sv[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tc_ld32(tmem_s[b] + lane_addr + 32u * c, sv[c]);
+      tc_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_read + b);
       float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tc_ld32(tmem_s[b] + lane_addr + 32u * c, v);
-        tc_wait_ld();
+      for (int c = 0; c < 4; ++c)
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(v[i]) * scale_log2;
+          float sc = __uint_as_float(sv[c][i]) * scale_log2;
           if (need_mask) {
             const int key = key0 + 32 * c + i;
-            if (!(key <= lim && key >= lo && key < k_end)) s = -INFINITY;
+            if (!(key <= lim && key >= lo && key < k_end)) sc = -INFINITY;
           }
-          mx = fmaxf(mx, s);
+          sv[c][i] = __float_as_uint(sc);
+          mx = fmaxf(mx, sc);
         }
+      float corr = 1.f;
+      if (mx > m_ref + 8.f || m_ref == -INFINITY) {           // (also the first tile that holds a visible key)
+        const float m_new = fmaxf(m_ref, mx);
+        corr = (m_new == -INFINITY) ? 1.f : ex2(m_ref - m_new);   // m_ref = -inf: O and l are still 0
+        m_ref = m_new;
+        l *= corr;
       }
-      const float m_new = fmaxf(m, mx);
-      const float msafe = (m_new == -INFINITY) ? 0.f : m_new;
-      const float corr = exp2f(m - msafe);
-      m = m_new;
-      l *= corr;
+      const float msafe = (m_ref == -INFINITY) ? 0.f : m_ref;
       // P may be overwritten, and O rescaled, only after the previous P V has completed
+      const unsigned long long t_b = (bspec::g_trace_buf != nullptr && j < 6) ? bspec::global_timer() : 0ull;
       if (j >= 1) {
         ok = mbar_wait(pv_done, (uint32_t)(j - 1) & 1u, abort_flag, status, 37);
         if (!ok) break;
         tc_fence_after();
       }
-      // pass 2: probabilities -> P in shared memory (bfloat16, operand layout)
+      if (threadIdx.x == 64 && j < 6) bspec::trace_mark(110 + j, t_b);          // (max done) waited for PV_{j-1}
       unsigned char* pdst = reinterpret_cast<unsigned char*>(Ps);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tc_ld32(tmem_s[b] + lane_addr + 32u * c, v);
-        tc_wait_ld();
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float s0 = __uint_as_float(v[i]) * scale_log2, s1 = __uint_as_float(v[i + 1]) * scale_log2;
-          if (need_mask) {
-            const int key = key0 + 32 * c + i;
-            if (!(key <= lim && key >= lo && key < k_end)) s0 = -INFINITY;
-            if (!(key + 1 <= lim && key + 1 >= lo && key + 1 < k_end)) s1 = -INFINITY;
-          }
-          const float p0 = exp2f(s0 - msafe), p1 = exp2f(s1 - msafe);
+          const float p0 = ex2(__uint_as_float(sv[c][i]) - msafe), p1 = ex2(__uint_as_float(sv[c][i + 1]) - msafe);
           l += p0 + p1;
           __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
           packed[i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
@@ -312,11 +323,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
           *reinterpret_cast<uint4*>(pdst + chunk_off(row, 4 * c + k4)) =
               make_uint4(packed[4 * k4], packed[4 * k4 + 1], packed[4 * k4 + 2], packed[4 * k4 + 3]);
       }
-      // S buffer b has been read twice: the MMA warp may overwrite it with tile j + 2
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_read + b);
-      // rescale this row of O if the maximum moved (whole warp decides together: the TMEM access is warp-wide)
+      // rescale this row of O if its scale moved (the warp decides together: the TMEM access is warp-wide)
       if (j >= 1 && __any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -333,6 +340,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_ready);
+      if (threadIdx.x == 64 && j < 6) bspec::trace_mark(120 + j, t_b);          // P written, arrived
     }
     // the last P V
     if (ok && n_tiles > 0) ok = mbar_wait(pv_done, (uint32_t)(n_tiles - 1) & 1u, abort_flag, status, 38);
