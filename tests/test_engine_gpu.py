@@ -276,6 +276,21 @@ def test_command_line_entry_point(tmp_path):
     assert summary["step_ms"]["count"] >= 6 and "attn.compute" in summary["buckets_ms"]
 
 
+def test_benchmark_entry_point(tmp_path):
+    cfgj, seed, page = H.TINY["C"]
+    folder = H.make_folder(tmp_path / "m", cfgj, seed, dtype=torch.bfloat16)
+    cmd = [sys.executable, "-m", "batchspec_b200.run_benchmark", "--checkpoint_path", str(folder), "--batch_size", "4",
+           "--prefix_len_list", "24", "70", "--max_gen_len", "10", "--num_total_runs", "3", "--temperature", "0.6",
+           "--top_k", "20", "--top_p", "0.95", "--force_budget", "--profiling", "--model_profiling", "false",
+           "--prof_output_dir", str(tmp_path / "prof")]
+    r = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "prefix 24:" in r.stdout and "prefix 70:" in r.stdout
+    for prefix in (24, 70):
+        summary = json.loads((tmp_path / "prof" / f"bench-bsz4-prefix{prefix}-gen10" / "summary.json").read_text())
+        assert summary["throughput_tok_s"] > 0 and summary["runs"] == 3 and summary["warmup_runs"] == 1
+
+
 # ------------------------------------------------------------------ a toy mixer with state, registered from the test
 
 def test_a_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
