@@ -182,30 +182,37 @@ BSPEC_API int bspec_gather_rows_add(const float* resid, const void* pending, int
 }
 
 // ---------------------------------------------------------------- SiLU(gate) * up
-// u [n, 2I] = [gate | up]  ->  m [n, I]
+// u [n, 2I] -> m [n, I].  group = 0: u = [gate | up] (two halves);  group = G > 0: u comes in blocks of 2G columns,
+// G gate columns followed by their G up columns (the layout of the fused-epilogue GEMM's weights).
+__device__ __forceinline__ size_t gate_col(size_t col, int inter, int group) {
+  return group > 0 ? (col / group) * 2 * group + (col % group) : col;
+}
+__device__ __forceinline__ size_t up_col(size_t col, int inter, int group) {
+  return group > 0 ? (col / group) * 2 * group + group + (col % group) : inter + col;
+}
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ u, T* __restrict__ m, int inter, size_t total) {
+__global__ void silu_mul_kernel(const T* __restrict__ u, T* __restrict__ m, int inter, size_t total, int group) {
   bspec::pdl_prologue(4);
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t row = idx / inter, col = idx - row * inter;
-    const float g = to_f32(u[row * 2 * inter + col]);
-    const float up = to_f32(u[row * 2 * inter + inter + col]);
+    const float g = to_f32(u[row * 2 * inter + gate_col(col, inter, group)]);
+    const float up = to_f32(u[row * 2 * inter + up_col(col, inter, group)]);
     const float s = g / (1.f + expf(-g));
     m[idx] = from_f32<T>(s * up);
   }
 }
 
-// the same, eight bfloat16 per thread (I a multiple of 8)
+// the same, eight bfloat16 per thread (I, and the group if any, multiples of 8)
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ u, __nv_bfloat16* __restrict__ m, int inter,
-                                       size_t total8) {
+                                       size_t total8, int group) {
   bspec::pdl_prologue(4);
   const int inter8 = inter / 8;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t row = idx / inter8, c8 = idx - row * inter8;
-    const uint4 gv = *reinterpret_cast<const uint4*>(u + row * 2 * inter + c8 * 8);
-    const uint4 uv = *reinterpret_cast<const uint4*>(u + row * 2 * inter + inter + c8 * 8);
+    const uint4 gv = *reinterpret_cast<const uint4*>(u + row * 2 * inter + gate_col(c8 * 8, inter, group));
+    const uint4 uv = *reinterpret_cast<const uint4*>(u + row * 2 * inter + up_col(c8 * 8, inter, group));
     const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
     const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
     uint4 ov;
@@ -220,25 +227,26 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ u, __nv
   }
 }
 
-BSPEC_API int bspec_silu_mul(const void* u, void* m, int dtype, int n, int inter, cudaStream_t stream) {
+BSPEC_API int bspec_silu_mul(const void* u, void* m, int dtype, int n, int inter, int group, cudaStream_t stream) {
   const size_t total = (size_t)n * inter;
   if (total == 0) return 0;
   const int threads = 256;
-  if (dtype == BSPEC_BF16 && inter % 8 == 0) {
+  if (group < 0 || (group > 0 && inter % group != 0)) return (int)cudaErrorInvalidValue;
+  if (dtype == BSPEC_BF16 && inter % 8 == 0 && group % 8 == 0) {
     const size_t total8 = total / 8;
     size_t want = (total8 + threads - 1) / threads;
     const int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
     BSPEC_LAUNCH((silu_mul_bf16x8_kernel), blocks, threads, 0, stream, (const __nv_bfloat16*)u, (__nv_bfloat16*)m,
-                 inter, total8);
+                 inter, total8, group);
     return BSPEC_LAUNCH_CHECK();
   }
   size_t want = (total + threads - 1) / threads;
   const int blocks = (int)(want > 148 * 32 ? 148 * 32 : want);
   if (dtype == BSPEC_F32)
-    BSPEC_LAUNCH((silu_mul_kernel<float>), blocks, threads, 0, stream, (const float*)u, (float*)m, inter, total);
+    BSPEC_LAUNCH((silu_mul_kernel<float>), blocks, threads, 0, stream, (const float*)u, (float*)m, inter, total, group);
   else
     BSPEC_LAUNCH((silu_mul_kernel<__nv_bfloat16>), blocks, threads, 0, stream, (const __nv_bfloat16*)u,
-                 (__nv_bfloat16*)m, inter, total);
+                 (__nv_bfloat16*)m, inter, total, group);
   return BSPEC_LAUNCH_CHECK();
 }
 

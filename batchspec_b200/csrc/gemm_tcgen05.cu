@@ -72,6 +72,7 @@ struct GemmParams {
   int splits;
   int kblocks_per_split;
   int stages;
+  int glu;               // rows of W come in groups of 128 = 64 gate rows + their 64 up rows; C[M, N/2] = silu(gate) * up
   int prefetch_kb;       // K blocks of weights (beyond the stages) to pull into the L2 before waiting on the predecessor
 };
 
@@ -200,7 +201,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         uint32_t v[16];
         tc_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
         tc_wait_ld();
-        if (!p.swap) {
+        if (!p.swap && p.glu) {
+          // rows = tokens, columns = outputs in groups of 64 gate + 64 up: this chunk of gate columns and its partner
+          if ((c0 & 64) == 0) {
+            uint32_t vu[16];
+            tc_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c0 + 64), vu);
+            tc_wait_ld();
+            const int n0 = tile_b * p.bn + c0;                       // gate column; output column below
+            const int o0 = (n0 >> 7) * 64 + (n0 & 63);
+            if (ra < p.M) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (n0 + j < p.N) {
+                  const float gte = __uint_as_float(v[j]);
+                  store_out(p.C, p.out_f32, (size_t)ra * (p.N / 2) + o0 + j,
+                            gte / (1.f + expf(-gte)) * __uint_as_float(vu[j]));
+                }
+            }
+          }
+        } else if (!p.swap) {
           // rows = tokens (ra < M), columns = outputs
           if (ra < p.M) {
             const int n0 = tile_b * p.bn + c0;
@@ -221,7 +240,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (n0 + j < p.N) store_out(p.C, p.out_f32, base + j, __uint_as_float(v[j]));
             }
           }
-        } else if (p.splits == 1) {
+        } else if (p.splits == 1 && !p.glu) {
           // rows = outputs (ra < N), columns = tokens: consecutive lanes write consecutive outputs of one token
           if (ra < p.N) {
 #pragma unroll
@@ -238,17 +257,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     }
   }
-  if (p.swap && p.splits > 1) {
+  if (p.swap && (p.splits > 1 || p.glu)) {
     // join the K slices inside the cluster: CTA r adds tokens r, r + splits, ... over all slices in slice order
     tc_fence_before();
     __syncthreads();
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (p.splits > 1)
+      asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     if (threadIdx.x == 64) bspec::trace_mark(22, t_trace);      // partial tiles of the cluster visible
     if (warp >= 2 && !*abort_flag) {
       const int row = (warp & 3) * 32 + lane;
-      const int ra = tile_a * TM + row;
-      if (ra < p.N) {
-        // addresses of this thread's row in every peer's partial tile
+      // plain: this thread owns output row `row` of the tile.  glu: threads 0..63 own gate row `row` and up row
+      // `row + 64` and produce output tile_a * 64 + row of the N / 2 outputs.
+      const bool active = p.glu ? row < 64 : true;
+      const int ra = p.glu ? tile_a * 64 + row : tile_a * TM + row;
+      const int n_out = p.glu ? p.N / 2 : p.N;
+      if (active && ra < n_out) {
+        // addresses of this thread's row(s) in every peer's partial tile
         uint32_t peer[8];
         const uint32_t mine = s32(part + row);
 #pragma unroll
@@ -258,21 +282,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const int tok = tile_b * p.bn + j;
           if (tok >= p.M) break;
           const uint32_t off = (uint32_t)j * TM * 4u;
-          float v[8];
+          float v[8], u[8];
 #pragma unroll
           for (int s = 0; s < 8; ++s)                      // all loads in flight before the first add
-            if (s < p.splits) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[s]) : "r"(peer[s] + off));
-          float acc = 0.f;
+            if (s < p.splits) {
+              asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[s]) : "r"(peer[s] + off));
+              if (p.glu) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(u[s]) : "r"(peer[s] + off + 256u));
+            }
+          float acc = 0.f, acc_u = 0.f;
 #pragma unroll
           for (int s = 0; s < 8; ++s)
-            if (s < p.splits) acc += v[s];                 // slice order
-          store_out(p.C, p.out_f32, (size_t)tok * p.N + ra, acc);
+            if (s < p.splits) {                            // slice order
+              acc += v[s];
+              if (p.glu) acc_u += u[s];
+            }
+          if (p.glu) acc = acc / (1.f + expf(-acc)) * acc_u;
+          store_out(p.C, p.out_f32, (size_t)tok * n_out + ra, acc);
         }
       }
     }
     if (threadIdx.x == 64) bspec::trace_mark(23, t_trace);      // joined and stored
     // nobody leaves while a peer may still read its shared memory
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (p.splits > 1)
+      asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     if (threadIdx.x == 64) bspec::trace_mark(24, t_trace);
   }
   tc_fence_before();
@@ -337,13 +369,17 @@ BSPEC_API long long bspec_gemm_tc_plan(int M, int N, int K, int sm_count, int* p
 }
 
 // C = X W^T.  `status`: one int on the device, 0 unless a bounded wait ran out.
-BSPEC_API int bspec_gemm_tc(const void* X, const void* W, void* C, int M, int N, int K, int out_f32, int* status,
-                            int sm_count, cudaStream_t stream) {
+// glu != 0: the rows of W come in groups of 128 (64 gate rows, then the 64 matching up rows; N a multiple of 128) and
+// C is [M, N/2] = silu(gate) * up.
+BSPEC_API int bspec_gemm_tc(const void* X, const void* W, void* C, int M, int N, int K, int out_f32, int glu,
+                            int* status, int sm_count, cudaStream_t stream) {
   int plan[5];
   if (bspec_gemm_tc_plan(M, N, K, sm_count, plan) < 0) return (int)cudaErrorInvalidValue;
+  if (glu && (N % 128 != 0)) return (int)cudaErrorInvalidValue;
+  if (glu && !plan[0] && plan[1] < 128) plan[1] = 128;     // a gate/up group must lie inside one tile
   GemmParams p;
   p.C = C; p.status = status;
-  p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32;
+  p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.glu = glu ? 1 : 0;
   p.swap = plan[0]; p.bn = plan[1]; p.splits = plan[2]; p.stages = plan[3];
   const int kb_total = (K + BK - 1) / BK;
   p.kblocks_per_split = (kb_total + p.splits - 1) / p.splits;

@@ -42,7 +42,7 @@ _SIGNATURES = {
     "bspec_embed": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
     "bspec_add_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
     "bspec_gather_rows_add": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
-    "bspec_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "bspec_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "bspec_rope_kv_append": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "bspec_rope_inplace": [c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p],
@@ -52,7 +52,7 @@ _SIGNATURES = {
                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                              c_int, c_int, c_int, c_int, c_void_p],
     "bspec_gemm_tc_plan": [c_int, c_int, c_int, c_int, c_void_p],
-    "bspec_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+    "bspec_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
     "bspec_attention_prefill_tc": [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                                    c_void_p],
@@ -187,12 +187,42 @@ def gather_rows_add(resid: torch.Tensor, pending: Optional[torch.Tensor], rows: 
                                                 out.shape[0], out.shape[1], _stream()), "gather_rows_add")
 
 
-def silu_mul(u: torch.Tensor, out: torch.Tensor) -> None:
+GLU_GROUP = 64     # gate/up interleave of weights prepared for the fused-epilogue GEMM: 64 gate rows, 64 up rows
+
+
+def silu_mul(u: torch.Tensor, out: torch.Tensor, group: int = 0) -> None:
+    """out = silu(gate) * up.  ``group`` 0: u = [gate | up]; G > 0: blocks of G gate columns and their G up columns."""
     _require_cuda(u, out)
     n, inter = out.shape
     assert u.shape == (n, 2 * inter) and u.dtype == out.dtype and u.is_contiguous() and out.is_contiguous()
-    _check(load_library().bspec_silu_mul(u.data_ptr(), out.data_ptr(), _dtype_code(u.dtype), n, inter, _stream()),
-           "silu_mul")
+    _check(load_library().bspec_silu_mul(u.data_ptr(), out.data_ptr(), _dtype_code(u.dtype), n, inter, int(group),
+                                         _stream()), "silu_mul")
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, group: int = GLU_GROUP) -> torch.Tensor:
+    """[I, d] gate and up rows -> [2I, d] in blocks of ``group`` gate rows followed by their up rows."""
+    inter, d = gate.shape
+    assert inter % group == 0 and up.shape == gate.shape
+    return torch.stack([gate.view(inter // group, group, d), up.view(inter // group, group, d)], dim=1).reshape(2 * inter, d).contiguous()
+
+
+def linear_glu(x: torch.Tensor, w13: torch.Tensor, group: int = GLU_GROUP) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) for bfloat16 with ``w13`` interleaved by ``interleave_gate_up``: one kernel with the
+    activation in the GEMM's epilogue for decode-sized steps, vendor GEMM + activation kernel otherwise."""
+    _require_cuda(x, w13)
+    M, K = x.shape
+    N = w13.shape[0]
+    inter = N // 2
+    if (x.dtype == torch.bfloat16 and K % 8 == 0 and M > 0 and group == GLU_GROUP and x.is_contiguous()
+            and (TC_GEMM == "all" or (TC_GEMM == "auto" and M <= TC_GEMM_MAX_M))):
+        out = torch.empty((M, inter), dtype=x.dtype, device=x.device)
+        _check(load_library().bspec_gemm_tc(x.data_ptr(), w13.data_ptr(), out.data_ptr(), M, N, K, 0, 1,
+                                            _status_word(x.device).data_ptr(), _SM_COUNT, _stream()), "gemm_tc_glu")
+        return out
+    u = linear(x, w13)
+    out = torch.empty((M, inter), dtype=x.dtype, device=x.device)
+    silu_mul(u, out, group)
+    return out
 
 
 def rope_kv_append(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
@@ -362,7 +392,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.T
     if K % 8 != 0 or M <= 0:
         raise KernelError(f"gemm_tc: sizes M={M} N={N} K={K} are not supported (K must be a multiple of 8)")
     out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-    _check(lib.bspec_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, int(out_dtype == torch.float32),
+    _check(lib.bspec_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, int(out_dtype == torch.float32), 0,
                              _status_word(x.device).data_ptr(), _SM_COUNT, _stream()), "gemm_tc")
     return out
 

@@ -336,6 +336,45 @@ def test_tcgen05_gemm(ops, M, N, K, out_dtype):
     assert torch.equal(got, again)
 
 
+@pytest.mark.parametrize("M,I,K", [(1, 64, 64), (8, 14336, 4096), (5, 192, 72), (64, 256, 96), (128, 128, 264),
+                                   (300, 320, 128), (2048, 1024, 512)])
+def test_gate_up_gemm_with_the_activation_in_its_epilogue(ops, M, I, K):
+    g = torch.Generator(device=DEV).manual_seed(M + I)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    wg = (torch.randn(I, K, device=DEV, generator=g) / K ** 0.5).bfloat16()
+    wu = (torch.randn(I, K, device=DEV, generator=g) / K ** 0.5).bfloat16()
+    w13 = ops.interleave_gate_up(wg, wu)
+    assert torch.equal(w13[:64], wg[:64]) and torch.equal(w13[64:128], wu[:64])
+    got = ops.linear_glu(x, w13)
+    torch.cuda.synchronize()
+    ops.check_status()
+    gate, up = x.float() @ wg.float().T, x.float() @ wu.float().T
+    want = gate * torch.sigmoid(gate) * up
+    assert got.shape == (M, I)
+    torch.testing.assert_close(got.float(), want, rtol=3e-2, atol=3e-2)
+    for mode in ("all", "none"):                      # both the fused epilogue and GEMM + activation kernel
+        old, ops.TC_GEMM = ops.TC_GEMM, mode
+        try:
+            torch.testing.assert_close(ops.linear_glu(x, w13).float(), want, rtol=3e-2, atol=3e-2)
+        finally:
+            ops.TC_GEMM = old
+    ops.check_status()
+
+
+def test_silu_mul_layouts(ops):
+    g = torch.Generator(device=DEV).manual_seed(3)
+    for dtype in (torch.float32, torch.bfloat16):
+        gate = (torch.randn(7, 192, device=DEV, generator=g) * 3).to(dtype)
+        up = torch.randn(7, 192, device=DEV, generator=g).to(dtype)
+        want = (gate.float() * torch.sigmoid(gate.float()) * up.float()).to(dtype)
+        halves = torch.cat([gate, up], dim=1).contiguous()
+        grouped = torch.stack([gate.view(7, 3, 64), up.view(7, 3, 64)], dim=2).reshape(7, 384).contiguous()
+        for u, group in ((halves, 0), (grouped, 64)):
+            out = torch.empty(7, 192, device=DEV, dtype=dtype)
+            ops.silu_mul(u, out, group)
+            torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+
+
 def test_tcgen05_gemm_rejects_what_it_cannot_do(ops):
     x = torch.zeros(4, 20, device=DEV, dtype=torch.bfloat16)
     w = torch.zeros(8, 20, device=DEV, dtype=torch.bfloat16)
