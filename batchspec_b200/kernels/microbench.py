@@ -60,12 +60,14 @@ class Timer:
         return statistics.median(ts)
 
 
-def bench_gemms(cfg, ms, timer, pk, dev):
+def bench_gemms(cfg, ms, timer, pk, dev, only=None):
     d, I, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
     q, kv = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
     shapes = [("qkv", q + 2 * kv, d), ("o", d, q), ("gate_up", 2 * I, d), ("down", d, I), ("lm_head", V, d)]
     print(f"{'gemm':8s} {'M':>5s} {'N':>7s} {'K':>6s} | {'tcgen05 ms':>10s} {'GB/s':>7s} {'TF/s':>7s} | {'library ms':>10s} {'GB/s':>7s} {'TF/s':>7s} | frac(tc) of {pk['source']} peak")
     for name, N, K in shapes:
+        if only and name not in only:
+            continue
         w = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
         for M in ms:
             if name == "lm_head" and M > 256:
@@ -148,6 +150,8 @@ def main():
     ap.add_argument("--config", default="llama-3-8b")
     ap.add_argument("--what", nargs="+", default=["gemm", "attention", "small"], choices=["gemm", "attention", "small"])
     ap.add_argument("--m", nargs="+", type=int, default=[1, 8, 64, 2048])
+    ap.add_argument("--gemm-only", nargs="+", choices=["qkv", "o", "gate_up", "down", "lm_head"],
+                    help="time only these projections")
     ap.add_argument("--attn-case", nargs=3, type=int, action="append", metavar=("BATCH", "Q_LEN", "KV_LEN"),
                     help="attention case(s) to time instead of the built-in list")
     a = ap.parse_args()
@@ -159,7 +163,7 @@ def main():
     print(f"peaks ({pk['source']}): {pk['hbm_gbs']:.0f} GB/s, {pk['bf16_tflops']:.0f} TFLOP/s bf16")
     with torch.inference_mode():
         if "gemm" in a.what:
-            bench_gemms(cfg, a.m, timer, pk, dev)
+            bench_gemms(cfg, a.m, timer, pk, dev, only=a.gemm_only)
         if "attention" in a.what:
             bench_attention(cfg, timer, pk, dev, cases=[tuple(c) for c in a.attn_case] if a.attn_case else None)
         if "small" in a.what:

@@ -187,6 +187,7 @@ def gather_rows_add(resid: torch.Tensor, pending: Optional[torch.Tensor], rows: 
                                                 out.shape[0], out.shape[1], _stream()), "gather_rows_add")
 
 
+GLU_FUSION = os.environ.get("BSPEC_GLU_FUSION", "1") != "0"
 GLU_GROUP = 64     # gate/up interleave of weights prepared for the fused-epilogue GEMM: 64 gate rows, 64 up rows
 
 
@@ -213,8 +214,8 @@ def linear_glu(x: torch.Tensor, w13: torch.Tensor, group: int = GLU_GROUP) -> to
     M, K = x.shape
     N = w13.shape[0]
     inter = N // 2
-    if (x.dtype == torch.bfloat16 and K % 8 == 0 and M > 0 and group == GLU_GROUP and x.is_contiguous()
-            and (TC_GEMM == "all" or (TC_GEMM == "auto" and M <= TC_GEMM_MAX_M))):
+    if (GLU_FUSION and x.dtype == torch.bfloat16 and K % 8 == 0 and M > 0 and group == GLU_GROUP
+            and x.is_contiguous() and (TC_GEMM == "all" or (TC_GEMM == "auto" and M <= TC_GEMM_MAX_M))):
         out = torch.empty((M, inter), dtype=x.dtype, device=x.device)
         _check(load_library().bspec_gemm_tc(x.data_ptr(), w13.data_ptr(), out.data_ptr(), M, N, K, 0, 1,
                                             _status_word(x.device).data_ptr(), _SM_COUNT, _stream()), "gemm_tc_glu")
