@@ -30,6 +30,15 @@ TINY_C = dict(
     num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2, head_dim=64, intermediate_size=208,
     rms_norm_eps=3e-6, rope_theta=50000.0, rope_scaling=dict(rope_type="linear", factor=2.0),
     max_position_embeddings=512, tie_word_embeddings=False)
+# One layer with the layer sizes of Llama-3-8B (the vocabulary cut down so that the oracle stays fast): the sizes
+# at which the tensor-core kernels, and not their generic fallbacks, run.
+WIDE = dict(
+    architectures=["LlamaForCausalLM"], model_type="llama", hidden_act="silu", vocab_size=2048, hidden_size=4096,
+    num_hidden_layers=1, num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=14336,
+    rms_norm_eps=1e-5, rope_theta=500000.0,
+    rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                      original_max_position_embeddings=8192),
+    max_position_embeddings=8192, tie_word_embeddings=False)
 TINY = {"A": (TINY_A, 0, 4), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 16)}     # config, seed, page size
 
 

@@ -89,3 +89,25 @@ def test_trace_run_program(tmp_path, dtype):
     got = H.run_trace_subprocess(folder, dtype, steps, tmp_path / "out", max_tokens)
     H.compare_with_oracle(got, folder, reqs, dtype)
     assert len(got) == sum(len(t) for t in reqs.values())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_layer_sizes_of_the_8b_model(tmp_path, dtype):
+    """One layer at Llama-3-8B's sizes (hidden 4096, 32/8 heads of 128, intermediate 14336), page 16: whole, tail
+    decoded, portions and a mixed schedule.  In bfloat16 this is where the tcgen05 GEMM (with the activation in
+    its epilogue), the tcgen05 attention for long portions and the TMA split-key decode attention run inside the
+    engine."""
+    stored = torch.float32 if dtype == "float32" else torch.bfloat16
+    folder = H.make_folder(tmp_path / "wide", H.WIDE, 5, dtype=stored, std=0.02, norm_std=0.1)
+    reqs = {"w0": H.random_tokens(300, 2048, 1), "w1": H.random_tokens(70, 2048, 2), "w2": H.random_tokens(150, 2048, 3)}
+    eng = _engine(folder, dtype, 16, 40, max_requests=3)
+    got = H.run_steps_in_process(eng, H.whole("w0", reqs["w0"]))
+    H.compare_with_oracle(got, folder, {"w0": reqs["w0"]}, dtype)
+    got = H.run_steps_in_process(eng, H.tail_decoded("w1", reqs["w1"], tail=32))
+    H.compare_with_oracle(got, folder, {"w1": reqs["w1"]}, dtype)
+    got = H.run_steps_in_process(eng, H.portions("w2", reqs["w2"], [40, 2, 70, 3, 20, 15]))
+    H.compare_with_oracle(got, folder, {"w2": reqs["w2"]}, dtype)
+    steps = H.mixed(reqs, seed=9, max_live=3, sizes=(64, 1, 2, 100, 1, 33, 1, 1))
+    eng2 = _engine(folder, dtype, 16, H.max_live_tokens(steps, 16) // 16, max_requests=3)
+    got = H.run_steps_in_process(eng2, steps)
+    H.compare_with_oracle(got, folder, reqs, dtype)
