@@ -62,6 +62,8 @@ class E2EArguments:
     num_questions_in_prompt: int = field(default=1, metadata={"help": "Accepted for compatibility; synthetic prompts ignore it."})
     num_total_runs: int = field(default=11, metadata={"help": "Accepted for compatibility."})
     num_prompts: Optional[int] = field(default=None, metadata={"help": "How many synthetic prompts (default: batch_size)."})
+    prefix_len_range: List[int] = field(default_factory=list, metadata={"help": "LO HI: synthetic prompt lengths uniform in [LO, HI] instead of --prefix_len."})
+    gen_len_range: List[int] = field(default_factory=list, metadata={"help": "LO HI: per-request token budgets uniform in [LO, HI] instead of --max_gen_len."})
 
 
 @dataclass
@@ -128,5 +130,7 @@ def parse_benchmark_args(argv=None) -> SimpleNamespace:
 def parse_e2e_args(argv=None) -> SimpleNamespace:
     args = _parse((CommonArguments, E2EArguments, SamplingArguments, ProfilerArguments), argv,
                   "batchspec_b200.run_e2e")
-    args.max_len = args.prefix_len + args.max_gen_len          # args.py:299 of the reference
+    longest_prompt = args.prefix_len_range[1] if args.prefix_len_range else args.prefix_len
+    longest_gen = args.gen_len_range[1] if args.gen_len_range else args.max_gen_len
+    args.max_len = longest_prompt + longest_gen                # args.py:299 of the reference: prefix_len + max_gen_len
     return args

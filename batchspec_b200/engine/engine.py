@@ -220,6 +220,7 @@ class Engine:
         steps = tokens_in = 0
         dec_steps = dec_tokens = dec_h2d = dec_d2h = 0
         dec_seconds = 0.0
+        step_ms = []
         prof = get_active_profiler()
         while not sched.is_done():
             t_step = time.perf_counter()
@@ -249,6 +250,7 @@ class Engine:
             if self.tracer is not None:
                 self.tracer.on_update(steps, sched, work, toks)
             steps += 1
+            step_ms.append((time.perf_counter() - t_step) * 1e3)
             tokens_in += sum(w.n_tokens for w in work)
             if len(wanting) == len(work) and all(w.n_tokens == 1 for w in work):      # a pure decode step
                 dec_steps += 1
@@ -258,7 +260,7 @@ class Engine:
                 dec_d2h += 4 * len(work)
         self.last_stats = dict(steps=steps, tokens_fed=tokens_in, preemptions=sched.num_preemptions,
                                generated=sum(len(s.output_ids) for s in sched.completed),
-                               decode_steps=dec_steps, decode_tokens=dec_tokens, decode_seconds=dec_seconds,
+                               step_ms=step_ms, decode_steps=dec_steps, decode_tokens=dec_tokens, decode_seconds=dec_seconds,
                                decode_h2d_bytes_per_step=dec_h2d // max(dec_steps, 1),
                                decode_d2h_bytes_per_step=dec_d2h // max(dec_steps, 1))
         return sched.completed

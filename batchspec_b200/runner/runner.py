@@ -73,8 +73,16 @@ class Runner:
 
     def run_e2e(self) -> List[Sequence]:
         a = self.args
-        prompts = self._prompts(a.num_prompts or a.batch_size, a.prefix_len, a.seed)
-        seqs = [Sequence(seq_id=i, prompt_ids=p, max_new_tokens=a.max_gen_len) for i, p in enumerate(prompts)]
+        n = a.num_prompts or a.batch_size
+        rng = random.Random(a.seed + 1)
+        if a.dataset == "synthetic" and a.prefix_len_range:
+            lo, hi = a.prefix_len_range
+            vocab = self.engine.config.vocab_size
+            prompts = [[rng.randrange(vocab) for _ in range(rng.randint(lo, hi))] for _ in range(n)]
+        else:
+            prompts = self._prompts(n, a.prefix_len, a.seed)
+        budgets = [rng.randint(*a.gen_len_range) if a.gen_len_range else a.max_gen_len for _ in prompts]
+        seqs = [Sequence(seq_id=i, prompt_ids=p, max_new_tokens=b) for i, (p, b) in enumerate(zip(prompts, budgets))]
         prof = get_active_profiler()
         prof.begin_run()
         torch.cuda.synchronize()
@@ -89,7 +97,14 @@ class Runner:
         print(f"Total generated tokens: {st['generated']}")
         print(f"Total model steps: {st['steps']} (batch_size: {a.batch_size}, preemptions: {st['preemptions']})")
         print(f"Mean generated tokens per step: {st['generated'] / max(st['steps'], 1):.2f}")
-        print(f"Wall time: {dt:.3f} s  ({st['generated'] / dt:.1f} generated tok/s, prompts included)")
+        print(f"Wall time: {dt:.3f} s  ({st['generated'] / dt:.1f} generated tok/s, prompts included; "
+              f"{(st['generated'] + st['tokens_fed']) / dt:.1f} processed tok/s)")
+        ms = sorted(st["step_ms"])
+        if ms:
+            pct = lambda q: ms[min(len(ms) - 1, int(q * len(ms)))]
+            print(f"Step wall time ms: p50 {pct(0.5):.2f}  p90 {pct(0.9):.2f}  p99 {pct(0.99):.2f}  max {ms[-1]:.2f}")
+        print("Pages: " + ", ".join(f"group {i}: high water {g.pool.high_water} of {g.pool.num_pages}"
+                                    for i, g in enumerate(self.engine.cache.groups)))
         return done
 
     def run_benchmark(self, prefix_len: int) -> dict:
