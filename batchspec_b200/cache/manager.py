@@ -29,12 +29,16 @@ class OutOfPages(RuntimeError):
 
 class PagePool:
     """Free list of page ids 0..num_pages-1.  ``allocate`` pops, ``free`` pushes;
-    both check that no page is handed out twice or returned twice."""
+    both check that no page is handed out twice or returned twice.  ``reserved``
+    extra ids (num_pages .. num_pages+reserved-1) exist in the page tensor but are
+    never handed out: the engine uses one as a scratch page for the padding rows of
+    captured decode steps."""
 
-    def __init__(self, num_pages: int):
+    def __init__(self, num_pages: int, reserved: int = 0):
         if num_pages <= 0:
             raise ValueError("a page pool needs at least one page")
         self.num_pages = int(num_pages)
+        self.reserved = int(reserved)
         self._free: List[int] = list(range(self.num_pages - 1, -1, -1))
         self._held = [False] * self.num_pages
         self.high_water = 0
@@ -123,7 +127,7 @@ class CacheManager:
     group).  ``allocate=False`` keeps the bookkeeping only (tests, planning)."""
 
     def __init__(self, needs, page_size: int, num_pages, max_requests: int, dtype: torch.dtype, device,
-                 allocate: bool = True):
+                 allocate: bool = True, scratch_page: bool = False):
         from ..models.decoder import LayerCache
         self.page_size = int(page_size)
         if self.page_size <= 0:
@@ -142,7 +146,7 @@ class CacheManager:
             if key not in key_to_group:
                 key_to_group[key] = len(self.groups)
                 n = num_pages[len(self.groups)] if isinstance(num_pages, (list, tuple)) else num_pages
-                self.groups.append(CacheGroup(need.cache, self.page_size, PagePool(n)))
+                self.groups.append(CacheGroup(need.cache, self.page_size, PagePool(n, reserved=int(scratch_page))))
             g = key_to_group[key]
             run_group[e] = (g, len(self.groups[g].runs))
             self.groups[g].runs.append(e)
@@ -150,7 +154,8 @@ class CacheManager:
             for grp in self.groups:
                 # zeroed once: kernels may load (and mask) rows of a page that no token has been written to yet,
                 # and those must not hold NaN or infinity
-                grp.pages = torch.zeros((len(grp.runs), grp.pool.num_pages, 2, self.page_size * grp.entry_elems),
+                grp.pages = torch.zeros((len(grp.runs), grp.pool.num_pages + grp.pool.reserved, 2,
+                                         self.page_size * grp.entry_elems),
                                         dtype=dtype, device=device)
         self.state_tensors: List[Optional[torch.Tensor]] = []
         self.layer_caches: List[Optional[LayerCache]] = []
@@ -169,6 +174,13 @@ class CacheManager:
                 self.layer_caches.append(None)
             else:
                 self.layer_caches.append(LayerCache(kv=kv, group=g, state=state, owner=need.cache_from is None))
+
+    def scratch_pages(self) -> Optional[List[int]]:
+        """Per group, the id of the page that no request ever holds (None if the
+        manager was made without one)."""
+        if not all(g.pool.reserved for g in self.groups):
+            return None
+        return [g.pool.num_pages for g in self.groups]
 
     # -- requests ---------------------------------------------------------------
     def admit(self, req_id) -> RequestCache:

@@ -99,21 +99,43 @@ class DecodeGraph:
             h_positions=None, extras={"min_q_len": 1, "captured": True})
 
     # -- host side -------------------------------------------------------------------
+    _PAD = object()        # marks a table row that currently points at the scratch page
+
     def _fill(self, req_ids: Sequence, tokens: Optional[Sequence[int]], temperature, top_k, top_p, stream_ids,
               counters) -> None:
         cache, off, B, P, m = self.engine.cache, self.off, self.B, self.P, self.meta
+        n = len(req_ids)
         reqs = [cache.requests[r] for r in req_ids]
-        lengths = np.fromiter((rc.length for rc in reqs), dtype=np.int32, count=B)
+        # rows n .. B-1 are padding: one token at position 0 of the scratch page, greedy, result ignored
+        lengths = np.zeros(B, dtype=np.int32)
+        lengths[:n] = [rc.length for rc in reqs]
+
+        def put(name, values, view=None, width=1):
+            dst = m[off[name]:off[name] + width * B]
+            if view is not None:
+                dst = dst.view(view)
+            dst[:n] = values
+            dst[n:] = 0
+
         if tokens is not None:
-            m[off["token_ids"]:off["token_ids"] + B] = tokens
+            put("token_ids", tokens)
         m[off["positions"]:off["positions"] + B] = lengths
         m[off["kv_len"]:off["kv_len"] + B] = lengths + 1
-        m[off["state_slots"]:off["state_slots"] + B] = [rc.slot for rc in reqs]
-        m[off["top_k"]:off["top_k"] + B] = top_k
-        m[off["temperature"]:off["temperature"] + B].view(np.float32)[:] = temperature
-        m[off["top_p"]:off["top_p"] + B].view(np.float32)[:] = top_p
-        m[off["stream_id"]:off["stream_id"] + 2 * B].view(np.int64)[:] = stream_ids
-        m[off["counter"]:off["counter"] + 2 * B].view(np.int64)[:] = counters
+        put("state_slots", [rc.slot for rc in reqs])
+        put("top_k", top_k)
+        put("temperature", temperature, np.float32)
+        put("top_p", top_p, np.float32)
+        put("stream_id", stream_ids, np.int64, 2)
+        put("counter", counters, np.int64, 2)
+        if n < B:
+            scratch = cache.scratch_pages()
+            for i in range(n, B):
+                if self.row_req[i] is not self._PAD:
+                    for g, page in enumerate(scratch):
+                        m[off[f"kv_indices{g}"] + i * P] = page
+                        self.row_pages[i][g] = 0
+                    self.row_req[i] = self._PAD
+                    self.tables_dirty = True
         for i, (rid, rc) in enumerate(zip(req_ids, reqs)):
             fresh = self.row_req[i] != rid
             for g, table in enumerate(rc.tables):
@@ -162,8 +184,9 @@ class DecodeGraph:
             counters) -> torch.Tensor:
         """One decode step of ``req_ids`` (pages already reserved).  ``tokens`` None:
         the ids chosen by the previous run are still on the device and are used.
-        Returns the chosen tokens, int32 [B] on the device (valid until the next run)."""
-        assert len(req_ids) == self.B
+        Fewer requests than the graph's batch size are padded (see ``_fill``).
+        Returns the chosen tokens, int32 [len(req_ids)] on the device (valid until the next run)."""
+        assert len(req_ids) == self.B or (len(req_ids) < self.B and self.engine.cache.scratch_pages() is not None)
         self._fill(req_ids, tokens, temperature, top_k, top_p, stream_ids, counters)
         self._upload(with_tokens=tokens is not None)
         self.uses += 1
@@ -172,12 +195,11 @@ class DecodeGraph:
             self._forward()                                                      # this step runs eagerly
             self.kernels_per_replay = ops.launch_count() - before
             result = self.next_tokens
-            if self.uses >= 2:
-                self._capture()
-            return result
+            self._capture()
+            return result[:len(req_ids)]
         self.graph.replay()
         ops.count_launches(self.kernels_per_replay)
-        return self.next_tokens
+        return self.next_tokens[:len(req_ids)]
 
     def _capture(self) -> None:
         """Capture the step for later replays.  Nothing runs during capture; the

@@ -116,7 +116,7 @@ class Engine:
         self.prefill_chunk_size = int(prefill_chunk_size)
         self.max_tokens_per_step = int(max_tokens_per_step or max(prefill_chunk_size, max_batch_size))
         self.cache = CacheManager(self.model.cache_needs(), page_size, num_pages, max_batch_size, self.dtype,
-                                  self.device)
+                                  self.device, scratch_page=True)
         self.model.attach_caches(self.cache.layer_caches)
         self._graphs = {}
         self.runner = StepRunner(self.model, self.cache, self.model.spec.vocab_size, self.device)
@@ -140,11 +140,19 @@ class Engine:
         prof = get_active_profiler()
         if prof.active and getattr(prof, "model_profiling", False):
             return None                       # per-kernel buckets need the kernels launched one by one
-        if batch not in self._graphs:
+        # one graph per bucket of batch sizes (1, 2, 4, 8, 16, 24, ...): smaller steps are padded with rows that
+        # write to, and attend over, the cache's scratch page
+        bucket = batch
+        if self.cache.scratch_pages() is not None:
+            bucket = 1
+            while bucket < batch:
+                bucket = bucket * 2 if bucket < 8 else bucket + 8
+            bucket = max(batch, min(bucket, self.max_batch_size))
+        if bucket not in self._graphs:
             from .decode_graph import DecodeGraph
             max_pages = -(-self.max_seq_length // self.page_size)
-            self._graphs[batch] = DecodeGraph(self, batch, max_pages, self.max_seq_length)
-        return self._graphs[batch]
+            self._graphs[bucket] = DecodeGraph(self, bucket, max_pages, self.max_seq_length)
+        return self._graphs[bucket]
 
     def decode_session(self, req_ids, first_tokens):
         """A device-resident greedy decode loop over live requests (see DecodeSession)."""
