@@ -19,6 +19,8 @@
 #include "common.cuh"
 #include "tma.cuh"
 #include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
 using namespace bspec;
 
 namespace {
@@ -555,6 +557,481 @@ template <int HD> size_t decode_tma_smem() {
   return 1024 + (size_t)TMA_STAGES * 2 * KT * HD * 2 + (size_t)16 * HD * 2 + 2 * TMA_STAGES * 8 + (size_t)TBL_MAX * 4 + 64;
 }
 
+// ------------------------------------------------------------------------------------ decode, equal shares
+// The same work as attn_decode_tma_kernel, cut differently.  All 64-key tiles of the launch form one sequence
+// (request by request, kv head by kv head, row tile by row tile, keys in order), and CTA b of R takes the tiles
+// [b T / R, (b + 1) T / R): every CTA streams the same number of tiles however different the requests' lengths are,
+// and its producer warp fetches the next piece's keys while the consumers still finish the last one.  A (request,
+// kv head, row tile) that lies inside one CTA's share is written at once; one that is spread over several CTAs
+// leaves one partial result per CTA, and the CTA that announces the last of them (a counter per row tile, reset
+// by that CTA) joins them in their order.  The cut depends only on the lengths of this launch's requests, so a
+// captured launch follows each replay's lengths.
+constexpr int BAL_MAX_ENTRIES = 512;   // requests of a launch (their tile counts are scanned in shared memory)
+constexpr int BAL_TBL = 512;           // block-table entries of a piece kept in shared memory
+constexpr int BAL_MIN_SHARE = 2;       // tiles: fewer CTAs take part rather than shares below this
+
+// What all CTAs (and the join) agree on: tiles before each request, the tiles in all, the CTAs that take part.
+struct Shares {
+  const int* cum;        // [n_entries + 1], tiles of a request = (cum[e + 1] - cum[e]) for ALL its kv heads and row tiles
+  long long total;
+  int ctas;
+  __device__ __forceinline__ long long start_of(int b) const { return (long long)b * total / ctas; }
+  __device__ __forceinline__ int cta_of(long long p) const { return (int)(((p + 1) * ctas - 1) / total); }
+};
+
+struct Piece {
+  TileGeom t;
+  int e, g, rt, row0, k_begin, k_end, n_tiles, lo_key;
+  int part, n_parts;     // which partial result of the row tile this is, of how many (1: written at once)
+  int tiles_taken;       // tiles of the sequence this piece covers (>= n_tiles: masked tiles are not fetched)
+};
+
+// The piece that starts at position `pos` of the sequence and ends with its row tile or with the CTA's share.
+__device__ __forceinline__ void piece_at(Piece& pc, long long pos, long long share_end, int b, const Shares& sh,
+                                         const int* pos0_of, const int* rows_of, int n_entries, int Hq, int Hkv,
+                                         int row_tiles, int window) {
+  int lo = 0, hi = n_entries;                    // largest e with cum[e] <= pos
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (sh.cum[mid] <= pos) lo = mid; else hi = mid;
+  }
+  const int e = lo;
+  const int tiles_e = (sh.cum[e + 1] - sh.cum[e]) / (Hkv * row_tiles);
+  const int rel = (int)(pos - sh.cum[e]);
+  const int pair = rel / tiles_e, t0 = rel - pair * tiles_e;
+  const int t1 = (int)min((long long)tiles_e, t0 + (share_end - pos));
+  pc.tiles_taken = t1 - t0;
+  pc.e = e;
+  pc.g = pair / row_tiles;
+  pc.rt = pair - pc.g * row_tiles;
+  const long long pair_start = sh.cum[e] + (long long)pair * tiles_e;
+  const int first = sh.cta_of(pair_start);
+  pc.n_parts = sh.cta_of(pair_start + tiles_e - 1) - first + 1;
+  pc.part = b - first;
+  TileGeom& t = pc.t;
+  t.e = e;
+  t.g = pc.g;
+  t.q_begin = rows_of[e] & ((1 << 26) - 1);
+  t.q_len = rows_of[e] >> 26;
+  t.pos0 = pos0_of[e];
+  t.G = Hq / Hkv;
+  t.rows_total = t.q_len * t.G;
+  pc.row0 = pc.rt * 16;
+  pc.n_tiles = 0;
+  pc.k_begin = pc.k_end = pc.lo_key = 0;
+  if (pc.row0 >= t.rows_total) return;
+  const int qi_lo = pc.row0 / t.G, qi_hi = min(t.q_len - 1, (pc.row0 + 15) / t.G);
+  const int hi_key = t.pos0 + qi_hi;
+  pc.lo_key = window > 0 ? max(0, t.pos0 + qi_lo - window + 1) : 0;
+  const int lo_entry = window > 0 ? max(0, t.pos0 - window + 1) : 0;      // the request's tiles start here
+  const int lo_al = (lo_entry / KT) * KT;
+  pc.k_begin = lo_al + t0 * KT;
+  pc.k_end = min(hi_key + 1, lo_al + t1 * KT);
+  if (pc.k_begin < pc.k_end && pc.lo_key < pc.k_end) pc.n_tiles = (pc.k_end - pc.k_begin + KT - 1) / KT;
+}
+
+// Tiles per request and their running sum (all threads of the CTA call this); also every request's first position
+// (pos0_of) and its first row with its number of new tokens (rows_of: q_begin | q_len << 26; q_len <= 16).
+// Returns false if the launch has no tiles at all.
+__device__ __forceinline__ bool make_shares(Shares& sh, int* cum, int* pos0_of, int* rows_of, int* red, int n_entries,
+                                            const int* __restrict__ qo_indptr, const int* __restrict__ positions,
+                                            const int* __restrict__ kv_len, int Hkv, int row_tiles, int window,
+                                            int max_parts, int max_q_short, int n_threads, int grid) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int most = 0, fewest = 0x7fffffff, live = 0;
+  for (int e = threadIdx.x; e < n_entries; e += n_threads) {
+    const int qb = qo_indptr[e], ql = qo_indptr[e + 1] - qb;
+    const int len_after = kv_len != nullptr ? kv_len[e] : 0;     // asked for together with the two loads above
+    int tiles = 0, pos0 = 0;
+    if (ql > 0 && ql <= max_q_short) {
+      pos0 = kv_len != nullptr ? len_after - ql : positions[qb];
+      const int lo_entry = window > 0 ? max(0, pos0 - window + 1) : 0;
+      tiles = (pos0 + ql - (lo_entry / KT) * KT + KT - 1) / KT;
+    }
+    pos0_of[e] = pos0;
+    rows_of[e] = qb | (tiles > 0 ? ql << 26 : 0);
+    cum[e + 1] = tiles * Hkv * row_tiles;
+    most = max(most, tiles);
+    if (tiles > 0) {
+      fewest = min(fewest, tiles);
+      ++live;
+    }
+  }
+  if (threadIdx.x == 0) { cum[0] = 0; red[0] = 0; red[1] = 0x7fffffff; red[2] = 0; }
+  __syncthreads();
+  atomicMax(&red[0], most);
+  atomicMin(&red[1], fewest);
+  if (live) atomicAdd(&red[2], live);
+  if (warp == 0) {                       // inclusive scan, 32 requests at a time
+    int carry = 0;
+    for (int base = 0; base < n_entries; base += 32) {
+      int v = base + lane < n_entries ? cum[base + lane + 1] : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += y;
+      }
+      if (base + lane < n_entries) cum[base + lane + 1] = v + carry;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+  }
+  __syncthreads();
+  sh.cum = cum;
+  sh.total = cum[n_entries];
+  if (sh.total <= 0) return false;
+  // a row tile of `most` tiles must not be spread over more than max_parts shares
+  const int least = max(BAL_MIN_SHARE, (red[0] + max_parts - 3) / (max_parts - 2));
+  sh.ctas = (int)max(1ll, min((long long)grid, sh.total / least));
+  // Requests of one length, and fewer row tiles than CTAs: give every row tile the same whole number of CTAs, so
+  // that no share reaches into the next row tile (a second piece costs a CTA about as much as four tiles).
+  const long long pairs = (long long)red[2] * Hkv * row_tiles;
+  if (red[0] == red[1] && pairs <= sh.ctas) {
+    const int per_pair = (int)min((long long)sh.ctas / pairs, (long long)max(1, red[0] / least));
+    const long long aligned = pairs * per_pair;
+    // tiles a CTA streams either way; a share that reaches into a second row tile pays for about four more
+    if (sh.total / aligned <= sh.total / sh.ctas + 4) sh.ctas = (int)aligned;
+  }
+  return true;
+}
+
+// Joins the n_parts partial results of one row tile (in their order, so the result does not depend on which CTA
+// does it).  Called by the 128 consumer threads; Wt: 64 * 16 + 16 floats of shared memory.
+template <int HD>
+__device__ __forceinline__ void join_parts(float* Wt, __nv_bfloat16* __restrict__ out, const float* __restrict__ o_part,
+                                           const float* __restrict__ ml_part, int e, int g, int row0, int q_begin,
+                                           int rows_total, int G, int Hq, int n_parts, int max_parts, int rows_pe) {
+  const int nrows = min(16, rows_total - row0);
+  float* Inv = Wt + 64 * 16;
+  {
+    // weights of the partial results: 8 threads per row, each with the parts sp = j, j + 8, ... (at most 8 of 64)
+    const int row = threadIdx.x >> 3, j8 = threadIdx.x & 7;
+    const bool live = row < nrows;
+    const int r = row0 + (live ? row : 0), qi = r / G, h = g * G + (r - qi * G);
+    const size_t ph = (size_t)(e * rows_pe + qi) * Hq + h;
+    float ms[8], ls[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int sp = j8 + 8 * u;
+      const bool in = live && sp < n_parts;
+      ms[u] = in ? __ldcg(ml_part + (ph * max_parts + sp) * 2) : -INFINITY;
+      ls[u] = in ? __ldcg(ml_part + (ph * max_parts + sp) * 2 + 1) : 0.f;
+    }
+    float mt = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) mt = fmaxf(mt, ms[u]);
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, o));
+    float lt = 0.f;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int sp = j8 + 8 * u;
+      const float f = (ms[u] == -INFINITY) ? 0.f : exp2f(ms[u] - mt);
+      if (live && sp < n_parts) Wt[sp * 16 + row] = f;
+      lt += ls[u] * f;
+    }
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) lt += __shfl_xor_sync(0xffffffffu, lt, o);
+    if (live && j8 == 0) Inv[row] = lt > 0.f ? 1.f / lt : 0.f;
+  }
+  bar_consumers();
+  for (int idx = threadIdx.x; idx < nrows * (HD / 4); idx += NTHREADS) {
+    const int row = idx / (HD / 4), c4 = idx - row * (HD / 4);
+    const int r = row0 + row, qi = r / G, h = g * G + (r - qi * G);
+    const float* src = o_part + ((size_t)(e * rows_pe + qi) * Hq + h) * max_parts * HD + 4 * c4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    int sp = 0;
+    for (; sp + 4 <= n_parts; sp += 4) {                  // four loads in flight; the order of the sum is fixed
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(sp + u) * HD));
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float f = Wt[(sp + u) * 16 + row];
+        acc.x += v[u].x * f; acc.y += v[u].y * f; acc.z += v[u].z * f; acc.w += v[u].w * f;
+      }
+    }
+    for (; sp < n_parts; ++sp) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (size_t)sp * HD));
+      const float f = Wt[sp * 16 + row];
+      acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
+    }
+    const float inv = Inv[row];
+    uint2 packed;
+    packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+    packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(out + ((size_t)(q_begin + qi) * Hq + h) * HD + 4 * c4) = packed;
+  }
+  bar_consumers();
+}
+
+template <int HD>
+__global__ void __launch_bounds__(DECODE_TMA_THREADS)
+attn_decode_shares_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bfloat16* __restrict__ q,
+                          long long q_row_stride, __nv_bfloat16* __restrict__ out, float* __restrict__ o_part,
+                          float* __restrict__ ml_part, int* __restrict__ tile_counters, int* __restrict__ status,
+                          const int* __restrict__ qo_indptr, const int* __restrict__ positions,
+                          const int* __restrict__ kv_len,
+                          const int* __restrict__ kv_indptr, const int* __restrict__ kv_indices, int n_entries, int Hq,
+                          int Hkv, int page_size, float scale_log2, int window, int max_parts, int rows_pe,
+                          int row_tiles, int max_q_short) {
+  // Lengths, positions and block tables were uploaded before the step's first kernel, and every cached key below
+  // the first new token was written by earlier steps: all of that may be read, and those tiles fetched, while the
+  // kernel before this one (which writes q and the new tokens' keys and values) still runs.
+  const unsigned long long t_trace = bspec::g_trace_buf != nullptr ? bspec::global_timer() : 0ull;
+  bspec::pdl_launch_dependents();
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  constexpr int TILE_ELEMS = KT * HD;
+  __nv_bfloat16* KV = reinterpret_cast<__nv_bfloat16*>(smem);                // TMA_STAGES x (K tile, V tile)
+  __nv_bfloat16* Qs = KV + TMA_STAGES * 2 * TILE_ELEMS;                      // [16][HD]
+  uint64_t* full = reinterpret_cast<uint64_t*>(Qs + 16 * HD);
+  uint64_t* empty = full + TMA_STAGES;
+  float* MsLs = reinterpret_cast<float*>(empty + TMA_STAGES);                // [224] the combine's small arrays
+  int* cum = reinterpret_cast<int*>(MsLs + 224);                             // [BAL_MAX_ENTRIES + 1]
+  int* pos0_of = cum + BAL_MAX_ENTRIES + 1;                                  // [BAL_MAX_ENTRIES]
+  int* rows_of = pos0_of + BAL_MAX_ENTRIES;                                  // [BAL_MAX_ENTRIES]
+  int* tbl = rows_of + BAL_MAX_ENTRIES;                                      // [BAL_TBL]
+  int* red = tbl + BAL_TBL;                                                  // [3]
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(red + 3);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TMA_STAGES; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 4);          // one arrival per consumer warp
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  Shares sh;
+  if (!make_shares(sh, cum, pos0_of, rows_of, red, n_entries, qo_indptr, positions, kv_len, Hkv, row_tiles, window, max_parts,
+                   max_q_short, DECODE_TMA_THREADS, gridDim.x))
+    return;
+  const int b = blockIdx.x;
+  if (b >= sh.ctas) return;
+  const long long share_begin = sh.start_of(b), share_end = sh.start_of(b + 1);
+  uint32_t tile_no = 0;                  // tiles this CTA has been through: stage and phase follow from it
+
+  if (warp == 4) {
+    // ---- producer: one lane issues every copy
+    bool waited = false, ok = true;
+    for (long long pos = share_begin; pos < share_end && ok;) {
+      Piece pc;
+      piece_at(pc, pos, share_end, b, sh, pos0_of, rows_of, n_entries, Hq, Hkv, row_tiles, window);
+      pos += pc.tiles_taken;
+      if (pc.n_tiles == 0) continue;
+      const int* table = kv_indices + kv_indptr[pc.e];
+      const int first_pg = max(pc.k_begin, pc.lo_key) / page_size, last_pg = (pc.k_end - 1) / page_size;
+      const int n_pg = last_pg - first_pg + 1;
+      const bool in_smem = n_pg <= BAL_TBL;
+      __syncwarp();
+      if (in_smem)
+        for (int i = lane; i < n_pg; i += 32) tbl[i] = table[first_pg + i];
+      __syncwarp();
+      if (lane == 0) {
+        const int pages_per_tile = KT / page_size;
+        constexpr uint32_t tile_bytes = 2u * TILE_ELEMS * 2u;
+        for (int k = 0; k < pc.n_tiles; ++k, ++tile_no) {
+          const int s = tile_no % TMA_STAGES;
+          const uint32_t ph = (tile_no / TMA_STAGES) & 1u;
+          if (!waited && (tile_no >= TMA_STAGES || pc.k_begin + (k + 1) * KT > pc.t.pos0)) {
+            bspec::pdl_wait();           // this tile holds new keys, or a stage must first be released by consumers
+            waited = true;
+          }
+          if (!mbar_wait(empty + s, ph ^ 1u, abort_flag, status, 13)) { ok = false; break; }
+          __nv_bfloat16* Ks = KV + (size_t)s * 2 * TILE_ELEMS;
+          mbar_expect_tx(full + s, tile_bytes);
+          const int key0 = pc.k_begin + k * KT;
+          for (int pp = 0; pp < pages_per_tile; ++pp) {
+            int pg = (key0 + pp * page_size) / page_size;
+            pg = min(max(pg, first_pg), last_pg);
+            const int page = in_smem ? tbl[pg - first_pg] : table[pg];
+            const int row_k = ((page * 2) * Hkv + pc.g) * page_size;           // first cache row of this page's K
+            const int row_v = row_k + Hkv * page_size;
+#pragma unroll
+            for (int c = 0; c < HD / 64; ++c) {
+              tma_load_2d(Ks + c * (KT * 64) + pp * page_size * 64, &kv_map, full + s, c * 64, row_k);
+              tma_load_2d(Ks + TILE_ELEMS + c * (KT * 64) + pp * page_size * 64, &kv_map, full + s, c * 64, row_v);
+            }
+          }
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+      tile_no = __shfl_sync(0xffffffffu, tile_no, 0);
+    }
+    return;
+  }
+
+  // ---- consumers (threads 0..127)
+  bspec::pdl_wait();
+  bspec::trace_record(8, t_trace);
+  // Only the first and the last row tile of a share can be shared with other CTAs: their partial results are
+  // announced after all of the share's streaming, so that the wait for those writes to land is paid once.
+  int n_pending = 0, pend_e[2], pend_g[2], pend_rt[2], pend_parts[2];
+  bool aborted = false;
+  for (long long pos = share_begin; pos < share_end;) {
+    Piece pc;
+    piece_at(pc, pos, share_end, b, sh, pos0_of, rows_of, n_entries, Hq, Hkv, row_tiles, window);
+    pos += pc.tiles_taken;
+    if (pc.row0 >= pc.t.rows_total) continue;               // no such row tile in this request: nothing to write
+    const TileGeom& t = pc.t;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+    int last_stage = -1;
+    if (pc.n_tiles > 0) {
+      int lim[2], lo[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int row = pc.row0 + (lane >> 2) + 8 * r;
+        const int qi = row / t.G;
+        lim[r] = row < t.rows_total ? t.pos0 + qi : -1;
+        lo[r] = window > 0 ? max(0, t.pos0 + qi - window + 1) : 0;
+      }
+      load_q_tile<HD>(Qs, q, q_row_stride, t, pc.row0, 16);
+      bar_consumers();
+      uint32_t qf[HD / 16][4];
+      {
+        const int mat = lane >> 3, r8 = lane & 7;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+          ldmatrix_x4(qf[ks], Qs + swz<HD>(8 * (mat & 1) + r8, 16 * ks + 8 * (mat >> 1)));
+      }
+      for (int k = 0; k < pc.n_tiles; ++k, ++tile_no) {
+        const int s = tile_no % TMA_STAGES;
+        const uint32_t ph = (tile_no / TMA_STAGES) & 1u;
+        if (!mbar_wait(full + s, ph, abort_flag, status, 14)) break;   // the flag is set: all warps leave below
+        const __nv_bfloat16* Ks = KV + (size_t)s * 2 * TILE_ELEMS;
+        const int key0 = pc.k_begin + k * KT;
+        if (key0 + 16 * warp < pc.k_end)
+          block16<HD, true>(qf, Ks, Ks + TILE_ELEMS, 16 * warp, key0, lim[0], lim[1], lo[0], lo[1], pc.k_end,
+                            scale_log2, m, l, o);
+        __syncwarp();
+        if (k + 1 < pc.n_tiles) {
+          if (lane == 0) mbar_arrive(empty + s);
+        } else {
+          last_stage = s;                                   // kept for the combine below
+        }
+      }
+    }
+    bar_consumers();                     // every warp is done with the last tile's keys (and with Qs)
+    if (*abort_flag) { aborted = true; break; }
+    if (pc.n_parts > 1 && n_pending < 2) {
+      pend_e[n_pending] = pc.e; pend_g[n_pending] = pc.g; pend_rt[n_pending] = pc.rt; pend_parts[n_pending] = pc.n_parts;
+      ++n_pending;
+    }
+
+    // ---- combine the 4 warps (in the last tile's stage), write the result or the partial result
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+    // Os: [4 warps][16 rows][HD] with the 4-float groups of a row XOR-ed by the row (no bank conflicts either way)
+    float* Os = last_stage >= 0 ? reinterpret_cast<float*>(KV + (size_t)last_stage * 2 * TILE_ELEMS) : nullptr;
+    float* Ms = MsLs;
+    float* Ls = MsLs + 64;
+    float* Fs = MsLs + 128;              // [4][16] weight of each warp's share of a row; [16] the row's sum after it
+    if (Os != nullptr) {
+#pragma unroll
+      for (int nd = 0; nd < HD / 8; ++nd)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const int row = (lane >> 2) + 8 * r, col = 8 * nd + 2 * (lane & 3);
+          *reinterpret_cast<float2*>(Os + (warp * 16 + row) * HD + ((((col >> 2) ^ (row & 7)) << 2) | (col & 3))) =
+              make_float2(o[nd][2 * r], o[nd][2 * r + 1]);
+        }
+      if ((lane & 3) == 0) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          Ms[warp * 16 + (lane >> 2) + 8 * r] = m[r];
+          Ls[warp * 16 + (lane >> 2) + 8 * r] = l[r];
+        }
+      }
+    }
+    bar_consumers();
+    if (threadIdx.x < 16) {
+      const int row = threadIdx.x;
+      float mt = -INFINITY, lt = 0.f;
+      if (Os != nullptr) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mt = fmaxf(mt, Ms[w * 16 + row]);
+      }
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float f = mt == -INFINITY ? 0.f : exp2f(Ms[w * 16 + row] - mt);
+        Fs[w * 16 + row] = f;
+        lt += mt == -INFINITY ? 0.f : Ls[w * 16 + row] * f;
+      }
+      Fs[64 + row] = lt;
+      Fs[80 + row] = mt;
+    }
+    bar_consumers();
+    const int nrows = min(16, t.rows_total - pc.row0);
+    for (int idx = threadIdx.x; idx < nrows * (HD / 4); idx += NTHREADS) {
+      const int row = idx / (HD / 4), c4 = idx - row * (HD / 4);
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (Os != nullptr) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const float f = Fs[w * 16 + row];
+          const float4 v = *reinterpret_cast<const float4*>(Os + (w * 16 + row) * HD + ((c4 ^ (row & 7)) << 2));
+          acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
+        }
+      }
+      const float lt = Fs[64 + row];
+      const int r = pc.row0 + row, qi = r / t.G, h = pc.g * t.G + (r - qi * t.G);
+      if (pc.n_parts == 1) {
+        const float inv = lt > 0.f ? 1.f / lt : 0.f;
+        uint2 packed;
+        packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+        packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+        *reinterpret_cast<uint2*>(out + ((size_t)(t.q_begin + qi) * Hq + h) * HD + 4 * c4) = packed;
+      } else {
+        const size_t ph = (size_t)(pc.e * rows_pe + qi) * Hq + h;     // partial results: by request and its row
+        *reinterpret_cast<float4*>(o_part + (ph * max_parts + pc.part) * HD + 4 * c4) = acc;
+        if (c4 == 0) {
+          ml_part[(ph * max_parts + pc.part) * 2] = Fs[80 + row];
+          ml_part[(ph * max_parts + pc.part) * 2 + 1] = lt;
+        }
+      }
+    }
+    // hand the stage back: the copies that will overwrite it run in the asynchronous proxy
+    if (last_stage >= 0) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      bar_consumers();
+      if (lane == 0) mbar_arrive(empty + last_stage);
+    }
+  }
+  if (aborted || n_pending == 0) return;
+  // The CTA that announces a row tile's last partial result joins them and resets the counter for the next launch.
+  __threadfence();
+  bar_consumers();
+  if ((int)threadIdx.x < n_pending) {
+    const int i = threadIdx.x;
+    const int tile_id = (pend_e[i] * Hkv + pend_g[i]) * row_tiles + pend_rt[i];
+    red[i] = atomicAdd(&tile_counters[tile_id], 1) == pend_parts[i] - 1;
+    if (red[i]) tile_counters[tile_id] = 0;
+  }
+  bar_consumers();
+  float* Wt = reinterpret_cast<float*>(KV);     // every tile of this CTA has been consumed: the stages are free
+  for (int i = 0; i < n_pending; ++i) {
+    if (!red[i]) continue;
+    __threadfence();
+    const int e = pend_e[i], q_begin = rows_of[e] & ((1 << 26) - 1), q_len = rows_of[e] >> 26, G = Hq / Hkv;
+    join_parts<HD>(Wt, out, o_part, ml_part, e, pend_g[i], pend_rt[i] * 16, q_begin, q_len * G, G, Hq, pend_parts[i],
+                   max_parts, rows_pe);
+  }
+}
+
+template <int HD> size_t decode_shares_smem() {
+  return 1024 + (size_t)TMA_STAGES * 2 * KT * HD * 2 + (size_t)16 * HD * 2 + 2 * TMA_STAGES * 8 + (size_t)224 * 4 +
+         (size_t)(3 * BAL_MAX_ENTRIES + 1 + BAL_TBL + 4) * 4 + 64;
+}
+
 // ------------------------------------------------------------------------------------ prefill, 128 rows, TMA
 // One warp: scores of its 16 rows against all 64 keys of a tile, one online-softmax step, P*V.
 template <int HD, bool TMA_TILE>
@@ -907,13 +1384,16 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
            int* tile_counters, int* status, long long kv_rows, const __nv_bfloat16* cache, const int* qo_indptr, const int* positions, const int* tok_entry,
            const int* kv_indptr, const int* kv_indices, int n_entries, int n_tokens, int max_q_len, int Hq, int Hkv,
            int page_size, float scale, int window, int n_splits, int max_q_short, int run_decode, int run_prefill,
-           cudaStream_t stream) {
+           cudaStream_t stream, int balanced = 0, const int* kv_len = nullptr) {
   const float scale_log2 = scale * 1.4426950408889634f;
   const int G = Hq / Hkv;
   static bool attr_set = false;
   if (!attr_set) {
     cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem<HD>());
     cudaFuncSetAttribute(attn_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_tma_smem<HD>());
+    cudaFuncSetAttribute(attn_decode_shares_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)decode_shares_smem<HD>());
+    cudaFuncSetAttribute(attn_decode_shares_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     cudaFuncSetAttribute(attn_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_smem<HD>());
     if constexpr (HD <= 128)
       cudaFuncSetAttribute(attn_prefill_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -929,6 +1409,25 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
     if (kv_rows > 0 && status != nullptr && page_size % 8 == 0 && KT % page_size == 0) {
       CUtensorMap kv_map;
       if (make_map_2d_bf16(&kv_map, cache, kv_rows, HD, page_size, 64)) {
+       if (balanced && n_entries <= BAL_MAX_ENTRIES && n_splits >= 4 && n_splits <= 64 && n_tokens < (1 << 26)) {
+        // equal shares of the tiles over as many CTAs as the device holds at once, then the join
+        static int resident = 0;
+        if (resident == 0) {
+          int dev = 0, sms = 0, per_sm = 0;
+          cudaGetDevice(&dev);
+          cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_shares_kernel<HD>, DECODE_TMA_THREADS,
+                                                        decode_shares_smem<HD>());
+          resident = sms * (per_sm > 0 ? per_sm : 1);
+        }
+        BSPEC_LAUNCH((attn_decode_shares_kernel<HD>), dim3(resident), DECODE_TMA_THREADS, decode_shares_smem<HD>(),
+                     stream, kv_map, q, q_row_stride, out, o_part, ml_part, tile_counters, status, qo_indptr, positions,
+                     kv_len, kv_indptr, kv_indices, n_entries, Hq, Hkv, page_size, scale_log2, window, n_splits,
+                     short_q, row_tiles, max_q_short);
+        launched = true;
+       }
+      }
+      if (!launched && make_map_2d_bf16(&kv_map, cache, kv_rows, HD, page_size, 64)) {
         BSPEC_LAUNCH((attn_decode_tma_kernel<HD>), grid, DECODE_TMA_THREADS, decode_tma_smem<HD>(), stream, kv_map, q,
                      q_row_stride, out, o_part, ml_part, tile_counters, status, qo_indptr, positions, kv_indptr,
                      kv_indices, Hq, Hkv, page_size, scale_log2, window, n_splits, row_tiles, max_q_short);
@@ -976,19 +1475,24 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
 // unsupported head_dim.
 // status: one int on the device (0 unless a bounded wait ran out); n_pages: pages of this cache layer (lets the
 // split-key kernel load K/V through TMA; 0 keeps it on plain asynchronous copies).
+// balanced != 0 (with n_pages > 0, 4 <= n_splits <= 64 and at most 512 requests): the short requests run on the
+// kernel that gives every CTA an equal share of all key tiles.  n_splits is then the most partial results a row
+// tile may get, and the scratch is indexed by request (o_part [n_entries * min(max_q_len, max_q_short) * Hq *
+// n_splits * hd], ml_part likewise).  kv_len (may be null): [n_entries] each request's length after this step, which saves
+// those kernels the dependent load of positions[qo_indptr[e]].
 BSPEC_API int bspec_attention_bf16(const void* q, long long q_row_stride, void* out, float* o_part, float* ml_part,
                                    int* tile_counters, int* status, long long n_pages, const void* cache, const int* qo_indptr, const int* positions,
                                    const int* tok_entry, const int* kv_indptr, const int* kv_indices, int n_entries,
                                    int n_tokens, int max_q_len, int Hq, int Hkv, int hd, int page_size, float scale,
                                    int window, int n_splits, int max_q_short, int run_decode, int run_prefill,
-                                   cudaStream_t stream) {
+                                   int balanced, const int* kv_len, cudaStream_t stream) {
   if (n_entries <= 0 || n_tokens <= 0) return 0;
   if (Hq % Hkv != 0 || n_splits < 1 || n_splits > 64) return (int)cudaErrorInvalidValue;
 #define GO(HDV)                                                                                                    \
   return launch<HDV>((const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, o_part, ml_part, tile_counters,   \
                      status, n_pages * 2 * Hkv * page_size, (const __nv_bfloat16*)cache, qo_indptr, positions, tok_entry, kv_indptr, kv_indices, n_entries, \
                      n_tokens, max_q_len, Hq, Hkv, page_size, scale, window, n_splits, max_q_short, run_decode,      \
-                     run_prefill, stream)
+                     run_prefill, stream, balanced, kv_len)
   if (hd == 64) GO(64);
   if (hd == 128) GO(128);
   if (hd == 256) GO(256);

@@ -75,34 +75,198 @@ __device__ int block_count(int v, int* iscratch) {
 
 // Stage 1 (one block per row): the smallest ordered key a token must reach to stay in the top-k / top-p set;
 // 0 (everything stays) for rows that are greedy or unrestricted, which leave at once.
-__global__ void __launch_bounds__(THREADS)
-threshold_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
-                 const int* __restrict__ top_k, const float* __restrict__ top_p, uint32_t* __restrict__ threshold) {
-  bspec::pdl_prologue(11);
-  __shared__ float fscratch[32];
-  __shared__ int iscratch[32];
-  const int r = blockIdx.x;
-  const float T = temperature[r];
-  const int k = top_k[r];
-  const float p = top_p[r];
-  const bool use_k = k > 0 && k < vocab, use_p = p > 0.f && p < 1.f;
-  if (!(T > 0.f) || (!use_k && !use_p)) {
-    if (threadIdx.x == 0) threshold[r] = 0u;
-    return;
+//
+// Three passes over the row.  (1) Its largest and smallest finite logit.  (2) A histogram over BINS equal steps of
+// the logit's value: of counts between smallest and largest for top-k, of probability mass over the 22 T below
+// the largest (below that a token's mass rounds to nothing) for top-p alone.  A scan from the top bin finds the bin
+// in which the k-th token lies (in which the mass reaches top_p).  (3) The tokens of that bin (with top-k: of that bin
+// and all above it, which are then all that top-p has to weigh) go to a list in shared memory, where the exact key is
+// found by comparing every listed token with every other.  Mass is summed in 64-bit fixed point (2^-30 of the largest
+// token's mass), so a sum does not depend on the order of its terms, and the threshold is the same in every run and
+// batch.  Rows whose list would not fit (k above LIST, thousands of equal logits) are bisected on the key bits
+// instead, one pass per bit.
+using u64 = unsigned long long;
+constexpr int BINS = 4096;
+constexpr int LIST = 2048;
+static_assert(BINS % THREADS == 0, "each thread scans BINS / THREADS bins");
+
+__device__ __forceinline__ uint32_t mass_of(float x, float mx, float invT) {   // at most 2^30
+  return (uint32_t)(expf((x - mx) * invT) * 1073741824.f + 0.5f);
+}
+
+__device__ __forceinline__ int bin_of(float x, float lo, float inv_step) {   // monotone in x; NaN and -inf to bin 0
+  return (int)fminf(fmaxf((x - lo) * inv_step, 0.f), (float)(BINS - 1));
+}
+
+template <class F>
+__device__ __forceinline__ void for_each_logit(const float* __restrict__ row, int vocab, F f) {
+  if ((vocab & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    const float4* r4 = reinterpret_cast<const float4*>(row);
+    for (int i = threadIdx.x; i < (vocab >> 2); i += blockDim.x) {
+      const float4 v = r4[i];
+      f(v.x); f(v.y); f(v.z); f(v.w);
+    }
+  } else {
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) f(row[i]);
   }
-  const float* row = logits + (size_t)r * vocab;
+}
+
+__device__ u64 block_sum_u64(u64 v, u64* wsum) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) wsum[warp] = v;
+  __syncthreads();
+  u64 t = lane < nw ? wsum[lane] : 0;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  __syncthreads();
+  return t;
+}
+
+// Every thread gets the largest bin d with sum(hist[d..BINS)) >= need, and what of need is left for that bin.
+// need is at least 1 and at most the histogram's total.  WIDE: a bin is hi[b] * 2^32 + lo[b].
+template <bool WIDE>
+__device__ void select_bin(const uint32_t* lo, const uint32_t* hi, u64 need, u64* wsum, u64* sel, int& d, u64& rem) {
+  constexpr int PER = BINS / THREADS;
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  u64 h[PER];
+  u64 local = 0;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int b = BINS - 1 - (t * PER + j);
+    h[j] = WIDE ? (((u64)hi[b] << 32) | lo[b]) : (u64)lo[b];
+    local += h[j];
+  }
+  u64 incl = local;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const u64 y = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += y;
+  }
+  if (lane == 31) wsum[warp] = incl;
+  __syncthreads();
+  for (int w = 0; w < warp; ++w) incl += wsum[w];
+  u64 run = incl - local;
+  if (run < need && need <= incl) {
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      if (run < need && need <= run + h[j]) { sel[0] = (u64)(BINS - 1 - (t * PER + j)); sel[1] = need - run; }
+      run += h[j];
+    }
+  }
+  __syncthreads();
+  d = (int)sel[0];
+  rem = sel[1];
+  __syncthreads();
+}
+
+__device__ __forceinline__ u64 share_of(float p, u64 z) {
+  const u64 need = (u64)((double)p * (double)z);
+  return need < 1 ? 1 : (need > z ? z : need);
+}
+
+struct ThresholdShared {
+  uint32_t lo[BINS];        // counts, or the low words of the mass; then the list's keys
+  u64 wide[BINS / 2];       // the high words of the mass, as uint32[BINS]; then the list's masses
+  u64 wsum[32];
+  u64 sel[2];
+  float fscratch[64];
+  int iscratch[32];
+  int n_list;
+  uint32_t best;
+};
+
+// False (for the whole block) if the row does not fit the lists; the threshold is then not written.
+__device__ bool threshold_binned(const float* __restrict__ row, int vocab, float mx, float mn, float T, int k, float p,
+                                 bool use_k, bool use_p, ThresholdShared& sh, uint32_t& th) {
   const float invT = 1.f / T;
-  float mx = -INFINITY;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) mx = fmaxf(mx, row[i]);
-  mx = warp_max(mx);
-  {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  uint32_t* hi = reinterpret_cast<uint32_t*>(sh.wide);
+  uint32_t* lkey = sh.lo;
+  u64* lmass = sh.wide;
+  const float lo_v = use_k ? mn : mx - 22.f * T;
+  const float inv_step = (float)BINS / (mx - lo_v);
+  if (!(inv_step < INFINITY) || !(inv_step > 0.f)) return false;
+  for (int i = threadIdx.x; i < BINS; i += blockDim.x) { sh.lo[i] = 0; hi[i] = 0; }
+  if (threadIdx.x == 0) { sh.n_list = 0; sh.best = 0xffffffffu; }
+  __syncthreads();
+  int d;
+  u64 need = 0, above = 0;   // top-p alone: the mass to reach, and the mass of the bins above d
+  if (use_k) {
+    for_each_logit(row, vocab, [&](float x) { atomicAdd(&sh.lo[bin_of(x, lo_v, inv_step)], 1u); });
     __syncthreads();
-    if (lane == 0) fscratch[warp] = mx;
+    u64 rem;
+    select_bin<false>(sh.lo, nullptr, (u64)k, sh.wsum, sh.sel, d, rem);
+    const u64 n = (u64)k - rem + sh.lo[d];
     __syncthreads();
-    float t = lane < nw ? fscratch[lane] : -INFINITY;
-    mx = warp_max(t);
+    if (n > LIST) return false;
+  } else {
+    for_each_logit(row, vocab, [&](float x) {
+      const uint32_t w = mass_of(x, mx, invT);
+      if (w) {
+        const int b = bin_of(x, lo_v, inv_step);
+        const uint32_t old = atomicAdd(&sh.lo[b], w);
+        if (old + w < old) atomicAdd(&hi[b], 1u);
+      }
+    });
+    __syncthreads();
+    u64 z = 0;
+    for (int i = threadIdx.x; i < BINS; i += blockDim.x) z += ((u64)hi[i] << 32) | sh.lo[i];
+    z = block_sum_u64(z, sh.wsum);
+    need = share_of(p, z);
+    u64 rem;
+    select_bin<true>(sh.lo, hi, need, sh.wsum, sh.sel, d, rem);
+    above = need - rem;
   }
+  // the list: with top-k every token from bin d up, else the tokens of bin d that have mass
+  for_each_logit(row, vocab, [&](float x) {
+    const int b = bin_of(x, lo_v, inv_step);
+    if (use_k ? b < d : b != d) return;
+    const uint32_t w = use_p ? mass_of(x, mx, invT) : 0u;
+    if (!use_k && w == 0) return;
+    const int slot = atomicAdd(&sh.n_list, 1);
+    if (slot < LIST) { lkey[slot] = order_key(x); lmass[slot] = w; }
+  });
+  __syncthreads();
+  const int n = sh.n_list;
+  if (n > LIST) return false;
+  uint32_t kth = 0;
+  if (use_k) {   // the k-th largest key: the smallest listed key with fewer than k keys above it
+    for (int e = threadIdx.x; e < n; e += blockDim.x) {
+      const uint32_t key = lkey[e];
+      int gt = 0;
+      for (int j = 0; j < n; ++j) gt += lkey[j] > key;
+      if (gt < k) atomicMin(&sh.best, key);
+    }
+    __syncthreads();
+    kth = sh.best;
+    __syncthreads();
+    if (!use_p) { th = kth; return true; }
+    u64 z = 0;
+    for (int e = threadIdx.x; e < n; e += blockDim.x) z += lkey[e] >= kth ? lmass[e] : 0ull;
+    z = block_sum_u64(z, sh.wsum);
+    need = share_of(p, z);
+    if (threadIdx.x == 0) sh.best = 0xffffffffu;
+    __syncthreads();
+  }
+  // top-p: the smallest kept key with less than the wanted mass above it
+  for (int e = threadIdx.x; e < n; e += blockDim.x) {
+    const uint32_t key = lkey[e];
+    if (key < kth) continue;
+    u64 m = above;
+    for (int j = 0; j < n; ++j) m += lkey[j] > key ? lmass[j] : 0ull;
+    if (m < need) atomicMin(&sh.best, key);
+  }
+  __syncthreads();
+  th = sh.best;
+  return true;
+}
+
+// One pass over the row per bit of the key: for rows that the lists above do not hold.
+__device__ uint32_t threshold_bisected(const float* __restrict__ row, int vocab, float mx, float T, int k, float p,
+                                       bool use_k, bool use_p, float* fscratch, int* iscratch) {
+  const float invT = 1.f / T;
   // top-k: largest key such that count(key' >= key) >= k, by bisection on the ordered bits
   uint32_t kth = 0;
   if (use_k) {
@@ -135,7 +299,43 @@ threshold_kernel(const float* __restrict__ logits, int vocab, const float* __res
     }
     pth = lo;
   }
-  if (threadIdx.x == 0) threshold[r] = pth;
+  return pth;
+}
+
+__global__ void __launch_bounds__(THREADS)
+threshold_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
+                 const int* __restrict__ top_k, const float* __restrict__ top_p, uint32_t* __restrict__ threshold) {
+  bspec::pdl_prologue(11);
+  __shared__ ThresholdShared sh;
+  const int r = blockIdx.x;
+  const float T = temperature[r];
+  const int k = top_k[r];
+  const float p = top_p[r];
+  const bool use_k = k > 0 && k < vocab, use_p = p > 0.f && p < 1.f;
+  if (!(T > 0.f) || (!use_k && !use_p)) {
+    if (threadIdx.x == 0) threshold[r] = 0u;
+    return;
+  }
+  const float* row = logits + (size_t)r * vocab;
+  float mx = -INFINITY, mn = INFINITY;   // the smallest of the finite ones: masked tokens do not stretch the bins
+  for_each_logit(row, vocab, [&](float x) {
+    mx = fmaxf(mx, x);
+    if (x > -INFINITY) mn = fminf(mn, x);
+  });
+  mx = warp_max(mx);
+  mn = -warp_max(-mn);
+  {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    if (lane == 0) { sh.fscratch[warp] = mx; sh.fscratch[32 + warp] = -mn; }
+    __syncthreads();
+    mx = warp_max(lane < nw ? sh.fscratch[lane] : -INFINITY);
+    mn = -warp_max(lane < nw ? sh.fscratch[32 + lane] : -INFINITY);
+    __syncthreads();
+  }
+  uint32_t th = 0;
+  const bool binned = mx < INFINITY && mn < mx && threshold_binned(row, vocab, mx, mn, T, k, p, use_k, use_p, sh, th);
+  if (!binned) th = threshold_bisected(row, vocab, mx, T, k, p, use_k, use_p, sh.fscratch, sh.iscratch);
+  if (threadIdx.x == 0) threshold[r] = th;
 }
 
 // Stage 2 (grid: slices x rows): best of (logit / T + Gumbel noise) over one slice of the row's kept tokens;

@@ -143,6 +143,11 @@ def bench_small(cfg, ms, timer, pk, dev):
     for rows in (1, 8, 64):
         t = timer.time(lambda: ops.argmax(logits[:rows]))
         print(f"{'argmax':16s} {rows:5d} | {t:8.4f} {rows * cfg.vocab_size * 4 / t / 1e6:7.0f}")
+        f = lambda v, dt: torch.full((rows,), v, device=dev, dtype=dt)
+        for name, k, p in (("sample", -1, 0.0), ("sample k20", 20, 0.0), ("sample p.95", -1, 0.95), ("sample k20 p.95", 20, 0.95)):
+            T, K, P, sid, ctr = f(0.6, torch.float32), f(k, torch.int32), f(p, torch.float32), f(3, torch.int64), f(0, torch.int64)
+            t = timer.time(lambda: ops.sample(logits[:rows], T, K, P, sid, ctr, 1))
+            print(f"{name:16s} {rows:5d} | {t:8.4f} {rows * cfg.vocab_size * 4 / t / 1e6:7.0f}")
 
 
 def main():

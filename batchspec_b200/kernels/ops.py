@@ -50,7 +50,7 @@ _SIGNATURES = {
                                 c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "bspec_attention_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong,
                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                             c_int, c_int, c_int, c_int, c_void_p],
+                             c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "bspec_gemm_tc_plan": [c_int, c_int, c_int, c_int, c_void_p],
     "bspec_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
     "bspec_attention_prefill_tc": [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
@@ -262,6 +262,7 @@ def rope_inplace(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tenso
 
 USE_TMA_ATTENTION = os.environ.get("BSPEC_TMA_ATTENTION", "1") != "0"
 USE_TC_ATTENTION = os.environ.get("BSPEC_TC_ATTENTION", "1") != "0"    # tcgen05 kernel for long prompt portions
+BALANCED_ATTENTION = os.environ.get("BSPEC_BALANCED_ATTENTION", "1") != "0"   # equal chunks over a fixed grid for decode
 FORCE_GENERIC_ATTENTION = False      # tests set this to compare the tensor-core kernels with the generic one
 _SM_COUNT = 148
 
@@ -316,14 +317,21 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, c
     if qkv.dtype == torch.bfloat16 and head_dim in (64, 128, 256) and not FORCE_GENERIC_ATTENTION:
         group = n_heads // n_kv_heads
         short = max(1, 16 // group)
-        # the TMA-fed split-key kernel (page sizes 8..64) fits two CTAs per SM, the plain one three
+        # the TMA-fed split-key kernels (page sizes 8..64) fit two CTAs per SM, the plain one three
         tma = USE_TMA_ATTENTION and tables.page_size % 8 == 0 and 64 % tables.page_size == 0
-        n_splits = ctx.extras.get("attn_splits") or attention_splits(ctx.n_entries, n_kv_heads, group, ctx.max_q_len,
-                                                                     ctx.max_kv_len, 2 if tma else 3)
+        # Equal shares of all key tiles over a fixed grid (cut on the device from the step's lengths): n_splits is
+        # then only the most partial results a row tile may be left in, and the scratch is indexed by request.
+        balanced = int(tma and BALANCED_ATTENTION and ctx.n_entries <= 512 and not ctx.extras.get("attn_splits"))
+        if balanced:
+            n_splits = min(64, max(16, -(-4 * _SM_COUNT // (ctx.n_entries * n_kv_heads)) + 2))
+        else:
+            n_splits = ctx.extras.get("attn_splits") or attention_splits(ctx.n_entries, n_kv_heads, group, ctx.max_q_len,
+                                                                         ctx.max_kv_len, 2 if tma else 3)
         o_part = ml_part = counters = None
         if n_splits > 1:
-            o_part = torch.empty((ctx.n_tokens * n_heads * n_splits * head_dim,), dtype=torch.float32, device=qkv.device)
-            ml_part = torch.empty((ctx.n_tokens * n_heads * n_splits * 2,), dtype=torch.float32, device=qkv.device)
+            rows = ctx.n_entries * min(ctx.max_q_len, short) if balanced else ctx.n_tokens
+            o_part = torch.empty((rows * n_heads * n_splits * head_dim,), dtype=torch.float32, device=qkv.device)
+            ml_part = torch.empty((rows * n_heads * n_splits * 2,), dtype=torch.float32, device=qkv.device)
             row_tiles = -(-(min(ctx.max_q_len, short) * group) // 16)
             counters = _counters(qkv.device, ctx.n_entries * n_kv_heads * row_tiles)
         run_decode = int(ctx.extras.get("min_q_len", 1) <= short)
@@ -343,8 +351,8 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, c
             _status_word(qkv.device).data_ptr(), cache.shape[0] if tma else 0, cache.data_ptr(),
             ctx.qo_indptr.data_ptr(), ctx.positions.data_ptr(), ctx.tok_entry.data_ptr(), tables.kv_indptr.data_ptr(),
             tables.kv_indices.data_ptr(), ctx.n_entries, ctx.n_tokens, ctx.max_q_len, n_heads, n_kv_heads, head_dim,
-            tables.page_size, float(scale), int(window), n_splits, short, run_decode, run_prefill, _stream()),
-            "attention_bf16")
+            tables.page_size, float(scale), int(window), n_splits, short, run_decode, run_prefill, balanced,
+            _ptr(getattr(ctx, "kv_len", None)), _stream()), "attention_bf16")
         global _launches
         _launches += 1 if run_decode and run_prefill else 0
         return
@@ -443,10 +451,14 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
-           stream_id: torch.Tensor, counter: torch.Tensor, seed: int) -> torch.Tensor:
+           stream_id: torch.Tensor, counter: torch.Tensor, seed: int,
+           threshold_out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Per-row parameters on the device: temperature f32 (<= 0: greedy), top_k i32
     (<= 0: off), top_p f32 (<= 0 or >= 1: off), stream_id i64 and counter i64 (the
-    random stream of the row's request and the index of the draw in it)."""
+    random stream of the row's request and the index of the draw in it).
+    ``threshold_out`` (int32 [rows]) receives each row's threshold: the ordered key
+    (sign bit flipped for positive floats, all bits for negative) of the smallest
+    logit that stays in the top-k / top-p set, 0 where nothing is cut."""
     _require_cuda(logits, temperature, top_k, top_p, stream_id, counter)
     rows = logits.shape[0]
     assert logits.dtype == torch.float32 and logits.is_contiguous()
@@ -456,10 +468,11 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     if rows == 0:
         return out
     part_v, part_i = _pick_scratch(logits)
-    threshold = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    threshold = threshold_out if threshold_out is not None else torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    assert threshold.dtype == torch.int32 and threshold.numel() == rows and threshold.is_cuda
     _check(load_library().bspec_sample(logits.data_ptr(), rows, logits.shape[1], temperature.data_ptr(),
                                        top_k.data_ptr(), top_p.data_ptr(), stream_id.data_ptr(), counter.data_ptr(),
                                        int(seed) & 0xFFFFFFFFFFFFFFFF, threshold.data_ptr(), part_v.data_ptr(),
                                        part_i.data_ptr(), out.data_ptr(), _stream()), "sample")
-    count_launches(2)
+    count_launches(3)
     return out

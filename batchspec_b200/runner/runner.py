@@ -99,6 +99,10 @@ class Runner:
         print(f"Mean generated tokens per step: {st['generated'] / max(st['steps'], 1):.2f}")
         print(f"Wall time: {dt:.3f} s  ({st['generated'] / dt:.1f} generated tok/s, prompts included; "
               f"{(st['generated'] + st['tokens_fed']) / dt:.1f} processed tok/s)")
+        if st["decode_steps"]:
+            print(f"Pure decode steps: {st['decode_steps']} of {st['steps']}, mean "
+                  f"{1e3 * st['decode_seconds'] / st['decode_steps']:.2f} ms wall, "
+                  f"{st['decode_tokens'] / st['decode_seconds']:.1f} tok/s over them")
         ms = sorted(st["step_ms"])
         if ms:
             pct = lambda q: ms[min(len(ms) - 1, int(q * len(ms)))]

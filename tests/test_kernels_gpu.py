@@ -154,7 +154,7 @@ def test_rope_and_cache_append(ops, dtype, Hq, Hkv, hd, rot, inter, ps):
 
 
 def _attention_case(ops, dtype, Hq, Hkv, hd, ps, q_lens, kv_lens, window=0, spike=None, seed=0, force_generic=False,
-                    splits=None):
+                    splits=None, balanced=True, give_kv_len=False):
     """Random q/k/v, pages in scrambled order; returns (got, want)."""
     g = torch.Generator(device=DEV).manual_seed(seed)
     n_entries, G = len(q_lens), Hq // Hkv
@@ -187,15 +187,22 @@ def _attention_case(ops, dtype, Hq, Hkv, hd, ps, q_lens, kv_lens, window=0, spik
     ctx = SimpleNamespace(qo_indptr=torch.tensor(qo, dtype=torch.int32, device=DEV), positions=pos, tok_entry=ent,
                           n_entries=n_entries, n_tokens=n, max_q_len=max(q_lens), max_kv_len=max(kv_lens),
                           extras={"min_q_len": min(q_lens), "attn_splits": splits})
+    if give_kv_len:
+        ctx.kv_len = torch.tensor(kv_lens, dtype=torch.int32, device=DEV)
     tables = SimpleNamespace(kv_indptr=torch.tensor(indptr, dtype=torch.int32, device=DEV),
                              kv_indices=perm.to(DEV, torch.int32), page_size=ps)
     out = torch.full((n, Hq * hd), float("nan"), device=DEV, dtype=dtype)
     scale = 1.0 / math.sqrt(hd)
     ops.FORCE_GENERIC_ATTENTION = force_generic
+    was = ops.BALANCED_ATTENTION
+    ops.BALANCED_ATTENTION = balanced
     try:
         ops.paged_attention(q, out, cache, ctx, tables, Hq, Hkv, hd, scale, window)
+        torch.cuda.synchronize()
+        ops.check_status()
     finally:
         ops.FORCE_GENERIC_ATTENTION = False
+        ops.BALANCED_ATTENTION = was
     want = torch.empty(n, Hq, hd, device=DEV)
     for e, (ql, L) in enumerate(zip(q_lens, kv_lens)):
         qe = q[qo[e]:qo[e + 1]].float().view(ql, Hq, hd)
@@ -245,6 +252,36 @@ def test_split_keys_agree_with_one_pass(ops, splits):
     torch.testing.assert_close(a, want, rtol=3e-2, atol=2e-2)
     b, _ = _attention_case(ops, torch.bfloat16, 8, 2, 128, 16, [1, 1, 2], [1000, 70, 513], force_generic=True, seed=7)
     torch.testing.assert_close(a, b, rtol=3e-2, atol=2e-2)
+
+
+RAGGED = [
+    # Hq, Hkv, hd, page, q_lens, kv_lens, window: decode-sized requests of very different lengths
+    (8, 2, 128, 16, [1] * 9, [3000, 1, 64, 65, 700, 2, 1500, 129, 4000], 0),
+    (32, 8, 128, 16, [1] * 40, [17 * i + 1 for i in range(40)], 0),           # more row tiles than CTAs' shares
+    (6, 2, 64, 8, [2, 1, 2, 1, 1], [900, 5, 70, 2000, 333], 0),               # 3 heads per kv head, two new tokens
+    (40, 2, 64, 16, [1, 1, 1], [100, 1000, 3], 0),                            # 20 heads per kv head: two row tiles
+    (4, 1, 256, 32, [1, 1], [2500, 40], 0),
+    (8, 2, 128, 16, [1, 1, 3, 1], [1200, 90, 700, 64], 200),                  # a window that leaves out early pages
+    (8, 2, 128, 64, [1] * 3, [70000, 10, 5000], 0),                           # one request far longer than the others
+]
+
+
+@pytest.mark.parametrize("give_kv_len", [False, True])
+@pytest.mark.parametrize("shape", RAGGED, ids=lambda s: f"H{s[0]}k{s[1]}d{s[2]}n{len(s[4])}w{s[6]}")
+def test_equal_shares_of_ragged_requests(ops, shape, give_kv_len):
+    """The decode kernel that gives every CTA the same number of key tiles, against the reference and against the
+    kernel that cuts every request by itself."""
+    Hq, Hkv, hd, ps, q_lens, kv_lens, window = shape
+    got, want = _attention_case(ops, torch.bfloat16, Hq, Hkv, hd, ps, q_lens, kv_lens, window=window, seed=5,
+                                give_kv_len=give_kv_len)
+    assert not torch.isnan(got).any()
+    torch.testing.assert_close(got, want, rtol=3e-2, atol=2e-2)
+    other, _ = _attention_case(ops, torch.bfloat16, Hq, Hkv, hd, ps, q_lens, kv_lens, window=window, seed=5,
+                               balanced=False)
+    torch.testing.assert_close(got, other, rtol=2e-2, atol=1e-2)
+    again, _ = _attention_case(ops, torch.bfloat16, Hq, Hkv, hd, ps, q_lens, kv_lens, window=window, seed=5,
+                               give_kv_len=give_kv_len)
+    assert torch.equal(got, again), "the same launch gives the same bits"
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -308,6 +345,52 @@ def test_sampling_depends_on_stream_and_counter_only(ops):
     assert not torch.equal(a, _draw(ops, row, 64, 1.0, -1, 0.0, seed=1, stream=4))
     assert not torch.equal(a, _draw(ops, row, 64, 1.0, -1, 0.0, seed=2, stream=3))
     assert len(set(a.tolist())) > 20
+
+
+def _threshold_values(ops, logits, T, k, p):
+    """The smallest logit each row keeps, read back from the sampling kernels' threshold word."""
+    n = logits.shape[0]
+    f = lambda v, dt: torch.full((n,), v, device=DEV, dtype=dt)
+    th = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops.sample(logits, f(T, torch.float32), f(k, torch.int32), f(p, torch.float32), f(1, torch.int64),
+               torch.arange(n, device=DEV, dtype=torch.int64), 7, threshold_out=th)
+    key = th.cpu().numpy().view(np.uint32)
+    bits = np.where(key & 0x80000000, key & 0x7FFFFFFF, ~key).astype(np.uint32)
+    return bits.view(np.float32)
+
+
+@pytest.mark.parametrize("vocab", [128256, 50257, 1000])
+def test_sampling_thresholds_at_large_vocabularies(ops, vocab):
+    """The cut of top-k and of top-p against a sort in float64: flat rows (most of the row stays under top-p),
+    peaked rows (a handful stays), ties at the k-th value, k above and below the in-kernel list."""
+    g = torch.Generator().manual_seed(vocab)
+    flat = torch.randn(vocab, generator=g)
+    peaked = torch.randn(vocab, generator=g) * 6
+    tied = flat.clone()
+    tied[torch.randperm(vocab, generator=g)[:40]] = flat.max() + 1      # forty equal largest logits
+    many = flat.clone()
+    many[: vocab // 2] = 2.0                                            # half the row equal, near the top
+    rows = torch.stack([flat, peaked, tied, many]).to(DEV).contiguous()
+    for T, k, p in [(1.0, 20, 0.0), (0.7, 20, 0.95), (1.0, -1, 0.9), (0.6, -1, 0.5), (1.3, 700 if vocab <= 1000 else 5000, 0.8),
+                    (1.0, 1, 0.0), (1.0, -1, 1e-6)]:
+        got = _threshold_values(ops, rows, T, k, p)
+        for r in range(rows.shape[0]):
+            x = rows[r].cpu().double().numpy()
+            order = np.sort(x)[::-1]
+            kept = order
+            if 0 < k < vocab:
+                kept = order[order >= order[k - 1]]
+            lo = hi = kept[-1]
+            if 0 < p < 1:
+                w = np.exp((kept - kept[0]) / T)
+                c = np.cumsum(w)
+                # float32 weights and a mass in fixed point move the crossing by a token or two when p falls near a step
+                j_lo = int(np.searchsorted(c, (p - 2e-5) * c[-1], side="left"))
+                j_hi = int(np.searchsorted(c, (p + 2e-5) * c[-1], side="left"))
+                hi, lo = kept[min(j_lo, len(kept) - 1)], kept[min(j_hi, len(kept) - 1)]
+            assert lo <= got[r] <= hi, (vocab, T, k, p, r, got[r], lo, hi)
+            if not (0 < p < 1):
+                assert got[r] == np.float32(kept[-1])
 
 
 GEMM_SHAPES = [
