@@ -74,7 +74,7 @@ def bench_gemms(cfg, ms, timer, pk, dev, only=None):
                 continue
             x = torch.randn(M, K, device=dev).bfloat16()
             out_dtype = torch.float32 if name == "lm_head" else torch.bfloat16
-            t_tc = timer.time(lambda: ops.gemm_tc(x, w, out_dtype))
+            t_tc = timer.time(lambda: ops.linear(x, w, out_dtype))
             t_lib = timer.time(lambda: torch.mm(x, w.t()) if out_dtype == torch.bfloat16 else torch.mm(x, w.t(), out_dtype=out_dtype))
             ops.check_status()
             byts = 2 * (N * K + M * K) + M * N * (4 if out_dtype == torch.float32 else 2)

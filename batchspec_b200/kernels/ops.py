@@ -53,6 +53,9 @@ _SIGNATURES = {
                              c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "bspec_gemm_tc_plan": [c_int, c_int, c_int, c_int, c_void_p],
     "bspec_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+    "bspec_gemm_stream_plan": [c_int, c_int, c_int, c_int, c_void_p],
+    "bspec_gemm_stream": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                          c_int, c_void_p],
     "bspec_attention_prefill_tc": [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                                    c_void_p],
@@ -78,10 +81,13 @@ def load_library():
         for name, argtypes in _SIGNATURES.items():
             fn = getattr(lib, name)
             fn.argtypes = argtypes
-            fn.restype = c_longlong if name == "bspec_gemm_tc_plan" else c_int
+            fn.restype = c_longlong if name in ("bspec_gemm_tc_plan", "bspec_gemm_stream_plan") else c_int
         _lib = lib
         if os.environ.get("BSPEC_PDL", "1") == "0":
             set_pdl(False)
+        if os.environ.get("BSPEC_GEMM_CTAS_PER_SM"):
+            lib.bspec_gemm_stream_ctas_per_sm.argtypes = [c_int]
+            lib.bspec_gemm_stream_ctas_per_sm(int(os.environ["BSPEC_GEMM_CTAS_PER_SM"]))
         if os.environ.get("BSPEC_GEMM_SPLITS"):
             lib.bspec_gemm_tc_force_splits.argtypes = [c_int]
             lib.bspec_gemm_tc_force_splits(int(os.environ["BSPEC_GEMM_SPLITS"]))
@@ -97,7 +103,8 @@ def set_pdl(on: bool) -> None:
 
 
 _TRACE_SETTERS = ["bspec_trace_set_attention_tcgen05", "bspec_trace_set_elementwise", "bspec_trace_set_attention_generic", "bspec_trace_set_attention_bf16",
-                  "bspec_trace_set_gemm_fp32", "bspec_trace_set_sampling", "bspec_trace_set_gemm_tcgen05"]
+                  "bspec_trace_set_gemm_fp32", "bspec_trace_set_sampling", "bspec_trace_set_gemm_tcgen05",
+                  "bspec_trace_set_gemm_stream"]
 TRACE_KERNEL_NAMES = {1: "embed", 2: "add_rmsnorm", 3: "gather_rows_add", 4: "silu_mul", 5: "rope_kv_append",
                       6: "rope_inplace", 7: "attn_generic", 8: "attn_decode", 9: "attn_prefill", 10: "sgemm",
                       11: "sample_threshold", 12: "sample_pick", 13: "sample_final", 20: "gemm_tcgen05", 30: "attn_prefill_tc"}
@@ -216,6 +223,8 @@ def linear_glu(x: torch.Tensor, w13: torch.Tensor, group: int = GLU_GROUP) -> to
     inter = N // 2
     if (GLU_FUSION and x.dtype == torch.bfloat16 and K % 8 == 0 and M > 0 and group == GLU_GROUP
             and x.is_contiguous() and (TC_GEMM == "all" or (TC_GEMM == "auto" and M <= TC_GEMM_MAX_M))):
+        if STREAM_GEMM and M <= STREAM_GEMM_MAX_M and N % 128 == 0 and w13.is_contiguous():
+            return gemm_stream(x, w13, x.dtype, glu=True)
         out = torch.empty((M, inter), dtype=x.dtype, device=x.device)
         _check(load_library().bspec_gemm_tc(x.data_ptr(), w13.data_ptr(), out.data_ptr(), M, N, K, 0, 1,
                                             _status_word(x.device).data_ptr(), _SM_COUNT, _stream()), "gemm_tc_glu")
@@ -392,6 +401,46 @@ def check_status() -> None:
                               f"never freed, 12 = keys never arrived)")
 
 
+# BSPEC_STREAM_GEMM=1 sends decode-sized products (at most STREAM_GEMM_MAX_M tokens) to the kernel that gives every
+# CTA an equal share of the weights' (tile, K block) units instead of the one-tile-per-CTA kernel.  Measured on
+# B200 it streams the weights at the memory's rate but pays more for joining the tiles that CTAs share (a fence,
+# an atomic and a read of the partial tiles in global memory against a cluster barrier and distributed shared
+# memory): 1 to 6 % slower per decode step of 1B to 8B models at 8 to 64 requests.  Off by default.
+STREAM_GEMM = os.environ.get("BSPEC_STREAM_GEMM", "0") != "0"
+STREAM_GEMM_MAX_M = 128
+_stream_scratch = {}
+
+
+def _stream_buffers(device, scratch_bytes: int, tiles: int):
+    """Scratch for partial tiles and the zeroed tile counters.  Buffers only grow, and the old ones stay alive:
+    a captured graph may still point at them."""
+    bufs = _stream_scratch.setdefault(device, {"scratch": [], "counters": []})
+    if not bufs["scratch"] or bufs["scratch"][-1].numel() * 4 < scratch_bytes:
+        bufs["scratch"].append(torch.empty((max(scratch_bytes // 4, 1 << 20),), dtype=torch.float32, device=device))
+    if not bufs["counters"] or bufs["counters"][-1].numel() < 2 * tiles:
+        bufs["counters"].append(torch.zeros((max(2 * tiles, 8192),), dtype=torch.int32, device=device))
+    return bufs["scratch"][-1], bufs["counters"][-1]
+
+
+def gemm_stream(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, glu: bool = False) -> torch.Tensor:
+    """x [M <= 128, K] @ w[N, K]^T on the equal-shares tcgen05 kernel (bfloat16 operands, float32 accumulation);
+    ``glu``: w interleaved by ``interleave_gate_up``, result silu(gate) * up of width N / 2."""
+    lib = load_library()
+    M, K = x.shape
+    N = w.shape[0]
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
+    plan = (c_int * 4)()
+    need = lib.bspec_gemm_stream_plan(M, N, K, _SM_COUNT, plan)
+    if need < 0 or (glu and N % 128 != 0):
+        raise KernelError(f"gemm_stream: sizes M={M} N={N} K={K} are not supported (M <= 128, K a multiple of 8)")
+    scratch, counters = _stream_buffers(x.device, need, plan[3])
+    out = torch.empty((M, N // 2 if glu else N), dtype=out_dtype, device=x.device)
+    _check(lib.bspec_gemm_stream(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, int(out_dtype == torch.float32),
+                                 int(glu), scratch.data_ptr(), counters.data_ptr(), _status_word(x.device).data_ptr(),
+                                 _SM_COUNT, _stream()), "gemm_stream")
+    return out
+
+
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """x [M, K] @ w[N, K]^T on the tcgen05 kernel (bfloat16 operands, float32 accumulation)."""
     lib = load_library()
@@ -421,6 +470,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
         return out
     if (K % 8 == 0 and M > 0 and x.is_contiguous() and w.is_contiguous()
             and (TC_GEMM == "all" or (TC_GEMM == "auto" and M <= TC_GEMM_MAX_M))):
+        if STREAM_GEMM and M <= STREAM_GEMM_MAX_M:
+            return gemm_stream(x, w, out_dtype)
         return gemm_tc(x, w, out_dtype)
     if out_dtype == x.dtype:
         return torch.mm(x, w.t())

@@ -444,6 +444,50 @@ def test_gate_up_gemm_with_the_activation_in_its_epilogue(ops, M, I, K):
     ops.check_status()
 
 
+STREAM_SHAPES = [
+    # M <= 128, N, K: one tile, tiles cut between CTAs, ragged edges, many tiles, long K
+    (1, 128, 64), (8, 6144, 4096), (3, 200, 72), (16, 1000, 264), (17, 333, 1024), (64, 4096, 14336),
+    (100, 130, 520), (128, 256, 128), (48, 5120, 3072), (8, 100000, 256), (128, 3072, 8192), (2, 128, 16384),
+]
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", STREAM_SHAPES)
+def test_equal_shares_gemm(ops, M, N, K, out_dtype):
+    g = torch.Generator(device=DEV).manual_seed(M * 7 + N)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) / K ** 0.5).bfloat16()
+    got = ops.gemm_stream(x, w, out_dtype)
+    torch.cuda.synchronize()
+    ops.check_status()
+    want = x.float() @ w.float().T
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-4)
+    else:
+        torch.testing.assert_close(got.float(), want.bfloat16().float(), rtol=2e-2, atol=2e-2)
+    again = ops.gemm_stream(x, w, out_dtype)          # the tile counters were left at zero, the sums keep their order
+    assert torch.equal(got, again)
+    ops.check_status()
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 64, 64), (8, 14336, 4096), (5, 192, 72), (64, 256, 96), (128, 128, 264),
+                                   (48, 8192, 3072), (100, 1088, 520)])
+def test_equal_shares_gate_up_gemm(ops, M, I, K):
+    g = torch.Generator(device=DEV).manual_seed(M + I)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    wg = (torch.randn(I, K, device=DEV, generator=g) / K ** 0.5).bfloat16()
+    wu = (torch.randn(I, K, device=DEV, generator=g) / K ** 0.5).bfloat16()
+    w13 = ops.interleave_gate_up(wg, wu)
+    got = ops.gemm_stream(x, w13, torch.bfloat16, glu=True)
+    torch.cuda.synchronize()
+    ops.check_status()
+    gate, up = x.float() @ wg.float().T, x.float() @ wu.float().T
+    want = gate * torch.sigmoid(gate) * up
+    assert got.shape == (M, I)
+    torch.testing.assert_close(got.float(), want, rtol=3e-2, atol=3e-2)
+    assert torch.equal(got, ops.gemm_stream(x, w13, torch.bfloat16, glu=True))
+
+
 def test_silu_mul_layouts(ops):
     g = torch.Generator(device=DEV).manual_seed(3)
     for dtype in (torch.float32, torch.bfloat16):
