@@ -144,8 +144,18 @@ def _require_cuda(*tensors):
             raise KernelError("batchspec_b200 kernels run on a CUDA device only; got a tensor on " + str(t.device))
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_device_index = [None]
+
+
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """Handle of torch's current stream on the current device.  Asked for at every launch (a graph capture
+    switches streams), so through the one call that does nothing else."""
+    if _raw_stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    if _device_index[0] is None:
+        _device_index[0] = torch.cuda.current_device()
+    return _raw_stream(_device_index[0])
 
 
 def _check(err: int, name: str) -> None:
