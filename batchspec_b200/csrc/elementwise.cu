@@ -333,6 +333,73 @@ __global__ void rope_kv_append_kernel(T* __restrict__ qkv, int Hq, int Hkv, int 
   }
 }
 
+// The same for bfloat16 rows with the half-split pairing over the whole head (rot == hd, hd a multiple of 16): every
+// thread rotates eight neighbouring dims of the first half with their partners in the second half through 16-byte
+// loads and stores; v heads are copied 16 bytes at a time.  One block per (token, share of the token's work).
+__global__ void __launch_bounds__(256)
+rope_kv_append_vec_kernel(__nv_bfloat16* __restrict__ qkv, int Hq, int Hkv, int hd, const float* __restrict__ inv_freq,
+                          const int* __restrict__ positions, const int* __restrict__ tok_entry,
+                          const int* __restrict__ kv_indptr, const int* __restrict__ kv_indices,
+                          __nv_bfloat16* __restrict__ cache, int page_size, int write_kv) {
+  bspec::pdl_prologue(5);
+  extern __shared__ float cs[];  // [hd/2] cos, [hd/2] sin
+  const int t = blockIdx.x, half = hd / 2;
+  const int pos = positions[t];
+  for (int j = threadIdx.x; j < half; j += blockDim.x) {
+    float s, c;
+    sincosf((float)pos * inv_freq[j], &s, &c);
+    cs[j] = c;
+    cs[half + j] = s;
+  }
+  __syncthreads();
+  const int n_slots = Hq + 2 * Hkv;
+  __nv_bfloat16* row = qkv + (size_t)t * n_slots * hd;
+  __nv_bfloat16* kdst = nullptr;
+  __nv_bfloat16* vdst = nullptr;
+  if (write_kv) {
+    const int e = tok_entry[t];
+    const int page = kv_indices[kv_indptr[e] + pos / page_size];
+    const size_t page_elems = (size_t)Hkv * page_size * hd;
+    kdst = cache + ((size_t)page * 2) * page_elems + (size_t)(pos % page_size) * hd;
+    vdst = kdst + page_elems;
+  }
+  const int per_rot = half / 8;                 // items per rotated head: eight pairs each
+  const int n_rot = (Hq + Hkv) * per_rot;
+  const int per_v = hd / 8;                     // items per v head: eight elements each
+  const int n_items = n_rot + (write_kv ? Hkv * per_v : 0);
+  for (int w = blockIdx.y * blockDim.x + threadIdx.x; w < n_items; w += gridDim.y * blockDim.x) {
+    if (w >= n_rot) {
+      const int h = (w - n_rot) / per_v, c8 = (w - n_rot) - h * per_v;
+      *reinterpret_cast<uint4*>(vdst + (size_t)h * page_size * hd + 8 * c8) =
+          *reinterpret_cast<const uint4*>(row + (size_t)(Hq + Hkv + h) * hd + 8 * c8);
+      continue;
+    }
+    const int h = w / per_rot, j0 = 8 * (w - h * per_rot);
+    __nv_bfloat16* x = row + (size_t)h * hd;
+    const uint4 lo = *reinterpret_cast<const uint4*>(x + j0), hi = *reinterpret_cast<const uint4*>(x + half + j0);
+    const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(&lo);
+    const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(&hi);
+    uint4 out_lo, out_hi;
+    __nv_bfloat16* ya = reinterpret_cast<__nv_bfloat16*>(&out_lo);
+    __nv_bfloat16* yb = reinterpret_cast<__nv_bfloat16*>(&out_hi);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float xa = __bfloat162float(a[i]), xb = __bfloat162float(b[i]);
+      const float c = cs[j0 + i], sn = cs[half + j0 + i];
+      ya[i] = __float2bfloat16_rn(xa * c - xb * sn);
+      yb[i] = __float2bfloat16_rn(xa * sn + xb * c);
+    }
+    if (h < Hq) {
+      *reinterpret_cast<uint4*>(x + j0) = out_lo;
+      *reinterpret_cast<uint4*>(x + half + j0) = out_hi;
+    } else if (write_kv) {
+      __nv_bfloat16* kd = kdst + (size_t)(h - Hq) * page_size * hd;
+      *reinterpret_cast<uint4*>(kd + j0) = out_lo;
+      *reinterpret_cast<uint4*>(kd + half + j0) = out_hi;
+    }
+  }
+}
+
 BSPEC_API int bspec_rope_kv_append(void* qkv, int dtype, int n, int Hq, int Hkv, int hd, const float* inv_freq, int rot,
                                    int interleaved, const int* positions, const int* tok_entry, const int* kv_indptr,
                                    const int* kv_indices, void* cache, int page_size, int write_kv,
@@ -340,6 +407,13 @@ BSPEC_API int bspec_rope_kv_append(void* qkv, int dtype, int n, int Hq, int Hkv,
   if (n <= 0) return 0;
   const int threads = 128;
   const size_t smem = (size_t)(rot > 0 ? rot : 0) * sizeof(float);
+  if (dtype == BSPEC_BF16 && rot == hd && !interleaved && hd % 16 == 0 && n >= 64 &&
+      (reinterpret_cast<uintptr_t>(qkv) & 15) == 0 && (reinterpret_cast<uintptr_t>(cache) & 15) == 0) {
+    // many tokens: one block per token (or two while they are few) with 16-byte accesses
+    BSPEC_LAUNCH((rope_kv_append_vec_kernel), dim3(n, n >= 512 ? 1 : 2), 256, smem, stream, (__nv_bfloat16*)qkv, Hq, Hkv, hd,
+                 inv_freq, positions, tok_entry, kv_indptr, kv_indices, (__nv_bfloat16*)cache, page_size, write_kv);
+    return BSPEC_LAUNCH_CHECK();
+  }
   dim3 grid(n, (Hq + 2 * Hkv + ROPE_HEADS_PER_BLOCK - 1) / ROPE_HEADS_PER_BLOCK);
   if (grid.y > 65535) return (int)cudaErrorInvalidConfiguration;
   if (dtype == BSPEC_F32)

@@ -414,3 +414,174 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
         ref = oracle(toks)
         for p_ in range(len(toks)):
             assert H.rel_err(got[(rid, p_)], ref[p_]) <= H.TOL["float32"], (rid, p_)
+
+
+# ------------------------------------- run order as data; a routed feed-forward and another position encoding as toys
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_run_order_shared_cache_window_and_toy_parts(tmp_path, dtype):
+    """An architecture defined here, with everything the model description allows at once: two layers run four
+    times (layer 0, layer 1, layer 0 again with a cache of its own, layer 1 again reading the cache its first run
+    wrote); layer 1's attention sees a window of 5 keys (so its pages are a pool of their own and are given back
+    as the window passes) and uses a position encoding registered here (no rotation: q and k are scaled by
+    exp(+-rate * dim * position), which makes scores depend on distance); layer 1's feed-forward is a routed toy
+    registered here (router logits in 32-bit, the best 2 of 3 experts, weights renormalised; see TOPK).  Stepped whole, in
+    portions and mixed with reused pages and compared with an oracle written out below."""
+    from dataclasses import dataclass
+    from batchspec_b200.config import config_from_json_dict, register_config_class
+    from batchspec_b200.engine import Engine
+    from batchspec_b200.models import LayerSpec, ModelSpec, RunEntry, register_model
+    from batchspec_b200.parts import (FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, ParamSpec, PartSpec,
+                                      PositionEncoding, register_part)
+    from batchspec_b200.weights import write_random_model
+
+    W, HD, HQ, HKV, WINDOW, RATE, E, INNER = 32, 16, 2, 1, 5, 0.004, 3, 24
+    # the best 2 of 3 experts in 32-bit; in bfloat16 all 3 are weighed, because a near tie between the second and
+    # the third would flip the choice on rounding alone and the comparison with the oracle would test luck
+    TOPK = 2 if dtype == "float32" else 3
+    OUT_SCALE = 1.0
+
+    @register_part(POSITION_ENCODINGS, "toy_distance_scale")
+    class ToyDistanceScale(PositionEncoding):
+        def __init__(self, runtime, head_dim, rate):
+            self.runtime, self.rate = runtime, rate
+            self.dims = torch.arange(head_dim, dtype=torch.float32, device=runtime.device)
+
+        def param_specs(self):
+            return {}
+
+        def bind(self, params):
+            pass
+
+        def apply(self, q, k, ctx):
+            f = torch.exp(self.rate * ctx.positions.float()[:, None, None] * self.dims)      # [n, 1, hd], 32-bit
+            q.copy_((q.float() * f).to(q.dtype))
+            k.copy_((k.float() / f).to(k.dtype))
+
+    @register_part(FEED_FORWARDS, "toy_routed")
+    class ToyRouted(FeedForward):
+        def __init__(self, runtime, dim, inner, experts, top_k, out_scale):
+            self.runtime, self.dim, self.inner, self.experts, self.top_k = runtime, dim, inner, experts, top_k
+            self.out_scale = out_scale
+
+        def param_specs(self):
+            return {"router": ParamSpec((self.experts, self.dim)), "w1": ParamSpec((self.experts * self.inner, self.dim)),
+                    "w2": ParamSpec((self.experts * self.dim, self.inner))}
+
+        def bind(self, params):
+            self.router = params["router"].float()
+            self.w1 = params["w1"].view(self.experts, self.inner, self.dim)
+            self.w2 = params["w2"].view(self.experts, self.dim, self.inner)
+
+        def forward(self, x, ctx):
+            logits = x.float() @ self.router.T                                   # 32-bit router
+            top, idx = torch.topk(logits, self.top_k, dim=-1)
+            gate = torch.softmax(top, dim=-1)
+            out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+            for e in range(self.experts):
+                h = torch.relu(x @ self.w1[e].T)
+                y = (h @ self.w2[e].T).float()
+                out += y * (gate * (idx == e)).sum(-1, keepdim=True)
+            return (out * self.out_scale).to(x.dtype)
+
+    @dataclass(frozen=True)
+    class MixConfig:
+        architecture: str
+        vocab_size: int
+        eps: float
+
+        @classmethod
+        def from_json_dict(cls, d):
+            return cls(d["architectures"][0], d["vocab_size"], d["eps"])
+
+        def to_json_dict(self):
+            return dict(architectures=[self.architecture], vocab_size=self.vocab_size, eps=self.eps)
+
+    def build(cfg):
+        norm = PartSpec("rmsnorm", dict(dim=W, eps=cfg.eps))
+        att0 = PartSpec("attention", dict(dim=W, n_heads=HQ, n_kv_heads=HKV, head_dim=HD,
+                                          position=PartSpec("rope", dict(head_dim=HD, theta=100.0))))
+        att1 = PartSpec("attention", dict(dim=W, n_heads=HQ, n_kv_heads=HKV, head_dim=HD, window=WINDOW,
+                                          position=PartSpec("toy_distance_scale", dict(head_dim=HD, rate=RATE))))
+        ffn0 = PartSpec("swiglu", dict(dim=W, intermediate=40))
+        ffn1 = PartSpec("toy_routed", dict(dim=W, inner=INNER, experts=E, top_k=TOPK, out_scale=OUT_SCALE))
+        names0 = {"norm1.weight": "a.n1", "norm2.weight": "a.n2", "ffn.gate": "a.gate", "ffn.up": "a.up", "ffn.down": "a.down"}
+        names0.update({"mixer." + k: "a." + k for k in "qkvo"})
+        names1 = {"norm1.weight": "b.n1", "norm2.weight": "b.n2", "ffn.router": "b.router", "ffn.w1": "b.w1", "ffn.w2": "b.w2"}
+        names1.update({"mixer." + k: "b." + k for k in "qkvo"})
+        layers = [LayerSpec(norm, att0, norm, ffn0, names0), LayerSpec(norm, att1, norm, ffn1, names1)]
+        order = [RunEntry(0), RunEntry(1), RunEntry(0), RunEntry(1, cache_from=1)]
+        return ModelSpec(cfg.vocab_size, W, layers, order, norm, "emb", {"weight": "final"}, None)
+
+    register_config_class("ToyMixLM", MixConfig)
+    register_model("ToyMixLM", build)
+    cfg = config_from_json_dict(dict(architectures=["ToyMixLM"], vocab_size=53, eps=1e-5))
+    folder = write_random_model(cfg, tmp_path, seed=9, dtype=torch.float32 if dtype == "float32" else torch.bfloat16,
+                                std=0.08, norm_std=0.1)
+    _, w = P.read_model_folder(folder)
+
+    def rope(t, T):
+        f = 100.0 ** (-2.0 * torch.arange(HD // 2, dtype=torch.float64) / HD)
+        ang = torch.arange(T, dtype=torch.float64)[:, None] * f[None]
+        c, sn = torch.cos(ang)[:, None], torch.sin(ang)[:, None]
+        h = HD // 2
+        return torch.cat([t[..., :h] * c - t[..., h:] * sn, t[..., :h] * sn + t[..., h:] * c], -1)
+
+    def oracle(tokens):
+        T = len(tokens)
+        x = w["emb"][torch.tensor(tokens)]
+        dist = torch.exp(RATE * torch.arange(T, dtype=torch.float64)[:, None, None] * torch.arange(HD, dtype=torch.float64))
+        kept = {}
+        for run, (layer, reads) in enumerate([("a", None), ("b", None), ("a", None), ("b", 1)]):
+            a = P.rms_norm(x, w[f"{layer}.n1"], cfg.eps)
+            q = (a @ w[f"{layer}.q"].T).reshape(T, HQ, HD)
+            k = (a @ w[f"{layer}.k"].T).reshape(T, HKV, HD)
+            v = (a @ w[f"{layer}.v"].T).reshape(T, HKV, HD)
+            if layer == "a":
+                q, k = rope(q, T), rope(k, T)
+                window = None
+            else:
+                q, k = q * dist, k / dist
+                window = WINDOW
+            if reads is None:
+                kept[run] = (k, v)
+            else:
+                k, v = kept[reads]                           # the keys and values its first run cached
+            y = P.causal_attention(q, k, v, window=window).reshape(T, HQ * HD) @ w[f"{layer}.o"].T
+            h = x + y
+            n2 = P.rms_norm(h, w[f"{layer}.n2"], cfg.eps)
+            if layer == "a":
+                f = P.swiglu(n2, torch.cat([w["a.gate"], w["a.up"]]), w["a.down"])
+            else:
+                logits = n2 @ w["b.router"].T
+                top, idx = torch.topk(logits, TOPK, dim=-1)
+                gate = torch.softmax(top, dim=-1)
+                f = torch.zeros_like(n2)
+                for e in range(E):
+                    w1, w2 = w["b.w1"][e * INNER:(e + 1) * INNER], w["b.w2"][e * W:(e + 1) * W]
+                    f += (torch.relu(n2 @ w1.T) @ w2.T) * (gate * (idx == e)).sum(-1, keepdim=True)
+                f = f * OUT_SCALE
+            x = h + f
+        return (P.rms_norm(x, w["final"], cfg.eps) @ w["emb"].T).numpy()
+
+    eng = Engine(dtype=dtype, device="cuda:0")
+    eng.load_model(model_dir=folder)
+    eng.setup_caches(max_batch_size=3, max_seq_length=48, page_size=4, num_pages=[40, 24])
+    needs = eng.model.cache_needs()
+    assert [n.cache_from for n in needs] == [None, None, None, 1]
+    assert len(eng.cache.groups) == 2 and [g.spec.policy for g in eng.cache.groups] == ["full", "window"]
+    assert [len(g.runs) for g in eng.cache.groups] == [2, 1], "layer 0 twice owns two caches, the reader none"
+    reqs = {f"m{i}": H.random_tokens(n, 53, 70 + i) for i, n in enumerate((19, 30, 7, 26))}
+    tol = H.TOL[dtype]
+    for rid, toks in reqs.items():
+        ref = oracle(toks)
+        for sched in (H.whole(rid, toks), H.portions(rid, toks, [4, 2, 7, 3])):
+            got = H.run_steps_in_process(eng, sched)
+            for p_ in range(len(toks)):
+                assert H.rel_err(got[(rid, p_)], ref[p_]) <= tol, (rid, p_, dtype)
+    got = H.run_steps_in_process(eng, H.mixed(reqs, seed=2, max_live=3))
+    for rid, toks in reqs.items():
+        ref = oracle(toks)
+        for p_ in range(len(toks)):
+            assert H.rel_err(got[(rid, p_)], ref[p_]) <= tol, (rid, p_, dtype)
+    eng.cache.check_invariants()

@@ -109,11 +109,13 @@ def _rope_reference(x, pos, inv_freq, rot, interleaved):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("lens", [[3, 1, 9], [70, 1, 200], [600]])           # few tokens; many (16-byte path in bfloat16)
 @pytest.mark.parametrize("Hq,Hkv,hd,rot,inter,ps", [(4, 2, 16, 16, False, 4), (3, 1, 32, 32, True, 1),
-                                                     (6, 3, 48, 24, False, 5), (32, 8, 128, 128, False, 16)])
-def test_rope_and_cache_append(ops, dtype, Hq, Hkv, hd, rot, inter, ps):
+                                                     (6, 3, 48, 24, False, 5), (32, 8, 128, 128, False, 16),
+                                                     (5, 1, 80, 80, False, 8)])
+def test_rope_and_cache_append(ops, dtype, Hq, Hkv, hd, rot, inter, ps, lens):
     g = torch.Generator(device=DEV).manual_seed(5)
-    lens, before = [3, 1, 9], [0, 6, 11]                         # three requests: new tokens, tokens already cached
+    before = [0, 6, 11][:len(lens)]                              # new tokens per request after tokens already cached
     n = sum(lens)
     qkv = torch.randn(n, (Hq + 2 * Hkv) * hd, device=DEV, generator=g).to(dtype)
     inv_freq = (10000.0 ** (-torch.arange(0, rot // 2, device=DEV).float() * 2 / rot))
