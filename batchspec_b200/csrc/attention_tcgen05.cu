@@ -26,8 +26,9 @@ constexpr int HD = 128;
 constexpr int ROWS = 128;            // rows per Q tile = accumulator lanes
 constexpr int QT = 2;                // Q tiles per CTA
 constexpr int KT = 64;               // keys per tile
-constexpr int STAGES = 3;
-constexpr int THREADS = 32 * (2 + 4 * QT);
+constexpr int STAGES = 4;
+constexpr int MMA_WARP_1 = 2 + 4 * QT;                 // the second Q tile's MMA warp: after the softmax warps
+constexpr int THREADS = 32 * (3 + 4 * QT);
 constexpr int SUBQ = ROWS * 64;      // elements of a [128][64] sub-tile (16 KB): Q halves, P
 constexpr int SUBK = KT * 64;        // elements of a [64][64] sub-tile (8 KB): K and V halves
 constexpr int QTILE = 2 * SUBQ;      // [128][128] Q tile
@@ -154,7 +155,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(kv_full + s, 1);
-      mbar_init(kv_empty + s, 1);
+      mbar_init(kv_empty + s, QT);      // one arrival per Q tile's MMA thread
     }
     for (int i = 0; i < 2 * QT; ++i) {
       mbar_init(s_full + i, 1);
@@ -213,59 +214,65 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issue
+  } else if (warp == 1 || warp == MMA_WARP_1) {
+    // ------------------------------------------------------------------ MMA issue, one thread per Q tile
+    // A wait on an mbarrier costs this thread some 300 cycles even when the barrier is long complete, and its
+    // tcgen05.mma instructions block while the tensor core's queue is full: with one thread for both Q tiles the
+    // waits and the issues of the two tiles stood in one line and that line was the kernel's critical path.  Each
+    // Q tile now has its own issuing thread (in different warps); the tensor core takes from both.
+    const int tt = warp == 1 ? 0 : 1;
     if (lane == 0) {
       const uint32_t id_s = idesc(KT, false), id_o = idesc(HD, true);
+      const int my_tiles = n_kt[tt];
       bool ok = true;
-      for (int tt = 0; tt < QT && ok; ++tt)
-        if (n_kt[tt] > 0) ok = mbar_wait(q_ready + tt, 0, abort_flag, status, 32);
+      if (my_tiles > 0) ok = mbar_wait(q_ready + tt, 0, abort_flag, status, 32);
       tc_fence_after();
-      // S_{t,j} = Q_t K_j^T into S buffer j & 1 of every Q tile that still sees key tile j
+      const uint64_t qdesc = desc_kmajor(Qs + tt * QTILE), pdesc = desc_kmajor(Ps + tt * SUBQ);
+      // S_j = Q K_j^T into S buffer j & 1
       auto issue_s = [&](int j) -> bool {
-        const int st = j % STAGES, b = j & 1;
+        const int st = j % STAGES, bf = j & 1;
         if (!mbar_wait(kv_full + st, (uint32_t)(j / STAGES) & 1u, abort_flag, status, 33)) return false;
+        // the buffer was last used by key tile j - 2: the softmax must have read it
+        if (j >= 2 && !mbar_wait(s_read + 2 * tt + bf, (uint32_t)((j - 2) >> 1) & 1u, abort_flag, status, 34)) return false;
+        tc_fence_after();
         const uint64_t kdesc = desc_kmajor(KV + (size_t)st * 2 * KTILE);
-        for (int tt = 0; tt < QT; ++tt) {
-          if (j >= n_kt[tt]) continue;
-          // the buffer was last used by key tile j - 2: its softmax must have read it
-          if (j >= 2 && !mbar_wait(s_read + 2 * tt + b, (uint32_t)((j - 2) >> 1) & 1u, abort_flag, status, 34)) return false;
-          tc_fence_after();
-          const uint64_t qdesc = desc_kmajor(Qs + tt * QTILE);
-          const uint32_t d = tmem + (uint32_t)(tt * 128 + b * 64);
+        const uint32_t d = tmem + (uint32_t)(tt * 128 + bf * 64);
 #pragma unroll
-          for (int ks = 0; ks < HD / 16; ++ks) {
-            const uint64_t a_off = (uint64_t)((ks >> 2) * ((SUBQ * 2) >> 4) + 2 * (ks & 3));
-            const uint64_t b_off = (uint64_t)((ks >> 2) * ((SUBK * 2) >> 4) + 2 * (ks & 3));
-            tc_mma(d, qdesc + a_off, kdesc + b_off, id_s, ks > 0 ? 1u : 0u);
-          }
-          tc_commit(s_full + 2 * tt + b);
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint64_t a_off = (uint64_t)((ks >> 2) * ((SUBQ * 2) >> 4) + 2 * (ks & 3));
+          const uint64_t b_off = (uint64_t)((ks >> 2) * ((SUBK * 2) >> 4) + 2 * (ks & 3));
+          tc_mma(d, qdesc + a_off, kdesc + b_off, id_s, ks > 0 ? 1u : 0u);
         }
+        tc_commit(s_full + 2 * tt + bf);
         return true;
       };
-      // S runs two key tiles ahead of P V (two S buffers per Q tile, three K/V stages)
-      for (int j = 0; j < 2 && j < n_tiles && ok; ++j) ok = issue_s(j);
+      // S runs two key tiles ahead of P V (two S buffers per Q tile, four K/V stages)
+      for (int j = 0; j < 2 && j < my_tiles && ok; ++j) ok = issue_s(j);
       for (int j = 0; j < n_tiles && ok; ++j) {
-        // O_t += P_{t,j} V_j
         const int st = j % STAGES;
-        const uint64_t vdesc = desc_mnmajor(KV + (size_t)st * 2 * KTILE + KTILE);
-        for (int tt = 0; tt < QT && ok; ++tt) {
-          if (j >= n_kt[tt]) continue;
-          ok = mbar_wait(p_ready + tt, (uint32_t)j & 1u, abort_flag, status, 35);
-          if (!ok) break;
-          tc_fence_after();
-          const uint64_t pdesc = desc_kmajor(Ps + tt * SUBQ);
-          const uint32_t d = tmem + (uint32_t)(256 + tt * 128);
-#pragma unroll
-          for (int kk = 0; kk < KT / 16; ++kk)        // 16 keys: 32 bytes along P's rows, 16 rows of V
-            tc_mma(d, pdesc + (uint64_t)(2 * kk), vdesc + (uint64_t)(kk * ((16 * 128) >> 4)), id_o,
-                   (j > 0 || kk > 0) ? 1u : 0u);
-          tc_commit(pv_done + tt);                     // O_t holds key tiles 0..j, P_t may be overwritten
+        if (j >= my_tiles) {
+          // Key tiles that only the other Q tile sees: this tile's share of the release of their stage, given once
+          // the tile has arrived (so that two of these cannot fall into one phase of the stage's barrier).
+          ok = mbar_wait(kv_full + st, (uint32_t)(j / STAGES) & 1u, abort_flag, status, 33);
+          if (ok) mbar_arrive(kv_empty + st);
+          continue;
         }
+        // S of key tile j + 2 first: its K arrived a step ago, its buffer is free as soon as the softmax of tile j
+        // has read it, and the tensor core works on it while that softmax computes
+        if (j + 2 < my_tiles) ok = issue_s(j + 2);
         if (!ok) break;
-        tc_commit(kv_empty + st);                      // K_j and V_j are no longer read
-        // S of key tile j + 2 (its K was fetched into the stage that P V_{j-1} released one tile ago)
-        if (j + 2 < n_tiles) ok = issue_s(j + 2);
+        // O += P_j V_j
+        ok = mbar_wait(p_ready + tt, (uint32_t)j & 1u, abort_flag, status, 35);
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t vdesc = desc_mnmajor(KV + (size_t)st * 2 * KTILE + KTILE);
+        const uint32_t d = tmem + (uint32_t)(256 + tt * 128);
+#pragma unroll
+        for (int kk = 0; kk < KT / 16; ++kk)          // 16 keys: 32 bytes along P's rows, 16 rows of V
+          tc_mma(d, pdesc + (uint64_t)(2 * kk), vdesc + (uint64_t)(kk * ((16 * 128) >> 4)), id_o,
+                 (j > 0 || kk > 0) ? 1u : 0u);
+        tc_commit(pv_done + tt);                       // O holds key tiles 0..j, P may be overwritten
+        tc_commit(kv_empty + st);                      // this Q tile no longer reads K_j and V_j
       }
     }
   } else {
@@ -321,16 +328,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
       if (lane == 0) mbar_arrive(s_read + 2 * tt + b);
       // maximum of the raw scores (the scale is positive), masked entries set to -inf in place
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (need_mask) {                     // a tile on the diagonal, at the window's edge or at the end of the keys
 #pragma unroll
-      for (int c = 0; c < 2; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          if (need_mask) {
+          for (int i = 0; i < 32; ++i) {
             const int key = key0 + 32 * c + i;
             if (!(key <= lim && key >= lo && key < my_k_end)) sv[c][i] = 0xff800000u;      // -inf
+            mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[c][i]));
           }
-          mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[c][i]));
-        }
+      } else {                             // most tiles: no comparisons of key indices at all
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[c][i]));
+      }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
       float corr = 1.f;
       if (mx > m_ref + 8.f || m_ref == -INFINITY) {           // (also the first tile that holds a visible key)
