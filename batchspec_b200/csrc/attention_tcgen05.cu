@@ -27,6 +27,10 @@ constexpr int ROWS = 128;            // rows per Q tile = accumulator lanes
 constexpr int QT = 2;                // Q tiles per CTA
 constexpr int KT = 64;               // keys per tile
 constexpr int STAGES = 4;
+#ifndef BSPEC_ATTN_EMU
+#define BSPEC_ATTN_EMU 3
+#endif
+constexpr int EMU = BSPEC_ATTN_EMU;   // every EMU-th pair of exponentials on the FMA pipe (0: none)
 constexpr int MMA_WARP_1 = 2 + 4 * QT;                 // the second Q tile's MMA warp: after the softmax warps
 constexpr int THREADS = 32 * (3 + 4 * QT);
 constexpr int SUBQ = ROWS * 64;      // elements of a [128][64] sub-tile (16 KB): Q halves, P
@@ -72,6 +76,18 @@ __device__ __forceinline__ float ex2(float x) {          // 2^x on the special-f
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// 2^x without the special-function unit: round x to the nearest integer n by adding 1.5 * 2^23 (n then sits in the
+// sum's low mantissa bits), a cubic for 2^(x - n) on [-0.5, 0.5] (relative error 7.5e-5, far below bfloat16's
+// step), and n added to the exponent.  x <= 8 here; below -126 the result is about 1e-38.
+__device__ __forceinline__ float ex2_fma(float x) {
+  x = fmaxf(x, -126.f);
+  const float t = x + 12582912.f;
+  const float f = x - (t - 12582912.f);
+  float p = fmaf(0.05517165f, f, 0.24261113f);
+  p = fmaf(p, f, 0.69326097f);
+  p = fmaf(p, f, 0.99992806f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -355,16 +371,34 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
       // exponentials first (they do not need P's buffer), then wait until the previous P V has completed
       float l4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t packed[32];
+      if (need_mask) {
 #pragma unroll
-      for (int c = 0; c < 2; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float p0 = ex2(fmaf(__uint_as_float(sv[c][i]), scale_log2, neg_m));
-          const float p1 = ex2(fmaf(__uint_as_float(sv[c][i + 1]), scale_log2, neg_m));
-          l4[(i >> 1) & 3] += p0 + p1;
-          __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
-          packed[16 * c + (i >> 1)] = *reinterpret_cast<uint32_t*>(&hh);
-        }
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = ex2(fmaf(__uint_as_float(sv[c][i]), scale_log2, neg_m));
+            const float p1 = ex2(fmaf(__uint_as_float(sv[c][i + 1]), scale_log2, neg_m));
+            l4[(i >> 1) & 3] += p0 + p1;
+            __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+            packed[16 * c + (i >> 1)] = *reinterpret_cast<uint32_t*>(&hh);
+          }
+      } else {
+        // The special-function unit makes 16 exponentials per clock and SM, which is as long as the tensor core
+        // needs for the two products of the tile: every EMU-th pair of exponentials goes to the FMA pipe instead.
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float x0 = fmaf(__uint_as_float(sv[c][i]), scale_log2, neg_m);
+            const float x1 = fmaf(__uint_as_float(sv[c][i + 1]), scale_log2, neg_m);
+            const bool emu = EMU > 0 && ((i >> 1) % EMU) == EMU - 1;
+            const float p0 = emu ? ex2_fma(x0) : ex2(x0);
+            const float p1 = emu ? ex2_fma(x1) : ex2(x1);
+            l4[(i >> 1) & 3] += p0 + p1;
+            __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+            packed[16 * c + (i >> 1)] = *reinterpret_cast<uint32_t*>(&hh);
+          }
+      }
       l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       if (j >= 1) {
         ok = mbar_wait(pv_done + tt, (uint32_t)(j - 1) & 1u, abort_flag, status, 37);
