@@ -5,16 +5,22 @@
 // of 128 rows with a softmax warpgroup each, and walks the visible keys in tiles of 64:
 //   warp 0    TMA: K and V pages of the key tile into a three-stage ring (one box per page and 64-column half,
 //             128-byte swizzle, completion on an mbarrier);
-//   warp 1    one thread issues tcgen05.mma for both Q tiles:  S = Q K^T  (128 x 64 x 128, operands K-major in
-//             shared memory) into one of the tile's two S buffers in tensor memory, and  O += P V  (A = P in
-//             shared memory, B = V read MN-major straight from the loaded pages) into the tile's O accumulator;
+//   warps 1, 10   one thread each issues tcgen05.mma for Q tile 0 / 1:  S = Q K^T  (128 x 64 x 128, operands
+//             K-major in shared memory) into one of the tile's two S buffers in tensor memory, and  O += P V
+//             (A = P in shared memory, B = V read MN-major straight from the loaded pages) into the tile's O
+//             accumulator.  S runs two key tiles ahead; P V of tile j is issued the moment P_j is announced.
 //   warps 2-5 / 6-9   Q tile 0 / 1, one thread per row: read its S row from tensor memory, scale, mask, online
-//             softmax in float32, write P (bfloat16) into shared memory in the operand layout, rescale its O row
-//             in tensor memory when its scale moved, and at the end normalise and store O.
-// While one warpgroup does the softmax of its tile the tensor core works for the other, and S of key tile j+1 is
-// computed while the softmax of tile j runs.  Tensor memory: 2 x 2 S buffers of 64 columns, 2 O accumulators of
-// 128 (all 512 columns).  Every mbarrier wait is bounded; on expiry a code goes to `status`, all roles stop and
-// the tensor memory is given back.
+//             softmax in float32 (a third of the exponentials as a cubic on the FMA pipe, the rest on the
+//             special-function unit, which alone would be as slow as the tensor core), write P (bfloat16) into
+//             one of the tile's two P buffers in shared memory in the operand layout, rescale its O row in tensor
+//             memory when its scale moved, and at the end normalise and store O.
+// The softmax of a tile never waits for the tensor core in the steady state: S of the next key tile is ready, and
+// its P goes to the buffer that the P V before last has long released.  The issuing threads are two, in different
+// warps, because they share their schedulers with softmax warps whose long runs of independent instructions keep
+// them waiting some 300 cycles at every mbarrier they look at: with one thread for both Q tiles those waits and
+// the (blocking) issues of both tiles stood in one line, and that line was the kernel's critical path.
+// Tensor memory: 2 x 2 S buffers of 64 columns, 2 O accumulators of 128 (all 512 columns).  Every mbarrier wait is
+// bounded; on expiry a code goes to `status`, all roles stop and the tensor memory is given back.
 #include "common.cuh"
 #include "tma.cuh"
 #include <math.h>
@@ -26,7 +32,7 @@ constexpr int HD = 128;
 constexpr int ROWS = 128;            // rows per Q tile = accumulator lanes
 constexpr int QT = 2;                // Q tiles per CTA
 constexpr int KT = 64;               // keys per tile
-constexpr int STAGES = 4;
+constexpr int STAGES = 3;
 #ifndef BSPEC_ATTN_EMU
 #define BSPEC_ATTN_EMU 3
 #endif
@@ -112,7 +118,7 @@ struct Geom {
   int q_begin, q_len, pos0, G, rows_total;
 };
 
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bfloat16* __restrict__ q,
                        long long q_row_stride, __nv_bfloat16* __restrict__ out, int* __restrict__ status,
                        const int* __restrict__ qo_indptr, const int* __restrict__ positions,
@@ -122,16 +128,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem);                  // QT x [128][128]
-  __nv_bfloat16* Ps = Qs + QT * QTILE;                                         // QT x [128][64]
-  __nv_bfloat16* KV = Ps + QT * SUBQ;                                          // STAGES x (K tile, V tile)
+  __nv_bfloat16* Ps = Qs + QT * QTILE;                                         // QT x 2 buffers x [128][64]
+  __nv_bfloat16* KV = Ps + QT * 2 * SUBQ;                                      // STAGES x (K tile, V tile)
   uint64_t* bars = reinterpret_cast<uint64_t*>(KV + STAGES * 2 * KTILE);
   uint64_t* kv_full = bars;                        // [STAGES]
   uint64_t* kv_empty = kv_full + STAGES;           // [STAGES]
   uint64_t* s_full = kv_empty + STAGES;            // [QT][2]
-  uint64_t* s_read = s_full + 2 * QT;              // [QT][2]
-  uint64_t* p_ready = s_read + 2 * QT;             // [QT]
-  uint64_t* pv_done = p_ready + QT;                // [QT]
-  uint64_t* q_ready = pv_done + QT;                // [QT]
+  uint64_t* p_ready = s_full + 2 * QT;             // [QT][2]
+  uint64_t* pv_done = p_ready + 2 * QT;            // [QT][2]
+  uint64_t* q_ready = pv_done + 2 * QT;            // [QT]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_ready + QT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -175,13 +180,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
     }
     for (int i = 0; i < 2 * QT; ++i) {
       mbar_init(s_full + i, 1);
-      mbar_init(s_read + i, 4);
-    }
-    for (int i = 0; i < QT; ++i) {
       mbar_init(p_ready + i, 4);
       mbar_init(pv_done + i, 1);
-      mbar_init(q_ready + i, 4);
     }
+    for (int i = 0; i < QT; ++i) mbar_init(q_ready + i, 4);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -243,13 +245,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
       bool ok = true;
       if (my_tiles > 0) ok = mbar_wait(q_ready + tt, 0, abort_flag, status, 32);
       tc_fence_after();
-      const uint64_t qdesc = desc_kmajor(Qs + tt * QTILE), pdesc = desc_kmajor(Ps + tt * SUBQ);
+      const uint64_t qdesc = desc_kmajor(Qs + tt * QTILE);
       // S_j = Q K_j^T into S buffer j & 1
       auto issue_s = [&](int j) -> bool {
         const int st = j % STAGES, bf = j & 1;
         if (!mbar_wait(kv_full + st, (uint32_t)(j / STAGES) & 1u, abort_flag, status, 33)) return false;
-        // the buffer was last used by key tile j - 2: the softmax must have read it
-        if (j >= 2 && !mbar_wait(s_read + 2 * tt + bf, (uint32_t)((j - 2) >> 1) & 1u, abort_flag, status, 34)) return false;
+        // The buffer was last used by key tile j - 2.  Its softmax read S out of it before it announced P of that
+        // tile, and this thread has seen that announcement (it issued the P V of tile j - 2): no wait here.
         tc_fence_after();
         const uint64_t kdesc = desc_kmajor(KV + (size_t)st * 2 * KTILE);
         const uint32_t d = tmem + (uint32_t)(tt * 128 + bf * 64);
@@ -262,7 +264,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
         tc_commit(s_full + 2 * tt + bf);
         return true;
       };
-      // S runs two key tiles ahead of P V (two S buffers per Q tile, four K/V stages)
+      // S runs two key tiles ahead of P V (two S buffers and two P buffers per Q tile, three K/V stages)
       for (int j = 0; j < 2 && j < my_tiles && ok; ++j) ok = issue_s(j);
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int st = j % STAGES;
@@ -273,22 +275,23 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
           if (ok) mbar_arrive(kv_empty + st);
           continue;
         }
-        // S of key tile j + 2 first: its K arrived a step ago, its buffer is free as soon as the softmax of tile j
-        // has read it, and the tensor core works on it while that softmax computes
-        if (j + 2 < my_tiles) ok = issue_s(j + 2);
-        if (!ok) break;
-        // O += P_j V_j
-        ok = mbar_wait(p_ready + tt, (uint32_t)j & 1u, abort_flag, status, 35);
+        // O += P_j V_j, as soon as the softmax has written P_j: the softmax of tile j + 1 then never waits for it
+        // (its P goes to the other buffer), and the tensor core has S of tiles j + 1 and j + 2 to work on meanwhile
+        const int bf = j & 1;
+        ok = mbar_wait(p_ready + 2 * tt + bf, (uint32_t)(j >> 1) & 1u, abort_flag, status, 35);
         if (!ok) break;
         tc_fence_after();
+        const uint64_t pdesc = desc_kmajor(Ps + (tt * 2 + bf) * SUBQ);
         const uint64_t vdesc = desc_mnmajor(KV + (size_t)st * 2 * KTILE + KTILE);
         const uint32_t d = tmem + (uint32_t)(256 + tt * 128);
 #pragma unroll
         for (int kk = 0; kk < KT / 16; ++kk)          // 16 keys: 32 bytes along P's rows, 16 rows of V
           tc_mma(d, pdesc + (uint64_t)(2 * kk), vdesc + (uint64_t)(kk * ((16 * 128) >> 4)), id_o,
                  (j > 0 || kk > 0) ? 1u : 0u);
-        tc_commit(pv_done + tt);                       // O holds key tiles 0..j, P may be overwritten
+        tc_commit(pv_done + 2 * tt + bf);              // O holds key tiles 0..j, this P buffer may be overwritten
         tc_commit(kv_empty + st);                      // this Q tile no longer reads K_j and V_j
+        // S of key tile j + 2 (its K was fetched into the stage that the P V of tile j - 1 released)
+        if (j + 2 < my_tiles) ok = issue_s(j + 2);
       }
     }
   } else {
@@ -325,7 +328,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
     // float32 and bfloat16), which after the first tiles is rare.
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
-    unsigned char* pdst = reinterpret_cast<unsigned char*>(Ps + tt * SUBQ) + row * 128;
+    unsigned char* pdst0 = reinterpret_cast<unsigned char*>(Ps + tt * 2 * SUBQ) + row * 128;
     for (int j = 0; j < my_tiles && ok; ++j) {
       const int b = j & 1;
       ok = mbar_wait(s_full + 2 * tt + b, (uint32_t)(j >> 1) & 1u, abort_flag, status, 36);
@@ -339,9 +342,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
       tc_ld32(s_addr, sv[0]);
       tc_ld32(s_addr + 32u, sv[1]);
       tc_wait_ld();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_read + 2 * tt + b);
       // maximum of the raw scores (the scale is positive), masked entries set to -inf in place
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {                     // a tile on the diagonal, at the window's edge or at the end of the keys
@@ -400,17 +400,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
           }
       }
       l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-      if (j >= 1) {
-        ok = mbar_wait(pv_done + tt, (uint32_t)(j - 1) & 1u, abort_flag, status, 37);
+      // this tile's P buffer was last read by the P V of key tile j - 2
+      if (j >= 2) {
+        ok = mbar_wait(pv_done + 2 * tt + b, (uint32_t)((j - 2) >> 1) & 1u, abort_flag, status, 37);
         if (!ok) break;
-        tc_fence_after();
       }
+      unsigned char* pdst = pdst0 + b * (SUBQ * 2);
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch)
         *reinterpret_cast<uint4*>(pdst + ((ch ^ (row & 7)) << 4)) =
             make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
-      // rescale this row of O if its scale moved (the warp decides together: the TMEM access is warp-wide)
+      // rescale this row of O if its scale moved (the warp decides together: the TMEM access is warp-wide); the
+      // P V of key tile j - 1 must have completed before O is touched
       if (j >= 1 && __any_sync(0xffffffffu, corr != 1.f)) {
+        ok = mbar_wait(pv_done + 2 * tt + (b ^ 1), (uint32_t)((j - 1) >> 1) & 1u, abort_flag, status, 37);
+        if (!ok) break;
+        tc_fence_after();
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t v[32];
@@ -425,10 +430,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
       fence_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_ready + tt);
+      if (lane == 0) mbar_arrive(p_ready + 2 * tt + b);
     }
     // the last P V
-    if (ok && my_tiles > 0) ok = mbar_wait(pv_done + tt, (uint32_t)(my_tiles - 1) & 1u, abort_flag, status, 38);
+    if (ok && my_tiles > 0)
+      ok = mbar_wait(pv_done + 2 * tt + ((my_tiles - 1) & 1), (uint32_t)((my_tiles - 1) >> 1) & 1u, abort_flag, status, 38);
     tc_fence_after();
     if (ok && my_tiles > 0) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -463,7 +469,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
 }
 
 size_t smem_bytes() {
-  return 1024 + (size_t)(QT * QTILE + QT * SUBQ + STAGES * 2 * KTILE) * 2 + (2 * STAGES + 7 * QT) * 8 + 64;
+  return 1024 + (size_t)(QT * QTILE + QT * 2 * SUBQ + STAGES * 2 * KTILE) * 2 + (2 * STAGES + 7 * QT) * 8 + 64;
 }
 }  // namespace
 // Attention of the requests with at least `min_q_long` new tokens; the others are skipped (the split-key kernel
