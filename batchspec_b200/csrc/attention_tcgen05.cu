@@ -140,7 +140,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_ready + QT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  const int g = blockIdx.y, e = blockIdx.z;
+  // grid: (kv head, request, Q tile pair) with the tile index slowest, so that CTAs are handed out heavy tiles first
+  // over all heads and requests together (causal tiles differ in length by a factor of the tile count)
+  const int g = blockIdx.x, e = blockIdx.y;
   Geom t;
   t.q_begin = qo_indptr[e];
   t.q_len = qo_indptr[e + 1] - t.q_begin;
@@ -149,8 +151,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
   t.G = Hq / Hkv;
   t.rows_total = t.q_len * t.G;
   const int n_cta_tiles = (t.rows_total + QT * ROWS - 1) / (QT * ROWS);
-  if ((int)blockIdx.x >= n_cta_tiles) return;
-  const int row0 = (n_cta_tiles - 1 - blockIdx.x) * QT * ROWS;                 // late (heavy) tiles first
+  if ((int)blockIdx.z >= n_cta_tiles) return;
+  const int row0 = (n_cta_tiles - 1 - blockIdx.z) * QT * ROWS;                 // late (heavy) tiles first
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // key range of the CTA, and how many key tiles each Q tile needs (causal: the first tile needs fewer)
   const int qi_lo = row0 / t.G;
@@ -494,7 +496,8 @@ BSPEC_API int bspec_attention_prefill_tc(const void* q, long long q_row_stride, 
     attr_set = true;
   }
   const int G = Hq / Hkv;
-  dim3 grid((max_q_len * G + QT * ROWS - 1) / (QT * ROWS), Hkv, n_entries);
+  dim3 grid(Hkv, n_entries, (max_q_len * G + QT * ROWS - 1) / (QT * ROWS));
+  if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
   BSPEC_LAUNCH((attn_prefill_tc_kernel), grid, THREADS, smem_bytes(), stream, kv_map, (const __nv_bfloat16*)q,
                q_row_stride, (__nv_bfloat16*)out, status, qo_indptr, positions, kv_indptr, kv_indices, Hq, Hkv, page_size,
                scale * 1.4426950408889634f, window, min_q_long);
