@@ -204,6 +204,12 @@ class CacheManager:
         ps = self.page_size
         return -(-(length + n_new) // ps) - (-(-length // ps))
 
+    def pages_missing(self, req_id, n_new: int) -> int:
+        """Pages a live request still has to get before it can take n_new more tokens (pages it already holds
+        beyond its length, from a reservation that was never committed, count as held)."""
+        rc = self.requests[req_id]
+        return max(0, -(-(rc.length + n_new) // self.page_size) - len(rc.tables[0])) if rc.tables else 0
+
     def can_reserve(self, demands: Sequence[Tuple[int, int]]) -> bool:
         """demands: (current length, new tokens) per request; True if every pool
         can serve all of them together."""
@@ -214,7 +220,7 @@ class CacheManager:
         """Make table entries for positions length .. length+n_new-1 in every group;
         all or nothing (raises OutOfPages and leaves the request as it was)."""
         rc = self.requests[req_id]
-        need = self.pages_needed(rc.length, n_new)
+        need = self.pages_missing(req_id, n_new)        # reserving twice for the same step is harmless
         if need == 0:
             return
         for g in self.groups:

@@ -56,6 +56,8 @@ class Engine:
         self.page_size = None
         self.max_batch_size = None
         self.max_seq_length = None
+        self.decode_lookahead = True        # launch the next captured decode step before reading this one's tokens
+        self._ahead = None
         self.prefill_chunk_size = 128
         self.max_tokens_per_step = 2048
         self.sampling = SamplingParams()
@@ -198,22 +200,65 @@ class Engine:
             [d.top_p if s.top_p is None else s.top_p for s in wanting],
             [s.seq_id for s in wanting], [len(s.output_ids) for s in wanting])
 
-    def _graph_decode_step(self, graph, work: List[Workload]) -> List[int]:
-        """A pure decode step through the captured graph: host token ids in, host
-        token ids out."""
+    def _launch_decode(self, graph, seqs, tokens, ahead: int):
+        """Enqueue one captured decode step of ``seqs`` and the copy of its chosen tokens into pinned host memory.
+        ``tokens`` None: the step's input ids are the ones the step before left on the device.  ``ahead``: 1 if
+        the step before has not been accounted for on the host yet (its output token counts as drawn)."""
         d = self.sampling
-        seqs = [w.seq for w in work]
         ids = [s.seq_id for s in seqs]
         for rid in ids:
             self.cache.reserve(rid, 1)
-        out = graph.run(ids, [s.known_token(w.start) for s, w in zip(seqs, work)],
+        out = graph.run(ids, tokens,
                         [d.temperature if s.temperature is None else s.temperature for s in seqs],
                         [d.top_k if s.top_k is None else s.top_k for s in seqs],
                         [d.top_p if s.top_p is None else s.top_p for s in seqs],
-                        ids, [len(s.output_ids) for s in seqs])
+                        ids, [len(s.output_ids) + ahead for s in seqs])
+        k = self._tok_turn = (getattr(self, "_tok_turn", 0) + 1) % 2
+        if not hasattr(self, "_tok_host") or self._tok_host[0].numel() < self.max_batch_size:
+            self._tok_host = [torch.empty((self.max_batch_size,), dtype=torch.int32).pin_memory() for _ in range(2)]
+        host = self._tok_host[k][:len(ids)]
+        host.copy_(out, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        return dict(graph=graph, ids=ids, host=host, event=ev, h2d=graph.last_h2d_bytes)
+
+    def _graph_decode_step(self, graph, work: List[Workload], sched: Optional[Scheduler] = None) -> List[int]:
+        """A pure decode step through the captured graph: host token ids in, host token ids out.
+
+        With a scheduler at hand the step AFTER this one is launched before this one's tokens are read, whenever it
+        is certain to be the same requests again unless one of them ends on a token only the GPU knows yet: the
+        host's work for a step (reading tokens, updating and planning, filling and uploading the next step's
+        metadata, the graph launch) then overlaps with the GPU instead of alternating with it.  The step launched
+        ahead takes its input ids from the device.  If the next plan turns out to be a subset of it (a request hit
+        an end-of-sequence token), its tokens are used for the requests that go on; if not, it is dropped: it wrote
+        keys that the real step writes again, and its page reservations are the real step's."""
+        seqs = [w.seq for w in work]
+        ids = [s.seq_id for s in seqs]
+        cur, ahead = None, self._ahead
+        self._ahead = None
+        if ahead is not None and set(ids) <= set(ahead["ids"]):
+            cur = ahead                                    # this step is already running (or done)
+        if cur is None:
+            cur = self._launch_decode(graph, seqs, [s.known_token(w.start) for s, w in zip(seqs, work)], 0)
         for rid in ids:
             self.cache.commit(rid, 1)
-        return out.cpu().tolist()
+        # Launch the next step now?  Only when the next plan cannot differ from this one except by requests that end
+        # on a token the host does not know yet: nobody waits for admission, nobody reaches a length limit with
+        # this step's token, and the pages the next step needs are free.
+        if (sched is not None and self.decode_lookahead and cur["ids"] == ids and cur["graph"] is graph
+                and not sched.waiting_queue and self.tracer is None and not get_active_profiler().active
+                and all(len(s.output_ids) + 1 < s.max_new_tokens and s.total_len + 1 < sched.max_model_len
+                        for s in seqs)):
+            need = sum(self.cache.pages_missing(rid, 1) for rid in ids)
+            if all(need <= g.pool.num_free for g in self.cache.groups):
+                self._ahead = self._launch_decode(graph, seqs, None, 1)
+        cur["event"].synchronize()
+        toks = cur["host"].tolist()
+        self._last_h2d = cur["h2d"]
+        if cur["ids"] == ids:
+            return toks
+        where = {rid: i for i, rid in enumerate(cur["ids"])}
+        return [toks[where[rid]] for rid in ids]
 
     @torch.inference_mode()
     def generate(self, sequences: List[Sequence]) -> List[Sequence]:
@@ -223,6 +268,7 @@ class Engine:
         if self.sampler is None:
             self.setup_sampling_params()
         self.cache.release_all()
+        self._ahead = None
         sched = self.make_scheduler()
         sched.add_sequences(sequences)
         steps = tokens_in = 0
@@ -243,8 +289,8 @@ class Engine:
                 w.n_tokens == 1 for w in work) else None
             with prof.step_timing_ctx():
                 if graph is not None:
-                    toks = self._graph_decode_step(graph, work)
-                    h2d = graph.last_h2d_bytes
+                    toks = self._graph_decode_step(graph, work, sched)
+                    h2d = self._last_h2d
                 else:
                     entries = [StepEntry(w.seq.seq_id, w.seq.known_tokens(w.start, w.start + w.n_tokens),
                                          (w.n_tokens - 1,) if w.wants_token else ()) for w in work]

@@ -122,7 +122,7 @@ class Scheduler:
             for s in self.running:
                 if s.status is not Status.DECODE:
                     continue
-                need = cache.pages_needed(s.num_computed, 1)
+                need = cache.pages_missing(s.seq_id, 1)
                 if budget < 1:
                     break
                 if need > free:
@@ -139,7 +139,7 @@ class Scheduler:
                     n = self._portion(s, budget, free)
                     if n == 0:
                         continue
-                    free -= cache.pages_needed(s.num_computed, n)
+                    free -= cache.pages_missing(s.seq_id, n)
                     budget -= n
                     work.append(Workload(s, s.num_computed, n, s.num_computed + n == s.total_len))
             # 3. admit waiting requests while slots, budget and pages allow

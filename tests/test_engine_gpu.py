@@ -227,6 +227,44 @@ def test_captured_decode_steps_equal_plain_ones(tmp_path, dtype):
     assert outs[True] == outs[False]
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_steps_launched_ahead_change_nothing(tmp_path, dtype):
+    """The engine launches the next captured decode step before it has read the current one's tokens.  Requests
+    that end on an end-of-sequence token (which only the GPU knows when the step ahead is launched), on their token
+    limit or on the context limit, more requests than fit at once (so that others are admitted when one ends) and
+    different lengths must give exactly the tokens of an engine that does not look ahead."""
+    from batchspec_b200.engine import Sequence
+    cfgj, seed, page = H.TINY["C"]
+    folder = H.make_folder(tmp_path, cfgj, seed, dtype=torch.float32 if dtype == "float32" else torch.bfloat16)
+    prompts = [H.random_tokens(n, cfgj["vocab_size"], 7 * n + 1) for n in (30, 4, 61, 12, 33, 5, 90)]
+    limits = [40, 3, 25, 60, 1, 17, 50]
+    def run(ahead, eos, count=None):
+        eng = engine_for(folder, dtype, page, max_batch=4, max_seq=120, prefill_chunk_size=64, max_tokens_per_step=128)
+        eng.decode_lookahead = ahead
+        eng.setup_sampling_params(temperature=0.9, top_k=50, seed=3)
+        eng.setup_special_tokens(eos_token_ids=eos)
+        if count is not None:
+            real = eng._launch_decode
+            def counting(graph, seqs, tokens, is_ahead):
+                count[0] += int(is_ahead)
+                return real(graph, seqs, tokens, is_ahead)
+            eng._launch_decode = counting
+        done = eng.generate([Sequence(i, p, max_new_tokens=m) for i, (p, m) in enumerate(zip(prompts, limits))])
+        eng.cache.check_invariants()
+        return {s.seq_id: s.output_ids for s in done}, {s.seq_id: s.finish_reason for s in done}
+
+    # end-of-sequence tokens that do turn up: what requests 0, 2 and 3 draw a third of the way in
+    free, _ = run(False, [])
+    eos = sorted({free[i][len(free[i]) // 3] for i in (0, 2, 3)})
+    outs, reasons, count = {}, {}, [0]
+    for ahead in (False, True):
+        outs[ahead], reasons[ahead] = run(ahead, eos, count if ahead else None)
+    launched_ahead = count[0]
+    assert outs[True] == outs[False] and reasons[True] == reasons[False]
+    assert launched_ahead > 10, "no step was launched ahead"
+    assert "eos" in reasons[True].values() and "length" in reasons[True].values()
+
+
 def test_temperature_sampling_does_not_depend_on_the_schedule(tmp_path):
     """Config B's workload: five prompts, chunks of 16 mixed with decode steps,
     temperature 0.8 under a fixed seed: the same tokens whatever the batching."""
