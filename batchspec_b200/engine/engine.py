@@ -243,10 +243,12 @@ class Engine:
         for rid in ids:
             self.cache.commit(rid, 1)
         # Launch the next step now?  Only when the next plan cannot differ from this one except by requests that end
-        # on a token the host does not know yet: nobody waits for admission, nobody reaches a length limit with
-        # this step's token, and the pages the next step needs are free.
+        # on a token the host does not know yet: nobody waits for admission (or no slot can come free: all are
+        # taken and no request stops at an end-of-sequence token), nobody reaches a length limit with this step's
+        # token, and the pages the next step needs are free.
         if (sched is not None and self.decode_lookahead and cur["ids"] == ids and cur["graph"] is graph
-                and not sched.waiting_queue and self.tracer is None and not get_active_profiler().active
+                and (not sched.waiting_queue or (sched.ignore_eos and len(sched.running) >= sched.max_concurrency))
+                and self.tracer is None and not get_active_profiler().active
                 and all(len(s.output_ids) + 1 < s.max_new_tokens and s.total_len + 1 < sched.max_model_len
                         for s in seqs)):
             need = sum(self.cache.pages_missing(rid, 1) for rid in ids)
