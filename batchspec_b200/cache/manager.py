@@ -175,6 +175,12 @@ class CacheManager:
             else:
                 self.layer_caches.append(LayerCache(kv=kv, group=g, state=state, owner=need.cache_from is None))
 
+    def page_bytes(self) -> int:
+        """Bytes of all pools' page tensors (whether or not they were allocated)."""
+        item = torch.empty((), dtype=self.dtype).element_size()
+        return sum(len(g.runs) * (g.pool.num_pages + g.pool.reserved) * 2 * self.page_size * g.entry_elems * item
+                   for g in self.groups)
+
     def scratch_pages(self) -> Optional[List[int]]:
         """Per group, the id of the page that no request ever holds (None if the
         manager was made without one)."""

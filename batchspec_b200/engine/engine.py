@@ -117,10 +117,23 @@ class Engine:
         self.max_seq_length = max_seq_length
         self.prefill_chunk_size = int(prefill_chunk_size)
         self.max_tokens_per_step = int(max_tokens_per_step or max(prefill_chunk_size, max_batch_size))
-        self.cache = CacheManager(self.model.cache_needs(), page_size, num_pages, max_batch_size, self.dtype,
-                                  self.device, scratch_page=True)
-        self.model.attach_caches(self.cache.layer_caches)
+        # the old pool (and the graphs that point into it) goes before the new one is made
         self._graphs = {}
+        self._ahead = None
+        self.cache = self.runner = None
+        self.model.attach_caches([None] * len(self.model.spec.order))
+        needs = self.model.cache_needs()
+        if torch.device(self.device).type == "cuda":
+            torch.cuda.empty_cache()
+            want = CacheManager(needs, page_size, num_pages, max_batch_size, self.dtype, self.device,
+                                allocate=False, scratch_page=True).page_bytes()
+            free, _ = torch.cuda.mem_get_info(self.device)
+            if want > free:
+                raise ValueError(
+                    f"the cache pools need {want / 2**30:.1f} GiB ({num_pages} pages of {page_size} tokens per pool) but "
+                    f"{free / 2**30:.1f} GiB are free on {self.device}: lower max_batch_size or max_seq_length, or give num_pages")
+        self.cache = CacheManager(needs, page_size, num_pages, max_batch_size, self.dtype, self.device, scratch_page=True)
+        self.model.attach_caches(self.cache.layer_caches)
         self.runner = StepRunner(self.model, self.cache, self.model.spec.vocab_size, self.device)
 
     # -- the step function ---------------------------------------------------------
