@@ -44,7 +44,7 @@ class CommonArguments:
     random_weights: bool = field(default=False, metadata={"help": "Draw weights from --seed for the configuration --model_name instead of reading a folder."})
     page_size: int = field(default=16, metadata={"help": "Tokens per cache page."})
     num_pages: Optional[int] = field(default=None, metadata={"help": "Pages in the pool (default: batch_size x ceil(max_len / page_size))."})
-    max_tokens_per_step: Optional[int] = field(default=None, metadata={"help": "Token budget of one step (default: max(prefill_chunk, batch_size))."})
+    max_tokens_per_step: Optional[int] = field(default=None, metadata={"help": "Token budget of one step (default: prefill_chunk * batch_size: every request of a full batch advances one portion per step, as in the reference)."})
     prefill_chunk: Optional[int] = field(default=None, metadata={"help": "Longest prompt portion per request per step (default: by batch size, as the reference)."})
     trace: bool = field(default=False, metadata={"help": "Print the scheduler's plan and updates every step."})
 

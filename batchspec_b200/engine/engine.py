@@ -105,7 +105,10 @@ class Engine:
                      max_tokens_per_step: Optional[int] = None) -> None:
         """``num_pages`` sizes every pool directly; else the pool holds
         ``max_batch_size`` requests of ``max_seq_length`` tokens (the reference's
-        sizing rule, backends/base/engine.py:66-93, without its +1 page)."""
+        sizing rule, backends/base/engine.py:66-93, without its +1 page).  The token
+        budget of a step defaults to ``prefill_chunk_size * max_batch_size``: a full
+        batch advances by one portion per request and step, as the reference's
+        chunked prefill does (standard_engine.py:176-214)."""
         if self.model is None:
             raise RuntimeError("load_model first")
         if num_pages is None:
@@ -116,7 +119,7 @@ class Engine:
         self.max_batch_size = int(max_batch_size)
         self.max_seq_length = max_seq_length
         self.prefill_chunk_size = int(prefill_chunk_size)
-        self.max_tokens_per_step = int(max_tokens_per_step or max(prefill_chunk_size, max_batch_size))
+        self.max_tokens_per_step = int(max_tokens_per_step or prefill_chunk_size * max_batch_size)
         # the old pool (and the graphs that point into it) goes before the new one is made
         self._graphs = {}
         self._ahead = None

@@ -58,7 +58,7 @@ class Runner:
         chunk = a.prefill_chunk or PREFILL_CHUNK_BY_BATCH.get(a.batch_size, 128)
         self.engine.setup_caches(max_batch_size=a.batch_size, max_seq_length=max_len, page_size=a.page_size,
                                  prefill_chunk_size=chunk, num_pages=a.num_pages,
-                                 max_tokens_per_step=a.max_tokens_per_step or max(chunk, a.batch_size))
+                                 max_tokens_per_step=a.max_tokens_per_step or chunk * a.batch_size)
         self.engine.setup_sampling_params(temperature=a.temperature, top_p=a.top_p, top_k=a.top_k,
                                           force_budget=a.force_budget, seed=a.seed)
         self.engine.setup_special_tokens()
