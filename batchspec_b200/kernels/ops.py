@@ -323,6 +323,40 @@ def _counters(device, n: int) -> torch.Tensor:
     return bufs[-1]
 
 
+def _attention_plan(device, ctx, tables, n_heads: int, n_kv_heads: int, head_dim: int):
+    """Which bfloat16 attention kernels a step launches for layers of these sizes, with their scratch and the
+    addresses of the step's metadata (kept alive by ``ctx`` and ``tables``)."""
+    group = n_heads // n_kv_heads
+    short = max(1, 16 // group)
+    # the TMA-fed split-key kernels (page sizes 8..64) fit two CTAs per SM, the plain one three
+    tma = USE_TMA_ATTENTION and tables.page_size % 8 == 0 and 64 % tables.page_size == 0
+    # Equal shares of all key tiles over a fixed grid (cut on the device from the step's lengths): n_splits is
+    # then only the most partial results a row tile may be left in, and the scratch is indexed by request.
+    balanced = int(tma and BALANCED_ATTENTION and ctx.n_entries <= 512 and not ctx.extras.get("attn_splits"))
+    if balanced:
+        n_splits = min(64, max(16, -(-4 * _SM_COUNT // (ctx.n_entries * n_kv_heads)) + 2))
+    else:
+        n_splits = ctx.extras.get("attn_splits") or attention_splits(ctx.n_entries, n_kv_heads, group, ctx.max_q_len,
+                                                                     ctx.max_kv_len, 2 if tma else 3)
+    run_decode = int(ctx.extras.get("min_q_len", 1) <= short)
+    run_prefill = int(ctx.max_q_len > short)
+    o_part = ml_part = counters = None
+    if n_splits > 1 and run_decode:
+        rows = ctx.n_entries * min(ctx.max_q_len, short) if balanced else ctx.n_tokens
+        o_part = torch.empty((rows * n_heads * n_splits * head_dim,), dtype=torch.float32, device=device)
+        ml_part = torch.empty((rows * n_heads * n_splits * 2,), dtype=torch.float32, device=device)
+        row_tiles = -(-(min(ctx.max_q_len, short) * group) // 16)
+        counters = _counters(device, ctx.n_entries * n_kv_heads * row_tiles)
+        ctx.extras[("attention scratch", n_heads, n_kv_heads, head_dim, id(tables))] = (o_part, ml_part)   # alive
+    elif n_splits > 1:
+        n_splits = 1                         # no short request in the step: the split-key kernel does not run
+    prefill_tc = bool(run_prefill and tma and USE_TC_ATTENTION and head_dim == 128)
+    return (tma, balanced, n_splits, short, run_decode, run_prefill, prefill_tc, _ptr(o_part), _ptr(ml_part),
+            _ptr(counters), _status_word(device).data_ptr(), ctx.qo_indptr.data_ptr(), ctx.positions.data_ptr(),
+            ctx.tok_entry.data_ptr(), tables.kv_indptr.data_ptr(), tables.kv_indices.data_ptr(),
+            _ptr(getattr(ctx, "kv_len", None)))
+
+
 def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, ctx, tables, n_heads: int,
                     n_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
     """Causal attention of the step's tokens over their requests' cached keys.
@@ -334,44 +368,28 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, c
     assert qkv.stride(1) == 1 and out.is_contiguous() and out.dtype == qkv.dtype == cache.dtype
     lib = load_library()
     if qkv.dtype == torch.bfloat16 and head_dim in (64, 128, 256) and not FORCE_GENERIC_ATTENTION:
-        group = n_heads // n_kv_heads
-        short = max(1, 16 // group)
-        # the TMA-fed split-key kernels (page sizes 8..64) fit two CTAs per SM, the plain one three
-        tma = USE_TMA_ATTENTION and tables.page_size % 8 == 0 and 64 % tables.page_size == 0
-        # Equal shares of all key tiles over a fixed grid (cut on the device from the step's lengths): n_splits is
-        # then only the most partial results a row tile may be left in, and the scratch is indexed by request.
-        balanced = int(tma and BALANCED_ATTENTION and ctx.n_entries <= 512 and not ctx.extras.get("attn_splits"))
-        if balanced:
-            n_splits = min(64, max(16, -(-4 * _SM_COUNT // (ctx.n_entries * n_kv_heads)) + 2))
-        else:
-            n_splits = ctx.extras.get("attn_splits") or attention_splits(ctx.n_entries, n_kv_heads, group, ctx.max_q_len,
-                                                                         ctx.max_kv_len, 2 if tma else 3)
-        o_part = ml_part = counters = None
-        if n_splits > 1:
-            rows = ctx.n_entries * min(ctx.max_q_len, short) if balanced else ctx.n_tokens
-            o_part = torch.empty((rows * n_heads * n_splits * head_dim,), dtype=torch.float32, device=qkv.device)
-            ml_part = torch.empty((rows * n_heads * n_splits * 2,), dtype=torch.float32, device=qkv.device)
-            row_tiles = -(-(min(ctx.max_q_len, short) * group) // 16)
-            counters = _counters(qkv.device, ctx.n_entries * n_kv_heads * row_tiles)
-        run_decode = int(ctx.extras.get("min_q_len", 1) <= short)
-        run_prefill = int(ctx.max_q_len > short)
-        if run_prefill and tma and USE_TC_ATTENTION and head_dim == 128:
+        # Everything that depends on the step and the layer's sizes only is worked out once per step (all layers of
+        # a model ask the same question), the scratch included: the layers run one after the other on one stream.
+        key = ("attention", n_heads, n_kv_heads, head_dim, id(tables), BALANCED_ATTENTION, USE_TMA_ATTENTION)
+        plan = ctx.extras.get(key)
+        if plan is None:
+            plan = ctx.extras[key] = _attention_plan(qkv.device, ctx, tables, n_heads, n_kv_heads, head_dim)
+        (tma, balanced, n_splits, short, run_decode, run_prefill, prefill_tc, o_part, ml_part, counters, status, qo, pos,
+         tok_entry, kv_indptr, kv_indices, kv_len) = plan
+        if prefill_tc:
             # long portions on the tcgen05 kernel; what is left for the call below are the short requests
             _check(lib.bspec_attention_prefill_tc(
-                qkv.data_ptr(), qkv.stride(0), out.data_ptr(), _status_word(qkv.device).data_ptr(), cache.shape[0],
-                cache.data_ptr(), ctx.qo_indptr.data_ptr(), ctx.positions.data_ptr(), tables.kv_indptr.data_ptr(),
-                tables.kv_indices.data_ptr(), ctx.n_entries, ctx.max_q_len, n_heads, n_kv_heads, head_dim,
-                tables.page_size, float(scale), int(window), short + 1, _stream()), "attention_prefill_tc")
+                qkv.data_ptr(), qkv.stride(0), out.data_ptr(), status, cache.shape[0], cache.data_ptr(), qo, pos,
+                kv_indptr, kv_indices, ctx.n_entries, ctx.max_q_len, n_heads, n_kv_heads, head_dim, tables.page_size,
+                float(scale), int(window), short + 1, _stream()), "attention_prefill_tc")
             run_prefill = 0
             if not run_decode:
                 return
         _check(lib.bspec_attention_bf16(
-            qkv.data_ptr(), qkv.stride(0), out.data_ptr(), _ptr(o_part), _ptr(ml_part), _ptr(counters),
-            _status_word(qkv.device).data_ptr(), cache.shape[0] if tma else 0, cache.data_ptr(),
-            ctx.qo_indptr.data_ptr(), ctx.positions.data_ptr(), ctx.tok_entry.data_ptr(), tables.kv_indptr.data_ptr(),
-            tables.kv_indices.data_ptr(), ctx.n_entries, ctx.n_tokens, ctx.max_q_len, n_heads, n_kv_heads, head_dim,
-            tables.page_size, float(scale), int(window), n_splits, short, run_decode, run_prefill, balanced,
-            _ptr(getattr(ctx, "kv_len", None)), _stream()), "attention_bf16")
+            qkv.data_ptr(), qkv.stride(0), out.data_ptr(), o_part, ml_part, counters, status,
+            cache.shape[0] if tma else 0, cache.data_ptr(), qo, pos, tok_entry, kv_indptr, kv_indices, ctx.n_entries,
+            ctx.n_tokens, ctx.max_q_len, n_heads, n_kv_heads, head_dim, tables.page_size, float(scale), int(window),
+            n_splits, short, run_decode, run_prefill, balanced, kv_len, _stream()), "attention_bf16")
         global _launches
         _launches += 1 if run_decode and run_prefill else 0
         return
