@@ -118,6 +118,7 @@ class RequestCache:
     slot: int
     length: int = 0
     tables: List[List[int]] = field(default_factory=list)   # per group: page id per logical page, -1 once released
+    serial: int = 0     # which admission this is: a request that is released and admitted again gets a new one
 
 
 class CacheManager:
@@ -196,7 +197,8 @@ class CacheManager:
         for st in self.state_tensors:
             if st is not None:
                 st[slot].zero_()
-        rc = RequestCache(req_id, slot, 0, [[] for _ in self.groups])
+        self._admissions = getattr(self, "_admissions", 0) + 1
+        rc = RequestCache(req_id, slot, 0, [[] for _ in self.groups], self._admissions)
         self.requests[req_id] = rc
         return rc
 

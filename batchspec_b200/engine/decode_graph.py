@@ -137,7 +137,9 @@ class DecodeGraph:
                     self.row_req[i] = self._PAD
                     self.tables_dirty = True
         for i, (rid, rc) in enumerate(zip(req_ids, reqs)):
-            fresh = self.row_req[i] != rid
+            # the row's table on the device is this request's only if it is the same admission: a request that was
+            # preempted and admitted again has the same id but other pages (perhaps as many as before)
+            fresh = self.row_req[i] != (rid, rc.serial)
             for g, table in enumerate(rc.tables):
                 have = 0 if fresh else self.row_pages[i][g]
                 if len(table) > P:
@@ -152,7 +154,7 @@ class DecodeGraph:
                     base = off[f"kv_indices{g}"] + i * P        # released pages turn into -1 in place
                     m[base:base + len(table)] = table
                     self.tables_dirty = True
-            self.row_req[i] = rid
+            self.row_req[i] = (rid, rc.serial)
 
     def _upload(self, with_tokens: bool) -> None:
         i = self.turn

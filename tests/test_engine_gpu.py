@@ -301,6 +301,48 @@ def test_preemption_under_page_pressure_changes_nothing(tmp_path):
     assert outs[0] == outs[1]
 
 
+def test_everything_at_once_gives_the_same_tokens(tmp_path):
+    """Many requests of random lengths and limits, sampled, some ending on end-of-sequence tokens, more than fit at
+    once, through a pool so small that requests are preempted: the tokens are those of a roomy engine without
+    captured graphs, whether decode steps are captured or not and launched ahead or not (float32: every kernel
+    then gives a row the same bits whatever else is in the step)."""
+    import random
+    from batchspec_b200.engine import Sequence
+    cfgj, seed, page = H.TINY["A"]
+    folder = H.make_folder(tmp_path, cfgj, seed, dtype=torch.float32)
+    rng = random.Random(4)
+    prompts = [H.random_tokens(rng.randint(1, 70), cfgj["vocab_size"], 100 + i) for i in range(14)]
+    limits = [rng.randint(1, 45) for _ in prompts]
+
+    def run(num_pages, graphs, ahead, eos):
+        eng = engine_for(folder, "float32", page, max_batch=5, max_seq=128, prefill_chunk_size=24,
+                         max_tokens_per_step=48, num_pages=num_pages)
+        eng.use_cuda_graphs, eng.decode_lookahead = graphs, ahead
+        eng.setup_sampling_params(temperature=0.8, top_k=30, top_p=0.9, seed=21)
+        eng.setup_special_tokens(eos_token_ids=eos)
+        done = eng.generate([Sequence(i, p, max_new_tokens=m) for i, (p, m) in enumerate(zip(prompts, limits))])
+        eng.cache.check_invariants()
+        assert all(g.pool.num_held == 0 for g in eng.cache.groups)
+        return ({s.seq_id: s.output_ids for s in done}, {s.seq_id: s.finish_reason for s in done},
+                eng.last_stats["preemptions"])
+
+    free, _, _ = run(400, False, False, [])
+    eos = sorted({free[i][len(free[i]) // 2] for i in (1, 4, 7, 10) if len(free[i]) > 3})
+    want = run(400, False, False, eos)
+    assert "eos" in want[1].values() and "length" in want[1].values()
+    tight = -(-max(len(p) + m for p, m in zip(prompts, limits)) // page) + 8       # the longest request and little more
+    preempted = 0
+    for graphs, ahead in [(False, False), (True, False), (True, True)]:
+        got = run(tight, graphs, ahead, eos)
+        for i in want[0]:
+            assert got[0][i] == want[0][i], (graphs, ahead, i, len(prompts[i]), limits[i], got[2],
+                                             [k for k, (a, b) in enumerate(zip(got[0][i], want[0][i])) if a != b][:3],
+                                             len(got[0][i]), len(want[0][i]))
+        assert got[1] == want[1], (graphs, ahead)
+        preempted += got[2]
+    assert preempted >= 3, "the small pool never forced a preemption"
+
+
 def test_command_line_entry_point(tmp_path):
     cfgj, seed, page = H.TINY["A"]
     folder = H.make_folder(tmp_path / "m", cfgj, seed, dtype=torch.bfloat16)
