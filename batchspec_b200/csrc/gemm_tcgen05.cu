@@ -246,26 +246,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
         for (int s = 0; s < 8; ++s)
           if (s < p.splits) asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer[s]) : "r"(mine), "r"(s));
-        for (int j = split; j < p.bn; j += p.splits) {
-          const int tok = tile_b * p.bn + j;
-          if (tok >= p.M) break;
-          const uint32_t off = (uint32_t)j * TM * 4u;
-          float v[8], u[8];
+        // four tokens at a time, all their loads in flight before the first add: a load from a peer's shared
+        // memory takes some hundred cycles, and with 64 tokens on the tile a CTA has up to 32 of them to join
+        for (int j0 = split; j0 < p.bn; j0 += 4 * p.splits) {
+          float v[4][8], u[4][8];
+          bool live[4];
 #pragma unroll
-          for (int s = 0; s < 8; ++s)                      // all loads in flight before the first add
-            if (s < p.splits) {
-              asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[s]) : "r"(peer[s] + off));
-              if (p.glu) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(u[s]) : "r"(peer[s] + off + 256u));
-            }
-          float acc = 0.f, acc_u = 0.f;
+          for (int t = 0; t < 4; ++t) {
+            const int j = j0 + t * p.splits;
+            live[t] = j < p.bn && tile_b * p.bn + j < p.M;
+            if (live[t]) {
+              const uint32_t off = (uint32_t)j * TM * 4u;
 #pragma unroll
-          for (int s = 0; s < 8; ++s)
-            if (s < p.splits) {                            // slice order
-              acc += v[s];
-              if (p.glu) acc_u += u[s];
+              for (int s = 0; s < 8; ++s)
+                if (s < p.splits) {
+                  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[t][s]) : "r"(peer[s] + off));
+                  if (p.glu) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(u[t][s]) : "r"(peer[s] + off + 256u));
+                }
             }
-          if (p.glu) acc = acc / (1.f + expf(-acc)) * acc_u;
-          store_out(p.C, p.out_f32, (size_t)tok * n_out + ra, acc);
+          }
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            if (!live[t]) continue;
+            float acc = 0.f, acc_u = 0.f;
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+              if (s < p.splits) {                          // slice order
+                acc += v[t][s];
+                if (p.glu) acc_u += u[t][s];
+              }
+            if (p.glu) acc = acc / (1.f + expf(-acc)) * acc_u;
+            store_out(p.C, p.out_f32, (size_t)(tile_b * p.bn + j0 + t * p.splits) * n_out + ra, acc);
+          }
         }
       }
     }

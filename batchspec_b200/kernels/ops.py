@@ -402,10 +402,13 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, c
 
 # ---------------------------------------------------------------------------- matrix products
 
-# Which bfloat16 products run on this package's tcgen05 kernel: "auto" (those with at most TC_GEMM_MAX_M rows,
-# i.e. decode-sized steps, where it streams the weights faster than the vendor library), "all", or "none".
+# Which bfloat16 products run on this package's tcgen05 kernel: "auto" (those with at most TC_GEMM_MAX_M rows),
+# "all", or "none".  Measured on B200 in whole decode steps of 1B to 8B models: with up to 8 tokens the kernel (weights
+# on the accumulator rows, K slices joined inside a cluster, the gate/up activation in its epilogue, weight tiles
+# fetched before the wait on the kernel before) beats the vendor library by 2 to 12 %; from 16 tokens on the library
+# wins, by 1 to 15 % (the join of the slices grows with the tokens), so larger steps go to the library.
 TC_GEMM = os.environ.get("BSPEC_TC_GEMM", "auto")
-TC_GEMM_MAX_M = 128
+TC_GEMM_MAX_M = int(os.environ.get("BSPEC_TC_GEMM_MAX_M", "8"))
 _status = {}
 
 
