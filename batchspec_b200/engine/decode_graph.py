@@ -19,6 +19,8 @@ Layout of the int32 metadata buffer for B entries and at most P pages per reques
 """
 from __future__ import annotations
 
+import gc
+
 from typing import Dict, List, Optional, Sequence
 
 import numpy as np
@@ -208,6 +210,15 @@ class DecodeGraph:
         cache and the token buffer are not touched."""
         torch.cuda.current_stream().synchronize()
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            self._forward()
+        # No cyclic garbage collection while the stream captures: what it frees may be another engine's captured
+        # graphs, and destroying a graph is not permitted during a capture (it invalidates this one).
+        gc_was_on = gc.isenabled()
+        gc.collect()
+        gc.disable()
+        try:
+            with torch.cuda.graph(g):
+                self._forward()
+        finally:
+            if gc_was_on:
+                gc.enable()
         self.graph = g
