@@ -259,10 +259,12 @@ class Engine:
         for rid in ids:
             self.cache.commit(rid, 1)
         # Launch the next step now?  Only when the next plan cannot differ from this one except by requests that end
-        # on a token the host does not know yet: nobody waits for admission (or no slot can come free: all are
-        # taken and no request stops at an end-of-sequence token), nobody reaches a length limit with this step's
-        # token, and the pages the next step needs are free.
+        # on a token the host does not know yet: every live request is in this step (none is in the middle of its
+        # prompt, held up for pages that an ending request would free), nobody waits for admission (or no slot can
+        # come free: all are taken and no request stops at an end-of-sequence token), nobody reaches a length limit
+        # with this step's token, and the pages the next step needs are free.
         if (sched is not None and self.decode_lookahead and cur["ids"] == ids and cur["graph"] is graph
+                and len(sched.running) == len(ids)
                 and (not sched.waiting_queue or (sched.ignore_eos and len(sched.running) >= sched.max_concurrency))
                 and self.tracer is None and not get_active_profiler().active
                 and all(len(s.output_ids) + 1 < s.max_new_tokens and s.total_len + 1 < sched.max_model_len
@@ -310,6 +312,7 @@ class Engine:
                     toks = self._graph_decode_step(graph, work, sched)
                     h2d = self._last_h2d
                 else:
+                    self._ahead = None        # a step launched ahead stands for the very next step or for none
                     entries = [StepEntry(w.seq.seq_id, w.seq.known_tokens(w.start, w.start + w.n_tokens),
                                          (w.n_tokens - 1,) if w.wants_token else ()) for w in work]
                     logits = self.runner.step(entries)

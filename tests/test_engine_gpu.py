@@ -343,6 +343,36 @@ def test_everything_at_once_gives_the_same_tokens(tmp_path):
     assert preempted >= 3, "the small pool never forced a preemption"
 
 
+def test_prompts_held_up_for_pages_beside_a_step_launched_ahead(tmp_path):
+    """Two requests decode while two more, admitted but in the middle of their prompts, get no pages; one of the
+    decoding ones ends on an end-of-sequence token that only the GPU knows when the next step has already been
+    launched ahead.  The step after that feeds prompt portions again, so the step launched ahead stands for nothing:
+    it must neither be launched in that situation nor be taken for a later step."""
+    from batchspec_b200.engine import Sequence
+    cfgj, seed, _ = H.TINY["B"]
+    page = 16
+    folder = H.make_folder(tmp_path, cfgj, seed, dtype=torch.float32)
+    lens, limits = [6, 96, 43, 15, 1, 104, 38, 83], [9, 25, 6, 3, 37, 4, 4, 10]
+    prompts = [H.random_tokens(n, cfgj["vocab_size"], 15600 + i) for i, n in enumerate(lens)]
+
+    def run(num_pages, graphs, ahead, eos):
+        eng = engine_for(folder, "float32", page, max_batch=5, max_seq=128, prefill_chunk_size=16,
+                         max_tokens_per_step=32, num_pages=num_pages)
+        eng.use_cuda_graphs, eng.decode_lookahead = graphs, ahead
+        eng.setup_sampling_params(temperature=0.9, top_k=5, top_p=0.9, seed=156)
+        eng.setup_special_tokens(eos_token_ids=eos)
+        done = eng.generate([Sequence(i, p, max_new_tokens=m) for i, (p, m) in enumerate(zip(prompts, limits))])
+        eng.cache.check_invariants()
+        return {s.seq_id: s.output_ids for s in done}, eng.last_stats["preemptions"]
+
+    free, _ = run(400, False, False, [])
+    eos = sorted({free[i][len(free[i]) // 2] for i in (0, 3, 6) if len(free[i]) > 3})
+    want, _ = run(400, False, False, eos)
+    got, preempted = run(9, True, True, eos)
+    assert preempted >= 1
+    assert got == want
+
+
 def test_command_line_entry_point(tmp_path):
     cfgj, seed, page = H.TINY["A"]
     folder = H.make_folder(tmp_path / "m", cfgj, seed, dtype=torch.bfloat16)
