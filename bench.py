@@ -222,7 +222,7 @@ def main() -> int:
     step_bytes = nums["weight_bytes"] + a.batch * mean_ctx * nums["kv_bytes_per_token"]
     achieved = step_bytes / (ms * 1e-3) / 1e9
     out = {
-        "metric": "decode tok/s (Llama-3-8B sizes, bf16, batch 8, 2048-token prompts)", "value": round(value, 2),
+        "metric": f"decode tok/s (Llama-3-8B sizes, bf16, batch {a.batch}, {PROMPT_LEN}-token prompts)", "value": round(value, 2),
         "unit": "tok/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "impl": "ours",
