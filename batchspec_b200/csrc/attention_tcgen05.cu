@@ -10,8 +10,8 @@
 //             (A = P in shared memory, B = V read MN-major straight from the loaded pages) into the tile's O
 //             accumulator.  S runs two key tiles ahead; P V of tile j is issued the moment P_j is announced.
 //   warps 2-5 / 6-9   Q tile 0 / 1, one thread per row: read its S row from tensor memory, scale, mask, online
-//             softmax in float32 (a third of the exponentials as a cubic on the FMA pipe, the rest on the
-//             special-function unit, which alone would be as slow as the tensor core), write P (bfloat16) into
+//             softmax in float32 (two values per instruction where sm_100 has a packed form; a quarter of the
+//             exponentials as a cubic on the FMA pipe, the rest on the special-function unit), write P (bfloat16) into
 //             one of the tile's two P buffers in shared memory in the operand layout, rescale its O row in tensor
 //             memory when its scale moved, and at the end normalise and store O.
 // The softmax of a tile never waits for the tensor core in the steady state: S of the next key tile is ready, and
@@ -34,7 +34,7 @@ constexpr int QT = 2;                // Q tiles per CTA
 constexpr int KT = 64;               // keys per tile
 constexpr int STAGES = 3;
 #ifndef BSPEC_ATTN_EMU
-#define BSPEC_ATTN_EMU 3
+#define BSPEC_ATTN_EMU 4
 #endif
 constexpr int EMU = BSPEC_ATTN_EMU;   // every EMU-th pair of exponentials on the FMA pipe (0: none)
 constexpr int MMA_WARP_1 = 2 + 4 * QT;                 // the second Q tile's MMA warp: after the softmax warps
@@ -94,6 +94,48 @@ __device__ __forceinline__ float ex2_fma(float x) {
   p = fmaf(p, f, 0.69326097f);
   p = fmaf(p, f, 0.99992806f);
   return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+// Two float32 operations per instruction (sm_100 has packed forms of add, mul and fma) and a maximum of three:
+// the softmax is bound by the number of instructions it issues, not by the arithmetic pipes.
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// ex2_fma for two values at once.
+__device__ __forceinline__ void ex2_fma2(uint64_t x2, float& p0, float& p1) {
+  float x0, x1;
+  unpack2(x2, x0, x1);
+  x2 = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const uint64_t t2 = add2(x2, pack2(12582912.f, 12582912.f));
+  const uint64_t u2 = add2(t2, pack2(-12582912.f, -12582912.f));
+  const uint64_t f2 = fma2(u2, pack2(-1.f, -1.f), x2);
+  uint64_t q2 = fma2(pack2(0.05517165f, 0.05517165f), f2, pack2(0.24261113f, 0.24261113f));
+  q2 = fma2(q2, f2, pack2(0.69326097f, 0.69326097f));
+  q2 = fma2(q2, f2, pack2(0.99992806f, 0.99992806f));
+  float t0, t1, q0, q1;
+  unpack2(t2, t0, t1);
+  unpack2(q2, q0, q1);
+  p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
+  p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -359,7 +401,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
 #pragma unroll
         for (int c = 0; c < 2; ++c)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[c][i]));
+          for (int i = 0; i < 32; i += 2)
+            mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1]));
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
       float corr = 1.f;
@@ -371,37 +414,48 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
       }
       const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
       // exponentials first (they do not need P's buffer), then wait until the previous P V has completed
-      float l4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t packed[32];
-      if (need_mask) {
+      const uint64_t scale2 = pack2(scale_log2, scale_log2), neg_m2 = pack2(neg_m, neg_m);
+      uint64_t l2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
+      if (need_mask) {                     // masked scores are -inf: their exponentials must be exactly 0
 #pragma unroll
         for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            const float p0 = ex2(fmaf(__uint_as_float(sv[c][i]), scale_log2, neg_m));
-            const float p1 = ex2(fmaf(__uint_as_float(sv[c][i + 1]), scale_log2, neg_m));
-            l4[(i >> 1) & 3] += p0 + p1;
+            float p0, p1;
+            unpack2(fma2(pack2(__uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1])), scale2, neg_m2), p0, p1);
+            p0 = ex2(p0);
+            p1 = ex2(p1);
+            l2[(i >> 1) & 1] = add2(l2[(i >> 1) & 1], pack2(p0, p1));
             __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
             packed[16 * c + (i >> 1)] = *reinterpret_cast<uint32_t*>(&hh);
           }
       } else {
         // The special-function unit makes 16 exponentials per clock and SM, which is as long as the tensor core
         // needs for the two products of the tile: every EMU-th pair of exponentials goes to the FMA pipe instead.
+        // Scaling, the cubic and the row sum handle two values per instruction (fma/add.f32x2).
 #pragma unroll
         for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            const float x0 = fmaf(__uint_as_float(sv[c][i]), scale_log2, neg_m);
-            const float x1 = fmaf(__uint_as_float(sv[c][i + 1]), scale_log2, neg_m);
+            const uint64_t x2 = fma2(pack2(__uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1])), scale2, neg_m2);
             const bool emu = EMU > 0 && ((i >> 1) % EMU) == EMU - 1;
-            const float p0 = emu ? ex2_fma(x0) : ex2(x0);
-            const float p1 = emu ? ex2_fma(x1) : ex2(x1);
-            l4[(i >> 1) & 3] += p0 + p1;
+            float p0, p1;
+            if (emu) {
+              ex2_fma2(x2, p0, p1);
+            } else {
+              unpack2(x2, p0, p1);
+              p0 = ex2(p0);
+              p1 = ex2(p1);
+            }
+            l2[(i >> 1) & 1] = add2(l2[(i >> 1) & 1], pack2(p0, p1));
             __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
             packed[16 * c + (i >> 1)] = *reinterpret_cast<uint32_t*>(&hh);
           }
       }
-      l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+      float la, lb;
+      unpack2(add2(l2[0], l2[1]), la, lb);
+      l += la + lb;
       // this tile's P buffer was last read by the P V of key tile j - 2
       if (j >= 2) {
         ok = mbar_wait(pv_done + 2 * tt + b, (uint32_t)((j - 2) >> 1) & 1u, abort_flag, status, 37);
