@@ -8,7 +8,8 @@
 
 namespace bspec {
 
-constexpr uint32_t WAIT_LIMIT = 1u << 24;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;             // polls
+constexpr uint64_t WAIT_NS = 2000000000ull;            // and wall time: a wait that is ever satisfied takes microseconds
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -27,12 +28,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "=r"(ok) : "r"(s32(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false (and raises the CTA's abort flag) when the limit is hit or another role aborted.
+__device__ __forceinline__ uint64_t wall_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  Returns false (and raises the CTA's abort flag) when another role of the CTA aborted, when the
+// limit (polls or time) is hit, or when any CTA of this or an earlier launch has given up (the status word in
+// global memory is set: the step's result is lost anyway, so the rest of the grid leaves at once instead of
+// waiting out its own limits one CTA after the other).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
                                           int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  uint64_t t0 = 0;
   for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
+    if ((i & 255u) == 255u) {
+      if (*reinterpret_cast<volatile int*>(status) != 0) {
+        *abort_flag = 1;
+        return false;
+      }
+      const uint64_t now = wall_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > WAIT_NS) break;
+    }
     if (i > 4096) __nanosleep(64);
   }
   *abort_flag = 1;

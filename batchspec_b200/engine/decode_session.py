@@ -51,7 +51,12 @@ class DecodeSession:
 
     def generated(self) -> List[List[int]]:
         """Token ids per request, on the host (one device->host copy)."""
-        return torch.stack(self.history, dim=1).cpu().tolist()
+        ops.status_to_host_async()
+        out = torch.stack(self.history, dim=1).cpu().tolist()
+        ops.raise_if_gave_up()
+        return out
 
     def close(self) -> None:
+        """Ends the session; raises if a kernel of one of its steps gave up a bounded wait."""
         self.history = []
+        ops.check_status()

@@ -18,6 +18,7 @@ import torch
 
 from ..cache.manager import CacheManager
 from ..config import get_config, load_config
+from ..kernels import ops
 from ..models import get_model
 from ..parts.base import Runtime
 from ..profiler import get_active_profiler
@@ -234,6 +235,7 @@ class Engine:
             self._tok_host = [torch.empty((self.max_batch_size,), dtype=torch.int32).pin_memory() for _ in range(2)]
         host = self._tok_host[k][:len(ids)]
         host.copy_(out, non_blocking=True)
+        ops.status_to_host_async()
         ev = torch.cuda.Event()
         ev.record()
         return dict(graph=graph, ids=ids, host=host, event=ev, h2d=graph.last_h2d_bytes)
@@ -273,6 +275,7 @@ class Engine:
             if all(need <= g.pool.num_free for g in self.cache.groups):
                 self._ahead = self._launch_decode(graph, seqs, None, 1)
         cur["event"].synchronize()
+        ops.raise_if_gave_up()
         toks = cur["host"].tolist()
         self._last_h2d = cur["h2d"]
         if cur["ids"] == ids:
@@ -317,7 +320,11 @@ class Engine:
                                          (w.n_tokens - 1,) if w.wants_token else ()) for w in work]
                     logits = self.runner.step(entries)
                     with prof.bucket("sampling"):
-                        toks = self.sample_workloads(work, logits).cpu().tolist() if wanting else []
+                        chosen = self.sample_workloads(work, logits) if wanting else None
+                        ops.status_to_host_async()
+                        toks = chosen.cpu().tolist() if wanting else []
+                        if wanting:
+                            ops.raise_if_gave_up()
                     h2d = self.runner.last_h2d_bytes
                 prof.set_step_tokens(len(wanting))
                 prof.set_step_seq_len([w.start + w.n_tokens for w in work])

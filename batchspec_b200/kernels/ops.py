@@ -418,18 +418,46 @@ def _status_word(device) -> torch.Tensor:
     return _status[device]
 
 
+def _raise_status(dev, code: int) -> None:
+    _status[dev].zero_()
+    for bufs in _tile_counters.values():
+        for b in bufs:
+            b.zero_()
+    raise KernelError(f"a kernel on {dev} gave up a bounded wait (code {code}: GEMM 1 = stage never freed, "
+                      f"2 = operands never arrived, 3 = accumulator never completed; attention 11 = stage "
+                      f"never freed, 12 = keys never arrived, 3x = a role of the prompt kernel).  The results of "
+                      f"the steps since the last check are not valid.")
+
+
 def check_status() -> None:
     """Raise if a kernel of this package gave up on a bounded wait (synchronises)."""
     for dev, t in _status.items():
         code = int(t.item())
         if code:
-            t.zero_()
-            for bufs in _tile_counters.values():
-                for b in bufs:
-                    b.zero_()
-            raise KernelError(f"a kernel on {dev} gave up a bounded wait (code {code}: GEMM 1 = stage never freed, "
-                              f"2 = operands never arrived, 3 = accumulator never completed; attention 11 = stage "
-                              f"never freed, 12 = keys never arrived)")
+            _raise_status(dev, code)
+
+
+_status_host = {}
+
+
+def status_to_host_async() -> None:
+    """Enqueue, on the current stream, a copy of the status word into pinned host memory: whoever synchronises
+    with the stream next (to read a step's tokens or logits) calls ``raise_if_gave_up`` afterwards, so that a step
+    whose kernels gave up a wait is never taken for a result, at no extra synchronisation."""
+    for dev, t in _status.items():
+        if dev not in _status_host:
+            _status_host[dev] = torch.zeros((1,), dtype=torch.int32).pin_memory()
+        _status_host[dev].copy_(t, non_blocking=True)
+
+
+def raise_if_gave_up() -> None:
+    """After a synchronisation that followed ``status_to_host_async``: raise if the copy shows a wait given up."""
+    for dev, h in _status_host.items():
+        code = int(h[0])
+        if code:
+            h.zero_()
+            torch.cuda.synchronize(dev)
+            _raise_status(dev, code)
 
 
 # BSPEC_STREAM_GEMM=1 sends decode-sized products (at most STREAM_GEMM_MAX_M tokens) to the kernel that gives every

@@ -373,6 +373,30 @@ def test_prompts_held_up_for_pages_beside_a_step_launched_ahead(tmp_path):
     assert got == want
 
 
+@pytest.mark.parametrize("graphs", [False, True])
+def test_a_wait_given_up_is_reported_not_taken_for_a_result(tmp_path, graphs):
+    """Kernels bound their waits and record a code in a status word when they give one up.  The engine looks at that
+    word whenever it reads a step's tokens.  The word is set by hand here (no kernel is made to wait in vain): the
+    next read raises instead of returning tokens, and afterwards the engine works as before."""
+    from batchspec_b200.engine import Sequence
+    from batchspec_b200.kernels import ops
+    cfgj, seed, page = H.TINY["C"]
+    folder = H.make_folder(tmp_path, cfgj, seed, dtype=torch.bfloat16)
+    eng = engine_for(folder, "bfloat16", page, max_batch=2, max_seq=64)
+    eng.use_cuda_graphs = graphs
+    eng.setup_sampling_params(temperature=0.0)
+    prompts = [H.random_tokens(9, cfgj["vocab_size"], 3), H.random_tokens(14, cfgj["vocab_size"], 4)]
+
+    def run():
+        return [s.output_ids for s in sorted(eng.generate([Sequence(i, p, max_new_tokens=6)
+                                                            for i, p in enumerate(prompts)]), key=lambda s: s.seq_id)]
+    want = run()
+    ops._status_word(torch.device(DEV)).fill_(12)
+    with pytest.raises(ops.KernelError, match="code 12"):
+        run()
+    assert run() == want
+
+
 def test_command_line_entry_point(tmp_path):
     cfgj, seed, page = H.TINY["A"]
     folder = H.make_folder(tmp_path / "m", cfgj, seed, dtype=torch.bfloat16)
