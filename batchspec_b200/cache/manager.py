@@ -212,6 +212,20 @@ class CacheManager:
         ps = self.page_size
         return -(-(length + n_new) // ps) - (-(-length // ps))
 
+    def peak_pages(self, total_len: int, portion: int) -> List[int]:
+        """Per group, the most pages one request of ``total_len`` tokens holds at any time when it is fed in
+        portions of at most ``portion`` tokens: all of them in a group that keeps every key; in a window's group
+        the pages from the oldest key a query still reads to the end of the portion being written (the pages the
+        window has passed were given back at the commit before)."""
+        ps = self.page_size
+        out = []
+        for g in self.groups:
+            n = -(-total_len // ps)
+            if g.spec.policy == "window":
+                n = min(n, (g.spec.window - 1 + max(1, portion) + ps - 1) // ps + 1)
+            out.append(n)
+        return out
+
     def pages_missing(self, req_id, n_new: int) -> int:
         """Pages a live request still has to get before it can take n_new more tokens (pages it already holds
         beyond its length, from a reservation that was never committed, count as held)."""

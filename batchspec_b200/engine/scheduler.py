@@ -90,9 +90,17 @@ class Scheduler:
             return "max_new_tokens must be >= 1"
         if s.prompt_len + 1 > self.max_model_len:
             return f"prompt of {s.prompt_len} tokens does not fit the context of {self.max_model_len}"
-        if self.cache.pages_needed(0, s.prompt_len + 1) > self._pool_pages():
+        first = min(self.prefill_chunk_len, self.max_tokens_per_step, s.prompt_len)
+        if self._outgrows_a_pool(s.prompt_len + 1) or self.cache.pages_needed(0, first) > self._pool_pages():
             return f"prompt of {s.prompt_len} tokens needs more pages than the whole pool has"
         return None
+
+    def _outgrows_a_pool(self, total_len: int) -> bool:
+        """True if a request of this many tokens, alone in the cache and fed token by token (portions shrink to the
+        room there is), would still need more pages of a group than that group's pool has.  A window's group only
+        ever holds the window and the tokens in flight."""
+        return any(need > g.pool.num_pages
+                   for need, g in zip(self.cache.peak_pages(total_len, 1), self.cache.groups))
 
     # -- planning ------------------------------------------------------------------
     def _preempt_latest(self) -> Sequence:
@@ -112,7 +120,7 @@ class Scheduler:
         cache = self.cache
         while True:
             # a live request whose known tokens no longer fit the whole pool can never go on
-            for s in [s for s in self.running if cache.pages_needed(0, s.total_len) > self._pool_pages()]:
+            for s in [s for s in self.running if self._outgrows_a_pool(s.total_len)]:
                 self._retire(s, "cache")
             budget = self.max_tokens_per_step
             free = self._free_pages()

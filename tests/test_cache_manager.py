@@ -142,3 +142,26 @@ def test_random_orders_keep_the_books(seed):
     m.release_all()
     m.check_invariants()
     assert all(g.pool.num_free == g.pool.num_pages for g in m.groups)
+
+
+def test_peak_pages_bound_what_a_request_ever_holds():
+    """``peak_pages`` is what the scheduler compares with the pools' sizes: never less than what a request holds
+    in any group at any moment, whatever the window, the page size and the portions; and small for a window."""
+    rng = random.Random(3)
+    for _ in range(200):
+        ps, window = rng.choice([1, 4, 8, 16]), rng.randint(1, 40)
+        portion, total = rng.randint(1, 30), rng.randint(1, 200)
+        needs = [CacheNeed(FULL, None, None), CacheNeed(CacheSpec("window", (2, 16), window=window), None, None)]
+        m = CacheManager(needs, ps, 400, 1, torch.float32, "cpu", allocate=False)
+        peak = m.peak_pages(total, portion)
+        assert peak[0] == -(-total // ps) and peak[1] <= peak[0]
+        assert peak[1] <= (window + portion) // ps + 3
+        m.admit("r")
+        done, worst = 0, [0, 0]
+        while done < total:
+            n = min(rng.randint(1, portion), total - done)
+            m.reserve("r", n)
+            worst = [max(w, g.pool.num_held) for w, g in zip(worst, m.groups)]
+            m.commit("r", n)
+            done += n
+        assert worst[0] <= peak[0] and worst[1] <= peak[1], (ps, window, portion, total, worst, peak)

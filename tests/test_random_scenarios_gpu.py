@@ -143,3 +143,95 @@ def test_step_function_under_random_cuts(folders):
     oracle = {}
     for seed in range(120):
         _replay_scenario(seed, folders, oracle)
+
+
+def test_generation_with_a_windows_group_under_random_pressure(tmp_path):
+    """An architecture registered here from the framework's own parts: one layer that keeps every key and two
+    that read a window, so that the cache has two groups with pools of their own and the window's pool is far
+    smaller than a request.  Generation through tight pools, captured steps and steps launched ahead gives the
+    tokens of a roomy eager engine."""
+    from dataclasses import dataclass
+    from batchspec_b200.config import config_from_json_dict, register_config_class
+    from batchspec_b200.engine import Sequence
+    from batchspec_b200.models import LayerSpec, ModelSpec, RunEntry, register_model
+    from batchspec_b200.parts import PartSpec
+    from batchspec_b200.weights import write_random_model
+    W, HD, HQ, HKV, VOC = 32, 16, 2, 1, 97
+
+    @dataclass(frozen=True)
+    class WinConfig:
+        architecture: str
+        vocab_size: int
+        eps: float
+        window: int
+
+        @classmethod
+        def from_json_dict(cls, d):
+            return cls(d["architectures"][0], d["vocab_size"], d["eps"], d["window"])
+
+        def to_json_dict(self):
+            return dict(architectures=[self.architecture], vocab_size=self.vocab_size, eps=self.eps,
+                        window=self.window)
+
+    def build(cfg):
+        norm = PartSpec("rmsnorm", dict(dim=W, eps=cfg.eps))
+        pos = PartSpec("rope", dict(head_dim=HD, theta=100.0))
+        full = PartSpec("attention", dict(dim=W, n_heads=HQ, n_kv_heads=HKV, head_dim=HD, position=pos))
+        near = PartSpec("attention", dict(dim=W, n_heads=HQ, n_kv_heads=HKV, head_dim=HD, window=cfg.window,
+                                          position=pos))
+        ffn = PartSpec("swiglu", dict(dim=W, intermediate=40))
+
+        def names(p):
+            n = {"norm1.weight": p + ".n1", "norm2.weight": p + ".n2", "ffn.gate": p + ".gate", "ffn.up": p + ".up",
+                 "ffn.down": p + ".down"}
+            n.update({"mixer." + k: p + "." + k for k in "qkvo"})
+            return n
+        layers = [LayerSpec(norm, full, norm, ffn, names("a")), LayerSpec(norm, near, norm, ffn, names("b")),
+                  LayerSpec(norm, near, norm, ffn, names("c"))]
+        return ModelSpec(cfg.vocab_size, W, layers, [RunEntry(0), RunEntry(1), RunEntry(2)], norm, "emb",
+                         {"weight": "final"}, None)
+
+    register_config_class("ToyWindowLM", WinConfig)
+    register_model("ToyWindowLM", build)
+    folders = {}
+    for window in (5, 17, 40):
+        cfg = config_from_json_dict(dict(architectures=["ToyWindowLM"], vocab_size=VOC, eps=1e-5, window=window))
+        folders[window] = write_random_model(cfg, tmp_path / f"w{window}", seed=window, dtype=torch.float32, std=0.08,
+                                             norm_std=0.1)
+    preempted = 0
+    for seed in range(40):
+        rng = random.Random(seed)
+        window, page, max_seq = rng.choice(list(folders)), rng.choice([4, 8, 16]), rng.choice([64, 128, 200])
+        prompts, limits = [], []
+        for i in range(rng.randint(1, 12)):
+            n = rng.randint(1, 20) if rng.random() < 0.5 else rng.randint(1, max_seq - 8)
+            prompts.append(H.random_tokens(n, VOC, seed * 100 + i))
+            limits.append(rng.randint(1, max(1, min(60, max_seq - n))))
+        max_batch, chunk = rng.randint(1, 5), rng.choice([2, 5, 8, 16, 24, 64])
+        budget = max(chunk, max_batch, rng.choice([chunk, 2 * chunk, 48]))
+        sampled = rng.random() < 0.5
+        tight = [-(-max(len(p) + m for p, m in zip(prompts, limits)) // page) + rng.randint(1, 10),
+                 max((window + page - 1) // page + 1, -(-min(chunk, budget) // page)) + rng.randint(0, 4)]
+        graphs, ahead = rng.random() < 0.8, rng.random() < 0.7
+        drew = dict(seed=seed, window=window, page=page, max_seq=max_seq, max_batch=max_batch, chunk=chunk,
+                    budget=budget, sampled=sampled, pages=tight, graphs=graphs, ahead=ahead,
+                    lens=[len(p) for p in prompts], limits=limits)
+
+        def run(num_pages, graphs, ahead):
+            eng = _engine(folders[window], "float32", page, max_batch, max_seq_length=max_seq,
+                          prefill_chunk_size=chunk, max_tokens_per_step=budget, num_pages=num_pages)
+            eng.use_cuda_graphs, eng.decode_lookahead = graphs, ahead
+            eng.setup_sampling_params(temperature=0.9 if sampled else 0.0, top_k=20, top_p=0.9, seed=seed)
+            done = eng.generate([Sequence(i, p, max_new_tokens=m) for i, (p, m) in enumerate(zip(prompts, limits))])
+            eng.cache.check_invariants()
+            assert all(g.pool.num_held == 0 for g in eng.cache.groups), drew
+            assert [g.spec.policy for g in eng.cache.groups] == ["full", "window"]
+            return ({s.seq_id: list(s.output_ids) for s in done}, {s.seq_id: s.finish_reason for s in done},
+                    eng.last_stats["preemptions"])
+        roomy = sum(-(-(len(p) + m) // page) for p, m in zip(prompts, limits)) + 8
+        want = run([roomy, roomy], False, False)
+        got = run(tight, graphs, ahead)
+        assert got[0] == want[0] and got[1] == want[1], drew
+        assert set(want[1].values()) == {"length"}, drew
+        preempted += got[2]
+    assert preempted > 20

@@ -161,3 +161,28 @@ def test_random_workloads_finish_with_clean_books(seed):
                 assert s.output_ids[-1] == 3 and 3 not in s.output_ids[:-1]
     assert cache.groups[0].pool.num_free == cache.groups[0].pool.num_pages
     cache.check_invariants()
+
+
+def test_a_windows_small_pool_does_not_refuse_a_long_prompt():
+    """A group of layers that reads a window of keys gives pages back as the window passes: its pool need not hold
+    a whole request.  A prompt longer than that pool is admitted, fed in portions and decoded to its end; only a
+    pool that cannot hold the first portion, or the window plus the token in flight, refuses it."""
+    win = CacheSpec("window", (1, 16), window=6)
+    def build(win_pages):
+        cache = CacheManager([CacheNeed(FULL, None, None), CacheNeed(win, None, None)], 4, [64, win_pages], 2,
+                             torch.float32, "cpu", allocate=False)
+        return cache, Scheduler(cache, 2, 8, 8, 1000)
+    cache, sched = build(5)                      # 20 tokens' worth of pages for the window's group
+    sched.add_sequences([Sequence(0, list(range(50)), 9), Sequence(1, list(range(31)), 4)])
+    run(cache, sched)
+    done = sorted(sched.completed, key=lambda s: s.seq_id)
+    assert [s.finish_reason for s in done] == ["length", "length"] and [len(s.output_ids) for s in done] == [9, 4]
+    assert all(g.pool.num_held == 0 for g in cache.groups) and cache.groups[1].pool.high_water <= 5
+    cache, sched = build(3)                      # later portions shrink to the room there is
+    sched.add_sequences([Sequence(0, list(range(50)), 9)])
+    run(cache, sched)
+    assert sched.completed[0].finish_reason == "length" and cache.groups[1].pool.high_water <= 3
+    for pages in (2, 1):                         # window 6 and a token in pages of 4 can take 3; the first portion 2
+        cache, sched = build(pages)
+        sched.add_sequences([Sequence(0, list(range(50)), 9)])
+        assert sched.completed[0].status is Status.FAILED and "more pages" in sched.completed[0].finish_reason
