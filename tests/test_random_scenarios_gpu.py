@@ -235,3 +235,47 @@ def test_generation_with_a_windows_group_under_random_pressure(tmp_path):
         assert set(want[1].values()) == {"length"}, drew
         preempted += got[2]
     assert preempted > 20
+
+
+def test_random_configurations_of_the_architecture(tmp_path):
+    """Every size the configuration allows, drawn at random: head sizes in steps of 16 up to 256, any number of
+    heads and groups, widths, inner sizes and vocabularies that are odd or no power of two, tied or separate
+    output weights, every kind of position scaling, every page size; both dtypes; mixed replay with reused pages
+    against the plain implementation."""
+    from batchspec_b200.engine import Engine
+    for seed in range(80):
+        rng = random.Random(seed)
+        hd = 16 * rng.randint(1, 16) if rng.random() < 0.6 else rng.choice([64, 128, 256])
+        hkv, group = rng.randint(1, 4), rng.choice([1, 2, 3, 4, 5, 8])
+        hidden = rng.choice([rng.randint(4, 80) * 8, rng.randint(20, 300) * 2, rng.randint(33, 301), 256, 512])
+        inter = rng.choice([rng.randint(4, 100) * 8, rng.randint(33, 400), 128 * rng.randint(1, 6)])
+        vocab = rng.choice([rng.randint(50, 3000), 1024, 128 * rng.randint(1, 20)])
+        scaling = rng.choice([None, dict(rope_type="linear", factor=2.0),
+                              dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                   original_max_position_embeddings=64)])
+        cfgj = dict(architectures=["LlamaForCausalLM"], model_type="llama", hidden_act="silu", vocab_size=vocab,
+                    hidden_size=hidden, num_hidden_layers=rng.randint(1, 2), num_attention_heads=hkv * group,
+                    num_key_value_heads=hkv, head_dim=hd, intermediate_size=inter,
+                    rms_norm_eps=rng.choice([1e-5, 1e-6, 3e-4]), rope_theta=rng.choice([10000.0, 500000.0]),
+                    rope_scaling=scaling, max_position_embeddings=512, tie_word_embeddings=rng.random() < 0.5)
+        dtype, page = rng.choice(["float32", "bfloat16"]), rng.choice([4, 8, 16, 32, 64])
+        folder = H.make_folder(tmp_path / f"s{seed}", cfgj, seed, std=min(0.08, 1.2 / hidden ** 0.5),
+                               dtype=torch.float32 if dtype == "float32" else torch.bfloat16)
+        requests = {f"r{i}": H.random_tokens(rng.randint(1, rng.choice([10, 70, 300])), vocab, seed * 10 + i)
+                    for i in range(rng.randint(1, 4))}
+        sizes = rng.choice([(1,), (2, 1), (5, 2, 9, 1, 3, 16, 1, 1, 7, 2), (64, 1, 1), (33, 17, 1), (300,),
+                            (130, 1, 1, 1)])
+        steps = H.mixed(requests, seed, max_live=rng.randint(1, 4), sizes=sizes)
+        eng = Engine(dtype=dtype, device="cuda:0")
+        eng.load_model(model_dir=folder)
+        eng.setup_caches(max_batch_size=4, page_size=page,
+                         num_pages=max(1, -(-H.max_live_tokens(steps, 64) // page)))
+        got = H.run_steps_in_process(eng, steps)
+        drew = {k: cfgj[k] for k in ("head_dim", "num_attention_heads", "num_key_value_heads", "hidden_size",
+                                      "intermediate_size", "vocab_size")}
+        for rid, toks in requests.items():
+            ref = H.oracle_logits(folder, toks)
+            scale = np.abs(ref).max()
+            for p in range(len(toks)):
+                err = float(np.abs(got[(rid, p)].astype(np.float64) - ref[p]).max() / scale)
+                assert err <= H.TOL[dtype], (seed, dtype, page, drew, rid, p, err)
