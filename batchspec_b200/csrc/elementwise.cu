@@ -203,16 +203,21 @@ __global__ void silu_mul_kernel(const T* __restrict__ u, T* __restrict__ m, int 
   }
 }
 
-// the same, eight bfloat16 per thread (I, and the group if any, multiples of 8)
+// the same, eight bfloat16 per thread (I, and the group if any, multiples of 8): grid.x over the columns, grid.y
+// over the rows (no 64-bit divisions per element), the exponential and the quotient in their fast forms (their
+// error is far below bfloat16's step)
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ u, __nv_bfloat16* __restrict__ m, int inter,
-                                       size_t total8, int group) {
+                                       int n, int group) {
   bspec::pdl_prologue(4);
-  const int inter8 = inter / 8;
-  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8;
-       idx += (size_t)gridDim.x * blockDim.x) {
-    const size_t row = idx / inter8, c8 = idx - row * inter8;
-    const uint4 gv = *reinterpret_cast<const uint4*>(u + row * 2 * inter + gate_col(c8 * 8, inter, group));
-    const uint4 uv = *reinterpret_cast<const uint4*>(u + row * 2 * inter + up_col(c8 * 8, inter, group));
+  const int c8 = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c8 * 8 >= inter) return;
+  const int col = c8 * 8;
+  const int gcol = group > 0 ? (col / group) * 2 * group + (col % group) : col;
+  const int ucol = group > 0 ? gcol + group : inter + col;
+  for (int row = blockIdx.y; row < n; row += gridDim.y) {
+    const __nv_bfloat16* src = u + (size_t)row * 2 * inter;
+    const uint4 gv = *reinterpret_cast<const uint4*>(src + gcol);
+    const uint4 uv = *reinterpret_cast<const uint4*>(src + ucol);
     const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
     const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
     uint4 ov;
@@ -220,10 +225,10 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ u, __nv
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const float ga = __low2float(g2[j]), gb = __high2float(g2[j]);
-      const float sa = ga / (1.f + expf(-ga)), sb = gb / (1.f + expf(-gb));
+      const float sa = __fdividef(ga, 1.f + __expf(-ga)), sb = __fdividef(gb, 1.f + __expf(-gb));
       o2[j] = __floats2bfloat162_rn(sa * __low2float(u2[j]), sb * __high2float(u2[j]));
     }
-    *reinterpret_cast<uint4*>(m + row * inter + c8 * 8) = ov;
+    *reinterpret_cast<uint4*>(m + (size_t)row * inter + col) = ov;
   }
 }
 
@@ -233,11 +238,11 @@ BSPEC_API int bspec_silu_mul(const void* u, void* m, int dtype, int n, int inter
   const int threads = 256;
   if (group < 0 || (group > 0 && inter % group != 0)) return (int)cudaErrorInvalidValue;
   if (dtype == BSPEC_BF16 && inter % 8 == 0 && group % 8 == 0) {
-    const size_t total8 = total / 8;
-    size_t want = (total8 + threads - 1) / threads;
-    const int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
-    BSPEC_LAUNCH((silu_mul_bf16x8_kernel), blocks, threads, 0, stream, (const __nv_bfloat16*)u, (__nv_bfloat16*)m,
-                 inter, total8, group);
+    const int inter8 = inter / 8;
+    const int tx = inter8 >= 256 ? 256 : ((inter8 + 31) / 32) * 32;
+    const dim3 grid((inter8 + tx - 1) / tx, n > 32768 ? 32768 : n);
+    BSPEC_LAUNCH((silu_mul_bf16x8_kernel), grid, tx, 0, stream, (const __nv_bfloat16*)u, (__nv_bfloat16*)m, inter, n,
+                 group);
     return BSPEC_LAUNCH_CHECK();
   }
   size_t want = (total + threads - 1) / threads;
