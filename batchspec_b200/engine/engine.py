@@ -59,6 +59,8 @@ class Engine:
         self.max_seq_length = None
         self.decode_lookahead = True        # launch the next captured decode step before reading this one's tokens
         self._ahead = None
+        self._tok_host = None               # two pinned buffers that captured steps' tokens are copied into in turn
+        self._tok_turn = 0
         self.prefill_chunk_size = 128
         self.max_tokens_per_step = 2048
         self.sampling = SamplingParams()
@@ -77,7 +79,6 @@ class Engine:
         """Either ``model_dir`` (config.json + safetensors), or a configuration
         (``config`` object or ``config_name`` of the by-name table) with
         ``random_seed`` for random weights."""
-        from ..kernels import ops
         ops.load_library()
         torch.cuda.set_device(self.device)
         runtime = Runtime(self.dtype, self.device)
@@ -230,8 +231,8 @@ class Engine:
                         [d.top_k if s.top_k is None else s.top_k for s in seqs],
                         [d.top_p if s.top_p is None else s.top_p for s in seqs],
                         ids, [len(s.output_ids) + ahead for s in seqs])
-        k = self._tok_turn = (getattr(self, "_tok_turn", 0) + 1) % 2
-        if not hasattr(self, "_tok_host") or self._tok_host[0].numel() < self.max_batch_size:
+        k = self._tok_turn = (self._tok_turn + 1) % 2
+        if self._tok_host is None or self._tok_host[0].numel() < self.max_batch_size:
             self._tok_host = [torch.empty((self.max_batch_size,), dtype=torch.int32).pin_memory() for _ in range(2)]
         host = self._tok_host[k][:len(ids)]
         host.copy_(out, non_blocking=True)
