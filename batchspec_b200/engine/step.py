@@ -189,7 +189,8 @@ class StepRunner:
             seen.add(e.req_id)
             if not cache.is_live(e.req_id):
                 raise KeyError(f"request {e.req_id!r} is not live (admit it first)")
-        if not cache.can_reserve([(cache.requests[e.req_id].length, len(e.tokens)) for e in entries]):
+        need = sum(cache.pages_missing(e.req_id, len(e.tokens)) for e in entries)   # pages held ahead count as held
+        if any(need > g.pool.num_free for g in cache.groups):
             from ..cache.manager import OutOfPages
             raise OutOfPages("the step needs more pages than are free; nothing was run")
         for e in entries:
