@@ -150,10 +150,39 @@ def bench_small(cfg, ms, timer, pk, dev):
             print(f"{name:16s} {rows:5d} | {t:8.4f} {rows * cfg.vocab_size * 4 / t / 1e6:7.0f}")
 
 
+def bench_prompt_step(cfg, layers, tokens):
+    """One prompt of ``tokens`` tokens through the engine's own step function, with ``layers`` of the
+    configuration's layers (random weights): the step whose kernels a launch list should show."""
+    import dataclasses
+    import random
+    from ..engine import Engine, StepEntry
+    cfg = dataclasses.replace(cfg, num_hidden_layers=layers)
+    eng = Engine(dtype="bfloat16", device="cuda:0")
+    eng.load_model(config=cfg, random_seed=0, draw_on_device=True)
+    eng.setup_caches(max_batch_size=1, max_seq_length=tokens + 16, page_size=16)
+    rng = random.Random(0)
+    prompt = [rng.randrange(cfg.vocab_size) for _ in range(tokens)]
+    print(f"prompt step: {tokens} tokens, {layers} layers |       ms")
+    for it in range(4):
+        eng.admit("p")
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        eng.step([StepEntry("p", prompt, want=(tokens - 1,))])
+        end.record()
+        torch.cuda.synchronize()
+        eng.release("p")
+        print(f"{'first (allocations, plans)' if it == 0 else 'step':>42s} | {start.elapsed_time(end):8.3f}")
+    ops.check_status()
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--config", default="llama-3-8b")
-    ap.add_argument("--what", nargs="+", default=["gemm", "attention", "small"], choices=["gemm", "attention", "small"])
+    ap.add_argument("--what", nargs="+", default=["gemm", "attention", "small"],
+                    choices=["gemm", "attention", "small", "prompt-step"])
+    ap.add_argument("--layers", type=int, default=4, help="layers of the prompt step")
+    ap.add_argument("--tokens", type=int, default=2048, help="tokens of the prompt step")
     ap.add_argument("--m", nargs="+", type=int, default=[1, 8, 64, 2048])
     ap.add_argument("--gemm-only", nargs="+", choices=["qkv", "o", "gate_up", "down", "lm_head"],
                     help="time only these projections")
@@ -173,6 +202,8 @@ def main():
             bench_attention(cfg, timer, pk, dev, cases=[tuple(c) for c in a.attn_case] if a.attn_case else None)
         if "small" in a.what:
             bench_small(cfg, [m for m in a.m if m <= 2048], timer, pk, dev)
+    if "prompt-step" in a.what:
+        bench_prompt_step(cfg, a.layers, a.tokens)
 
 
 if __name__ == "__main__":
