@@ -127,6 +127,10 @@ static void launch_add_rmsnorm_vec(float* resid, const void* delta, const void* 
                                    float eps, cudaStream_t stream) {
   const int quads = d / 4;
   int threads = quads >= 1024 ? 1024 : ((quads + 31) / 32) * 32;
+  // Many rows (a prompt): four quads per thread, so that a thread has more loads in flight and several rows share
+  // an SM; few rows (decode): as many threads per row as there are quads, for the shortest row.  Only for bfloat16
+  // output: in float32 a row's sum keeps one order of summation, whatever else is in the step.
+  if (sizeof(TO) == 2 && n >= 512 && quads >= 128) threads = (((quads + 3) / 4 + 31) / 32) * 32;
   if (threads < 32) threads = 32;
   const int vpt = (quads + threads - 1) / threads;
 #define LV(V) BSPEC_LAUNCH((add_rmsnorm_vec_kernel<TD, TO, TW, V>), n, threads, 0, stream, resid, (const TD*)delta, (const TW*)weight, (TO*)out, d, eps)

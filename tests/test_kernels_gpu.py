@@ -39,7 +39,8 @@ def test_embed(ops, dtype, n, d, vocab):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("wdtype", [torch.float32, None])
-@pytest.mark.parametrize("n,d,eps", [(3, 96, 1e-6), (17, 1000, 1e-5), (2, 4096, 1e-2), (1, 6144, 1e-5)])
+@pytest.mark.parametrize("n,d,eps", [(3, 96, 1e-6), (17, 1000, 1e-5), (2, 4096, 1e-2), (1, 6144, 1e-5),
+                                     (600, 4096, 1e-5), (513, 1000, 1e-5), (520, 8192, 1e-5)])
 def test_add_rmsnorm(ops, dtype, wdtype, n, d, eps):
     g = torch.Generator(device=DEV).manual_seed(1)
     resid = torch.randn(n, d, device=DEV, generator=g) * 3
