@@ -176,12 +176,43 @@ def bench_prompt_step(cfg, layers, tokens):
     ops.check_status()
 
 
+def bench_decode_step(cfg, layers, batch, context, steps=6):
+    """Decode steps of ``batch`` requests that each hold ``context`` tokens, with ``layers`` of the configuration's
+    layers (random weights).  The requests' pages are handed out and their lengths set without running their
+    prompts (the cache holds zeros there: the traffic is the same), so the program's first
+    launches are the decode steps themselves, which is what a launch list under a profiler needs."""
+    import dataclasses
+    from ..engine import Engine
+    cfg = dataclasses.replace(cfg, num_hidden_layers=layers)
+    eng = Engine(dtype="bfloat16", device="cuda:0")
+    eng.load_model(config=cfg, random_seed=0, draw_on_device=True)
+    eng.setup_sampling_params(temperature=0.0)
+    eng.setup_caches(max_batch_size=batch, max_seq_length=context + steps + 2, page_size=16)
+    for i in range(batch):
+        eng.admit(i)
+        eng.cache.reserve(i, context)
+        eng.cache.commit(i, context)
+    session = eng.decode_session(list(range(batch)), [1 + i for i in range(batch)])
+    print(f"decode step: {batch} requests of {context} tokens, {layers} layers |       ms")
+    for it in range(steps):
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        session.step()
+        end.record()
+        torch.cuda.synchronize()
+        print(f"{'first (eager, then captured)' if it == 0 else 'step':>52s} | {start.elapsed_time(end):8.3f}")
+    session.close()
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--config", default="llama-3-8b")
     ap.add_argument("--what", nargs="+", default=["gemm", "attention", "small"],
-                    choices=["gemm", "attention", "small", "prompt-step"])
-    ap.add_argument("--layers", type=int, default=4, help="layers of the prompt step")
+                    choices=["gemm", "attention", "small", "prompt-step", "decode-step"])
+    ap.add_argument("--batch", type=int, default=64, help="requests of the decode step")
+    ap.add_argument("--context", type=int, default=2048, help="tokens each request of the decode step holds")
+    ap.add_argument("--layers", type=int, default=4, help="layers of the prompt step or the decode step")
     ap.add_argument("--tokens", type=int, default=2048, help="tokens of the prompt step")
     ap.add_argument("--m", nargs="+", type=int, default=[1, 8, 64, 2048])
     ap.add_argument("--gemm-only", nargs="+", choices=["qkv", "o", "gate_up", "down", "lm_head"],
@@ -204,6 +235,8 @@ def main():
             bench_small(cfg, [m for m in a.m if m <= 2048], timer, pk, dev)
     if "prompt-step" in a.what:
         bench_prompt_step(cfg, a.layers, a.tokens)
+    if "decode-step" in a.what:
+        bench_decode_step(cfg, a.layers, a.batch, a.context)
 
 
 if __name__ == "__main__":
