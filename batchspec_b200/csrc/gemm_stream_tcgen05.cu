@@ -144,7 +144,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       for (int i = pre; i < n_units; ++i) {
         const int s = i % p.stages;
         const uint32_t ph = (uint32_t)(i / p.stages) & 1u;
-        if (!mbar_wait(empty + s, ph ^ 1u, abort_flag, p.status, 21)) break;
+        if (!mbar_wait(empty + s, ph ^ 1u, abort_flag, p.status, 41)) break;
         const long long u = u_begin + i;
         const int tile = (int)(u / p.kb_total), kb = (int)(u - (long long)tile * p.kb_total);
         unsigned char* dst = smem + (size_t)s * stage_bytes;
@@ -172,14 +172,14 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         u += sg.k1 - sg.k0;
         const int buf = seg_no & 1;
         // the accumulator is free once the epilogue has drained its use before the last one
-        ok = mbar_wait(acc_empty + buf, (((uint32_t)seg_no >> 1) & 1u) ^ 1u, abort_flag, p.status, 22);
+        ok = mbar_wait(acc_empty + buf, (((uint32_t)seg_no >> 1) & 1u) ^ 1u, abort_flag, p.status, 42);
         if (!ok) break;
         tc_fence_after();
         const uint32_t acc = tmem_base + (uint32_t)(buf * p.bn);
         for (int kb = sg.k0; kb < sg.k1 && ok; ++kb, ++i) {
           const int s = i % p.stages;
           const uint32_t ph = (uint32_t)(i / p.stages) & 1u;
-          ok = mbar_wait(full + s, ph, abort_flag, p.status, 23);
+          ok = mbar_wait(full + s, ph, abort_flag, p.status, 43);
           if (!ok) break;
           tc_fence_after();
           unsigned char* a_src = smem + (size_t)s * stage_bytes;
@@ -204,7 +204,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       const Segment sg = segment_at(cut, u, u_end, b);
       u += sg.k1 - sg.k0;
       const int buf = seg_no & 1;
-      ok = mbar_wait(acc_full + buf, ((uint32_t)seg_no >> 1) & 1u, abort_flag, p.status, 24);
+      ok = mbar_wait(acc_full + buf, ((uint32_t)seg_no >> 1) & 1u, abort_flag, p.status, 44);
       if (!ok) break;
       tc_fence_after();
       if (!waited) {
@@ -295,7 +295,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         while (*arrived < n_parts) {
           if (++spins > WAIT_LIMIT || *abort_flag) {
             *abort_flag = 1;
-            atomicCAS(p.status, 0, 25);
+            atomicCAS(p.status, 0, 45);
             break;
           }
           if (spins > 64) __nanosleep(32);

@@ -424,9 +424,10 @@ def _raise_status(dev, code: int) -> None:
         for b in bufs:
             b.zero_()
     raise KernelError(f"a kernel on {dev} gave up a bounded wait (code {code}: GEMM 1 = stage never freed, "
-                      f"2 = operands never arrived, 3 = accumulator never completed; attention 11 = stage "
-                      f"never freed, 12 = keys never arrived, 3x = a role of the prompt kernel).  The results of "
-                      f"the steps since the last check are not valid.")
+                      f"2 = operands never arrived, 3 = accumulator never completed; decode attention 11/13 = stage "
+                      f"never freed, 12/14 = keys never arrived; prompt attention 21/22 the same, 31-38 = a role of "
+                      f"the tensor-core prompt kernel; 41-45 = the equal-shares GEMM).  The results of the steps "
+                      f"since the last check are not valid.")
 
 
 def check_status() -> None:
