@@ -419,10 +419,11 @@ def _status_word(device) -> torch.Tensor:
 
 
 def _raise_status(dev, code: int) -> None:
-    _status[dev].zero_()
-    for bufs in _tile_counters.values():
-        for b in bufs:
-            b.zero_()
+    with torch.inference_mode():          # the words may have been made inside inference mode (by a step)
+        _status[dev].zero_()
+        for bufs in _tile_counters.values():
+            for b in bufs:
+                b.zero_()
     raise KernelError(f"a kernel on {dev} gave up a bounded wait (code {code}: GEMM 1 = stage never freed, "
                       f"2 = operands never arrived, 3 = accumulator never completed; decode attention 11/13 = stage "
                       f"never freed, 12/14 = keys never arrived; prompt attention 21/22 the same, 31-38 = a role of "
@@ -456,7 +457,8 @@ def raise_if_gave_up() -> None:
     for dev, h in _status_host.items():
         code = int(h[0])
         if code:
-            h.zero_()
+            with torch.inference_mode():
+                h.zero_()
             torch.cuda.synchronize(dev)
             _raise_status(dev, code)
 
