@@ -186,3 +186,31 @@ def test_a_windows_small_pool_does_not_refuse_a_long_prompt():
         cache, sched = build(pages)
         sched.add_sequences([Sequence(0, list(range(50)), 9)])
         assert sched.completed[0].status is Status.FAILED and "more pages" in sched.completed[0].finish_reason
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_workloads_with_a_windows_pool_finish_with_clean_books(seed):
+    """Two groups with pools of their own, the window's one tight: every request that is accepted runs to its end
+    (none is refused or cut short for the window's pool, which only has to hold the window and a portion), the
+    window's pool never holds more than it has, and all pages come back."""
+    rng = random.Random(100 + seed)
+    page, window = rng.choice([2, 4, 8]), rng.randrange(3, 20)
+    chunk, conc = rng.randrange(2, 12), rng.randrange(1, 5)
+    budget = rng.randrange(max(4, conc), 24)
+    first = min(chunk, budget)
+    win_pages = max((window + page - 1) // page + 1, -(-first // page)) + rng.randrange(0, 4)
+    win = CacheSpec("window", (1, 16), window=window)
+    cache = CacheManager([CacheNeed(FULL, None, None), CacheNeed(win, None, None)], page, [200, win_pages], conc,
+                         torch.float32, "cpu", allocate=False)
+    sched = Scheduler(cache, conc, budget, chunk, 120, (3,))
+    seqs = [Sequence(i, [rng.randrange(10) for _ in range(rng.randrange(1, 80))], rng.randrange(1, 30))
+            for i in range(20)]
+    sched.add_sequences(seqs)
+    run(cache, sched, token_of=lambda s: rng.randrange(10))
+    assert len(sched.completed) == 20 and not sched.running and not sched.waiting_queue
+    for s in sched.completed:
+        assert s.status is Status.COMPLETE and s.finish_reason in ("eos", "length", "context"), \
+            (s.seq_id, s.status, s.finish_reason, page, window, win_pages, chunk, budget)
+    assert cache.groups[1].pool.high_water <= win_pages
+    assert all(g.pool.num_free == g.pool.num_pages for g in cache.groups)
+    cache.check_invariants()
