@@ -9,9 +9,9 @@ checkpoint names.  The reference fixes the parts by subclass hooks
 one model may mix different mixers and feed-forwards.
 
 Registries: ``MIXERS``, ``FEED_FORWARDS``, ``NORMS``, ``POSITION_ENCODINGS``,
-``BLOCKS``.  ``register_part(registry, kind)`` is a class decorator;
-``build_part(registry, spec, runtime)`` instantiates ``spec.kind`` with
-``spec.params``.
+``BLOCKS``, ``INPUT_PARTS``, ``LOGITS_PARTS``.  ``register_part(registry, kind)``
+is a class decorator; ``build_part(registry, spec, runtime)`` instantiates
+``spec.kind`` with ``spec.params``.
 """
 from __future__ import annotations
 
@@ -49,11 +49,17 @@ class CacheSpec:
     policy ``full``: every token's entry is kept while the request lives.
     policy ``window``: only the last ``window`` tokens are ever read; pages that
     lie wholly before the window are given back.
-    ``entry_shape`` is the per-token shape of ONE of the two stored tensors
-    (keys, values), e.g. (n_kv_heads, head_dim)."""
+    ``entry_shape`` is the per-token shape of ONE stored tensor, e.g.
+    (n_kv_heads, head_dim); ``tensors`` says how many of them a token has: 2 for
+    keys and values, 1 for a mixer that stores a single (compressed) entry.
+    ``page_size``: tokens per page of this mixer's group, or None for the
+    engine's default; groups with different page sizes have block tables of
+    different lengths for the same request."""
     policy: str
     entry_shape: Tuple[int, ...]
     window: Optional[int] = None
+    tensors: int = 2
+    page_size: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -136,16 +142,20 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
-class Block:
-    """Arrangement of norm / mixer / norm / feed-forward around the residual
-    stream.  ``forward(resid, pending, ctx, cache)`` takes the float32 residual
-    and a not-yet-added branch output (or None) and returns the same pair, so the
-    add can be fused into the next norm."""
+class InputPart(Part):
+    """Runs once per step right after the embedding: ``forward(resid, ctx)`` changes
+    the float32 residual rows [n, d] in place (a learned absolute position row
+    added to each token, a multiplier ...)."""
 
-    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, ffn: FeedForward):
-        self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
+    def forward(self, resid: torch.Tensor, ctx) -> None:
+        raise NotImplementedError
 
-    def forward(self, resid, pending, ctx, cache):
+
+class LogitsPart(Part):
+    """Runs once per step on the head's output: ``forward(logits, ctx)`` changes the
+    float32 logits [wanted rows, vocab] in place (a scale, a soft cap ...)."""
+
+    def forward(self, logits: torch.Tensor, ctx) -> None:
         raise NotImplementedError
 
 
@@ -154,6 +164,36 @@ FEED_FORWARDS: Dict[str, type] = {}
 NORMS: Dict[str, type] = {}
 POSITION_ENCODINGS: Dict[str, type] = {}
 BLOCKS: Dict[str, type] = {}
+INPUT_PARTS: Dict[str, type] = {}
+LOGITS_PARTS: Dict[str, type] = {}
+
+
+class Block:
+    """Arrangement of a layer's parts around the residual stream.  A block kind
+    declares its slots as data: ``SLOTS`` maps slot name -> the registry its part
+    comes from, in the order the parts' tensors are listed; the model description
+    gives one ``PartSpec`` per slot.  ``MIXER_SLOT`` names the slot whose part
+    (a ``Mixer``) owns the layer's cache and per-request state.  The built parts
+    arrive as keyword arguments and are kept as attributes of the same names and in
+    ``self.parts``.
+
+    ``forward(resid, pending, ctx, cache)`` takes the float32 residual and a
+    not-yet-added branch output (or None) and returns the same pair, so the add
+    can be fused into the next norm."""
+    SLOTS: Dict[str, Dict[str, type]] = {}
+    MIXER_SLOT = "mixer"
+
+    def __init__(self, **parts):
+        missing, extra = set(self.SLOTS) - set(parts), set(parts) - set(self.SLOTS)
+        if missing or extra:
+            raise ValueError(f"block {type(self).__name__} has slots {list(self.SLOTS)}; missing {sorted(missing)}, "
+                             f"unexpected {sorted(extra)}")
+        self.parts = {slot: parts[slot] for slot in self.SLOTS}
+        for slot, part in self.parts.items():
+            setattr(self, slot, part)
+
+    def forward(self, resid, pending, ctx, cache):
+        raise NotImplementedError
 
 
 def register_part(registry: Dict[str, type], kind: str):

@@ -189,6 +189,54 @@ def run_e2e(eng, cfg, batch, steps, warmup, page_size=16):
     return st["decode_tokens"] / st["decode_seconds"], st["decode_h2d_bytes_per_step"], st["decode_d2h_bytes_per_step"]
 
 
+def reference_arm(a) -> int:
+    """``--impl reference``: the unmodified reference through its own ``StandardEngine.generate`` (see
+    baseline/reference_arm.py) on the same workload: batch, 2,048-token prompts, greedy decode steps.  If it cannot
+    be imported or run, one line says why and the exit code is 0."""
+    if a.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
+        return 2
+    a.warmup = max(a.warmup, 3)
+    cfg = json.loads((ROOT / "batchspec_b200" / "config" / "presets" / "llama-3-8b.json").read_text())
+    full_layers = cfg["num_hidden_layers"]
+    if a.layers:
+        cfg["num_hidden_layers"] = a.layers
+    try:
+        from baseline import reference_arm as RA
+        clocks = ClockSampler()
+        clocks.start()
+        try:
+            r = RA.bench(cfg, a.batch, PROMPT_LEN, a.steps, a.warmup)
+        finally:
+            clock_rec = clocks.stop()
+    except BaseException as exc:                                    # noqa: BLE001  (the line must say what happened)
+        if isinstance(exc, KeyboardInterrupt):
+            raise
+        why = " ".join(f"{type(exc).__name__}: {exc}".split())[:400]
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+    hd = cfg.get("head_dim") or cfg["hidden_size"] // cfg["num_attention_heads"]
+    out = {
+        "metric": f"decode tok/s (Llama-3-8B sizes, bf16, batch {a.batch}, {PROMPT_LEN}-token prompts)",
+        "value": round(a.batch * 1000.0 / r["ms_per_step"], 2), "unit": "tok/s", "n_gpus": 1, "steps": a.steps,
+        "warmup": a.warmup, "ms_per_step": round(r["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
+        "config": {"model": "llama-3-8b", "global_batch": a.batch, "seq_len": PROMPT_LEN, "parallelism": "single",
+                   "layers": cfg["num_hidden_layers"], "layers_full": full_layers, "hidden": cfg["hidden_size"],
+                   "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": hd,
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "page_size": 16,
+                   "weights": "random N(0,0.02)", "l2": "inputs_exceed_l2 (15 GB of weights per step)",
+                   "prefill_chunk": r["chunk"],
+                   "how": "StandardEngine.generate; CUDA events before each model call; tracer output discarded"},
+        "clocks": clock_rec,
+        "e2e": {"value": round(a.batch * 1000.0 / r["wall_ms_per_step"], 2), "unit": "tok/s",
+                "h2d_bytes_per_step": 0, "d2h_bytes_per_step": a.batch,
+                "note": "generate keeps token ids on the device and reads one end-of-sequence flag per request"},
+    }
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -200,10 +248,7 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (no prefill, b1, b64, e2e)")
     a = ap.parse_args()
     if a.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "siihwanpark/BatchSpec has no setup.py/pyproject.toml (pip: 'not installable') and its "
-                          "standard benchmark path calls StandardEngine.prefill/decode, which do not exist in the tree"}))
-        return 0
+        return reference_arm(a)
     if a.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
         return 2
