@@ -258,12 +258,14 @@ def generate_quietly(engine, sequences):
 
 def bench(cfg: dict, batch: int, prompt_len: int, steps: int, warmup: int, seed: int = 1) -> dict:
     """Decode speed of the reference at this batch: every request a ``prompt_len``-token prompt, prefilled in the
-    chunks its runner picks for the batch size (runner/runner.py:69-72), then ``warmup + steps + 1`` greedy tokens.
+    chunks its runner picks for the batch size (runner/runner.py:69-72), then ``warmup + steps + 1`` greedy tokens
+    (at least 32 untimed decode steps, until the SM clock has recovered from the prompt phase).
     Device time: CUDA events recorded before each model call, from the first timed decode step to the end of the
     last.  End to end: the host clock over the same steps (``generate`` keeps token ids on the device and reads
     one flag per request and step to test for the end of a sequence)."""
     import random
     import torch
+    warmup = max(warmup, 32)             # the same count of untimed decode steps as the other arm's end-to-end run
     chunk = {2: 128, 4: 128, 8: 128, 16: 128, 32: 128, 64: 64, 128: 16, 256: 8}.get(batch, 128)
     n_new = warmup + steps + 1
     max_len = prompt_len + n_new
@@ -298,7 +300,7 @@ def bench(cfg: dict, batch: int, prompt_len: int, steps: int, warmup: int, seed:
     after = probe.steps[timed[-1] + 1] if timed[-1] + 1 < len(probe.steps) else (0, end_ev, t_end)
     dev_ms = first[1].elapsed_time(after[1]) / steps
     wall_ms = (after[2] - first[2]) * 1e3 / steps
-    return dict(ms_per_step=dev_ms, wall_ms_per_step=wall_ms, steps=steps, batch=batch, chunk=chunk,
+    return dict(ms_per_step=dev_ms, wall_ms_per_step=wall_ms, steps=steps, batch=batch, chunk=chunk, warmup_steps=warmup,
                 generated=sum(int(s.num_generated_tokens) for s in done), model_calls=len(probe.steps))
 
 

@@ -70,10 +70,12 @@ class PagePool:
 
 
 class StateSlots:
-    """Ids 0..n-1 for per-request state of fixed size."""
+    """Ids 0..n-1 for per-request state of fixed size.  ``reserved`` extra ids (n ..) exist in the state tensors
+    but are never handed out: the padding rows of captured decode steps read and write the first of them."""
 
-    def __init__(self, n: int):
+    def __init__(self, n: int, reserved: int = 0):
         self.n = int(n)
+        self.reserved = int(reserved)
         self._free = list(range(self.n - 1, -1, -1))
         self._held = [False] * self.n
 
@@ -102,7 +104,7 @@ class CacheGroup:
     page_size: int
     pool: PagePool
     runs: List[int] = field(default_factory=list)        # indices into the model's order
-    pages: Optional[torch.Tensor] = None                  # [len(runs), num_pages, 2, page_size * entry_elems]
+    pages: Optional[torch.Tensor] = None       # [len(runs), num_pages, spec.tensors, page_size * entry_elems]
 
     @property
     def entry_elems(self) -> int:
@@ -124,8 +126,10 @@ class RequestCache:
 class CacheManager:
     """Built from the model's per-run needs (``DecoderModel.cache_needs()``).
 
-    ``num_pages`` is the size of every group's pool (an int, or a list per
-    group).  ``allocate=False`` keeps the bookkeeping only (tests, planning)."""
+    ``page_size`` is the default tokens-per-page; a mixer's ``CacheSpec.page_size`` overrides it for its group.
+    ``num_pages`` is the size of every group's pool in pages of the default size (a group with pages of its own
+    size gets as many as hold the same number of tokens), or a list with one count per group.
+    ``allocate=False`` keeps the bookkeeping only (tests, planning)."""
 
     def __init__(self, needs, page_size: int, num_pages, max_requests: int, dtype: torch.dtype, device,
                  allocate: bool = True, scratch_page: bool = False):
@@ -136,18 +140,24 @@ class CacheManager:
         self.max_requests = int(max_requests)
         self.dtype, self.device = dtype, device
         self.groups: List[CacheGroup] = []
-        self.slots = StateSlots(self.max_requests)
+        self.slots = StateSlots(self.max_requests, reserved=int(scratch_page))
         self.requests: Dict[object, RequestCache] = {}
         key_to_group: Dict[Tuple, int] = {}
         run_group: Dict[int, Tuple[int, int]] = {}           # run -> (group, index in group)
         for e, need in enumerate(needs):
             if need.cache is None or need.cache_from is not None:
                 continue
-            key = (need.cache.policy, need.cache.window, tuple(need.cache.entry_shape))
+            c = need.cache
+            if c.tensors < 1 or (c.page_size is not None and c.page_size <= 0):
+                raise ValueError(f"run {e}: a cache entry has at least one tensor and a positive page size, got {c}")
+            group_page = int(c.page_size or self.page_size)
+            key = (c.policy, c.window, tuple(c.entry_shape), c.tensors, group_page)
             if key not in key_to_group:
                 key_to_group[key] = len(self.groups)
                 n = num_pages[len(self.groups)] if isinstance(num_pages, (list, tuple)) else num_pages
-                self.groups.append(CacheGroup(need.cache, self.page_size, PagePool(n, reserved=int(scratch_page))))
+                if not isinstance(num_pages, (list, tuple)) and group_page != self.page_size:
+                    n = -(-n * self.page_size // group_page)         # the same number of tokens in pages of its own size
+                self.groups.append(CacheGroup(c, group_page, PagePool(n, reserved=int(scratch_page))))
             g = key_to_group[key]
             run_group[e] = (g, len(self.groups[g].runs))
             self.groups[g].runs.append(e)
@@ -155,15 +165,16 @@ class CacheManager:
             for grp in self.groups:
                 # zeroed once: kernels may load (and mask) rows of a page that no token has been written to yet,
                 # and those must not hold NaN or infinity
-                grp.pages = torch.zeros((len(grp.runs), grp.pool.num_pages + grp.pool.reserved, 2,
-                                         self.page_size * grp.entry_elems),
+                grp.pages = torch.zeros((len(grp.runs), grp.pool.num_pages + grp.pool.reserved, grp.spec.tensors,
+                                         grp.page_size * grp.entry_elems),
                                         dtype=dtype, device=device)
         self.state_tensors: List[Optional[torch.Tensor]] = []
         self.layer_caches: List[Optional[LayerCache]] = []
         for e, need in enumerate(needs):
             state = None
             if need.state is not None and allocate:
-                state = torch.zeros((self.max_requests, *need.state.shape), dtype=need.state.dtype, device=device)
+                state = torch.zeros((self.max_requests + self.slots.reserved, *need.state.shape),
+                                    dtype=need.state.dtype, device=device)
             self.state_tensors.append(state)
             owner_run = e if need.cache_from is None else need.cache_from
             if needs[owner_run].cache is None:
@@ -179,7 +190,7 @@ class CacheManager:
     def page_bytes(self) -> int:
         """Bytes of all pools' page tensors (whether or not they were allocated)."""
         item = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.runs) * (g.pool.num_pages + g.pool.reserved) * 2 * self.page_size * g.entry_elems * item
+        return sum(len(g.runs) * (g.pool.num_pages + g.pool.reserved) * g.spec.tensors * g.page_size * g.entry_elems * item
                    for g in self.groups)
 
     def scratch_pages(self) -> Optional[List[int]]:
@@ -188,6 +199,10 @@ class CacheManager:
         if not all(g.pool.reserved for g in self.groups):
             return None
         return [g.pool.num_pages for g in self.groups]
+
+    def scratch_slot(self) -> Optional[int]:
+        """The state slot that no request ever holds (None if the manager was made without one)."""
+        return self.slots.n if self.slots.reserved else None
 
     # -- requests ---------------------------------------------------------------
     def admit(self, req_id) -> RequestCache:
@@ -208,60 +223,69 @@ class CacheManager:
     def length(self, req_id) -> int:
         return self.requests[req_id].length
 
-    def pages_needed(self, length: int, n_new: int) -> int:
-        ps = self.page_size
-        return -(-(length + n_new) // ps) - (-(-length // ps))
+    def pages_needed(self, length: int, n_new: int) -> List[int]:
+        """Per group, the table entries a request of ``length`` tokens lacks for ``n_new`` more."""
+        return [-(-(length + n_new) // g.page_size) - (-(-length // g.page_size)) for g in self.groups]
 
     def peak_pages(self, total_len: int, portion: int) -> List[int]:
         """Per group, the most pages one request of ``total_len`` tokens holds at any time when it is fed in
         portions of at most ``portion`` tokens: all of them in a group that keeps every key; in a window's group
         the pages from the oldest key a query still reads to the end of the portion being written (the pages the
         window has passed were given back at the commit before)."""
-        ps = self.page_size
         out = []
         for g in self.groups:
+            ps = g.page_size
             n = -(-total_len // ps)
             if g.spec.policy == "window":
                 n = min(n, (g.spec.window - 1 + max(1, portion) + ps - 1) // ps + 1)
             out.append(n)
         return out
 
-    def pages_missing(self, req_id, n_new: int) -> int:
-        """Pages a live request still has to get before it can take n_new more tokens (pages it already holds
-        beyond its length, from a reservation that was never committed, count as held)."""
+    def pages_missing(self, req_id, n_new: int) -> List[int]:
+        """Per group, the pages a live request still has to get before it can take n_new more tokens (pages it
+        already holds beyond its length, from a reservation that was never committed, count as held)."""
         rc = self.requests[req_id]
-        return max(0, -(-(rc.length + n_new) // self.page_size) - len(rc.tables[0])) if rc.tables else 0
+        return [max(0, -(-(rc.length + n_new) // g.page_size) - len(t)) for g, t in zip(self.groups, rc.tables)]
+
+    def free_pages(self) -> List[int]:
+        return [g.pool.num_free for g in self.groups]
+
+    def room_for(self, length: int, free: Sequence[int]) -> int:
+        """How many more tokens a request of ``length`` tokens (holding exactly the pages of that length) can
+        take with at most ``free[g]`` new pages of each group."""
+        return min((f * g.page_size + (-length) % g.page_size for g, f in zip(self.groups, free)), default=1 << 60)
 
     def can_reserve(self, demands: Sequence[Tuple[int, int]]) -> bool:
         """demands: (current length, new tokens) per request; True if every pool
         can serve all of them together."""
-        need = sum(self.pages_needed(l, n) for l, n in demands)
-        return all(need <= g.pool.num_free for g in self.groups)
+        need = [0] * len(self.groups)
+        for l, n in demands:
+            need = [a + b for a, b in zip(need, self.pages_needed(l, n))]
+        return all(n <= g.pool.num_free for n, g in zip(need, self.groups))
 
     def reserve(self, req_id, n_new: int) -> None:
         """Make table entries for positions length .. length+n_new-1 in every group;
         all or nothing (raises OutOfPages and leaves the request as it was)."""
         rc = self.requests[req_id]
         need = self.pages_missing(req_id, n_new)        # reserving twice for the same step is harmless
-        if need == 0:
-            return
-        for g in self.groups:
-            if need > g.pool.num_free:
-                raise OutOfPages(f"request {req_id!r} needs {need} pages, a pool has {g.pool.num_free} free")
-        for g, table in zip(self.groups, rc.tables):
-            table.extend(g.pool.allocate(need))
+        for n, g in zip(need, self.groups):
+            if n > g.pool.num_free:
+                raise OutOfPages(f"request {req_id!r} needs {n} pages, a pool has {g.pool.num_free} free")
+        for n, g, table in zip(need, self.groups, rc.tables):
+            if n:
+                table.extend(g.pool.allocate(n))
 
     def commit(self, req_id, n_new: int) -> None:
         """The step wrote n_new tokens: grow the length and give back pages that a
         window has passed (every later query reads keys >= length - window + 1)."""
         rc = self.requests[req_id]
         rc.length += n_new
-        assert all(len(t) == -(-rc.length // self.page_size) for t in rc.tables), "block table out of step"
         for g, table in zip(self.groups, rc.tables):
+            assert len(table) == -(-rc.length // g.page_size), "block table out of step"
             if g.spec.policy != "window":
                 continue
             first_needed = max(0, rc.length - g.spec.window + 1)
-            dead = first_needed // self.page_size          # pages wholly before first_needed
+            dead = first_needed // g.page_size             # pages wholly before first_needed
             gone = [p for p in table[:dead] if p >= 0]
             if gone:
                 g.pool.free(gone)

@@ -64,6 +64,12 @@ class RopeScaling:
     @classmethod
     def from_json_dict(cls, d: Dict[str, Any]) -> "RopeScaling":
         kind = d.get("rope_type", d.get("type"))
+        read = {"rope_type", "type", "factor"} | ({"low_freq_factor", "high_freq_factor",
+                                                   "original_max_position_embeddings"} if kind == "llama3" else set())
+        unread = sorted(k for k, v in d.items() if k not in read and v is not None)
+        if unread:
+            raise ConfigError(f"config.json: rope_scaling of type {kind!r} has fields this engine does not apply: "
+                              f"{', '.join(unread)}")
         if kind == "linear":
             return cls("linear", _take(d, "factor", float))
         if kind != "llama3":
@@ -109,12 +115,34 @@ class LlamaConfig:
     bos_token_id: Optional[int] = None
     eos_token_ids: Tuple[int, ...] = ()
     torch_dtype: Optional[str] = None
+    unread_keys: Tuple[str, ...] = ()      # keys of config.json that nothing here reads or knows to be harmless
+
+    # keys whose only allowed value is the one that leaves the Llama-3 formulas as they are
+    _NEUTRAL = {"sliding_window": (None, 0), "attention_dropout": (None, 0, 0.0), "partial_rotary_factor": (None, 1, 1.0),
+                "attention_multiplier": (None,), "logits_scaling": (None, 1, 1.0), "residual_multiplier": (None, 1, 1.0),
+                "embedding_multiplier": (None, 1, 1.0), "final_logit_softcapping": (None,),
+                "attn_logit_softcapping": (None,), "use_qk_norm": (None, False), "qk_norm": (None, False),
+                "num_local_experts": (None, 0), "num_experts": (None, 0), "layer_types": (None,),
+                "no_rope_layers": (None,), "pretraining_tp": (None, 1)}
+    _READ = {"architectures", "vocab_size", "hidden_size", "num_hidden_layers", "num_attention_heads",
+             "num_key_value_heads", "head_dim", "intermediate_size", "rms_norm_eps", "rope_theta", "rope_scaling",
+             "max_position_embeddings", "tie_word_embeddings", "bos_token_id", "eos_token_id", "torch_dtype", "dtype",
+             "attention_bias", "mlp_bias", "hidden_act", "model_type"}
+    _HARMLESS = {"transformers_version", "use_cache", "pad_token_id", "initializer_range", "_name_or_path",
+                 "unread_keys"}
 
     @classmethod
     def from_json_dict(cls, d: Dict[str, Any]) -> "LlamaConfig":
         arch = (d.get("architectures") or [None])[0]
         if arch is None:
             raise ConfigError("config.json: 'architectures' is missing or empty")
+        if d.get("model_type", "llama") != "llama":
+            raise ConfigError(f"config.json: model_type {d['model_type']!r} is not 'llama'")
+        changed = sorted(k for k, ok in cls._NEUTRAL.items() if k in d and d[k] not in ok)
+        if changed:
+            raise ConfigError("config.json: " + ", ".join(f"{k}={d[k]!r}" for k in changed)
+                              + " would change the model's arithmetic and this engine does not apply it")
+        unread = tuple(sorted(k for k in d if k not in cls._READ and k not in cls._NEUTRAL and k not in cls._HARMLESS))
         n_head = _take(d, "num_attention_heads", int)
         hidden = _take(d, "hidden_size", int)
         if _take(d, "attention_bias", bool, False) or _take(d, "mlp_bias", bool, False):
@@ -142,6 +170,7 @@ class LlamaConfig:
             bos_token_id=d.get("bos_token_id"),
             eos_token_ids=eos_ids,
             torch_dtype=d.get("torch_dtype", d.get("dtype")),
+            unread_keys=unread,
         )
         cfg.validate()
         return cfg
@@ -165,7 +194,7 @@ class LlamaConfig:
             "attention_bias": False, "mlp_bias": False,
         }
         for f in fields(self):
-            if f.name in ("architecture", "rope_scaling", "eos_token_ids"):
+            if f.name in ("architecture", "rope_scaling", "eos_token_ids", "unread_keys"):
                 continue
             d[f.name] = getattr(self, f.name)
         d["rope_scaling"] = self.rope_scaling.to_json_dict() if self.rope_scaling else None

@@ -18,6 +18,7 @@
 // both.  Cache layer layout: [pages][2 (k, v)][Hkv][page_size][HD].
 #include "common.cuh"
 #include "tma.cuh"
+#include <mutex>
 #include <math.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -1387,8 +1388,12 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
            cudaStream_t stream, int balanced = 0, const int* kv_len = nullptr) {
   const float scale_log2 = scale * 1.4426950408889634f;
   const int G = Hq / Hkv;
-  static bool attr_set = false;
-  if (!attr_set) {
+  // The opt-in to large shared memory and the resident-CTA count are facts of a device: set up once per device,
+  // whichever thread gets there first.
+  static std::once_flag once_dev[bspec::kMaxDevices];
+  static int resident_dev[bspec::kMaxDevices] = {};
+  const int cur_dev = bspec::current_device();
+  std::call_once(once_dev[cur_dev], [cur_dev]() {
     cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem<HD>());
     cudaFuncSetAttribute(attn_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_tma_smem<HD>());
     cudaFuncSetAttribute(attn_decode_shares_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1398,8 +1403,12 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
     if constexpr (HD <= 128)
       cudaFuncSetAttribute(attn_prefill_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (int)prefill_tma_smem<HD>());
-    attr_set = true;
-  }
+    int per_sm = 0;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_shares_kernel<HD>, DECODE_TMA_THREADS,
+                                                  decode_shares_smem<HD>());
+    resident_dev[cur_dev] = bspec::sm_count() * (per_sm > 0 ? per_sm : 1);
+  });
+  const int resident = resident_dev[cur_dev];
   if (run_decode) {
     const int short_q = max_q_len < max_q_short ? max_q_len : max_q_short;
     const int row_tiles = (short_q * G + 15) / 16;
@@ -1411,15 +1420,6 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
       if (make_map_2d_bf16(&kv_map, cache, kv_rows, HD, page_size, 64)) {
        if (balanced && n_entries <= BAL_MAX_ENTRIES && n_splits >= 4 && n_splits <= 64 && n_tokens < (1 << 26)) {
         // equal shares of the tiles over as many CTAs as the device holds at once, then the join
-        static int resident = 0;
-        if (resident == 0) {
-          int dev = 0, sms = 0, per_sm = 0;
-          cudaGetDevice(&dev);
-          cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_shares_kernel<HD>, DECODE_TMA_THREADS,
-                                                        decode_shares_smem<HD>());
-          resident = sms * (per_sm > 0 ? per_sm : 1);
-        }
         BSPEC_LAUNCH((attn_decode_shares_kernel<HD>), dim3(resident), DECODE_TMA_THREADS, decode_shares_smem<HD>(),
                      stream, kv_map, q, q_row_stride, out, o_part, ml_part, tile_counters, status, qo_indptr, positions,
                      kv_len, kv_indptr, kv_indices, n_entries, Hq, Hkv, page_size, scale_log2, window, n_splits,
@@ -1503,7 +1503,6 @@ BSPEC_API int bspec_attention_bf16(const void* q, long long q_row_stride, void* 
 // ---------------------------------------------------------------------------------------------------------------
 // The same split-key decode attention for callers that cannot allocate: see attention_noalloc.h.
 #include "attention_noalloc.h"
-#include <mutex>
 #include <stdio.h>
 
 namespace {

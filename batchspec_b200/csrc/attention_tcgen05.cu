@@ -542,7 +542,8 @@ BSPEC_API int bspec_attention_prefill_tc(const void* q, long long q_row_stride, 
   if (Hkv > 65535 || n_entries > 65535) return (int)cudaErrorInvalidConfiguration;
   CUtensorMap kv_map;
   if (!make_map_2d_bf16(&kv_map, cache, n_pages * 2 * Hkv * page_size, HD, page_size, 64)) return (int)cudaErrorInvalidValue;
-  static bool attr_set = false;
+  static bool attr_set_dev[bspec::kMaxDevices] = {};            // per device
+  bool& attr_set = attr_set_dev[bspec::current_device()];
   if (!attr_set) {
     const cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                (int)smem_bytes());

@@ -96,6 +96,25 @@ __device__ __forceinline__ void pdl_prologue(int kid = 0) {
   trace_record(kid, t0);
 }
 
+// Facts about a device are kept per device: a process may use several.
+constexpr int kMaxDevices = 64;
+inline int current_device() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return dev < 0 || dev >= kMaxDevices ? 0 : dev;
+}
+// Number of SMs of the current device (asked once per device).
+inline int sm_count() {
+  static int count[kMaxDevices] = {};
+  const int dev = current_device();
+  if (count[dev] == 0) {
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    count[dev] = n > 0 ? n : 1;
+  }
+  return count[dev];
+}
+
 inline bool& pdl_enabled() {
   static bool on = true;
   return on;

@@ -250,7 +250,8 @@ BSPEC_API int bspec_silu_mul(const void* u, void* m, int dtype, int n, int inter
     return BSPEC_LAUNCH_CHECK();
   }
   size_t want = (total + threads - 1) / threads;
-  const int blocks = (int)(want > 148 * 32 ? 148 * 32 : want);
+  const size_t cap = (size_t)bspec::sm_count() * 32;
+  const int blocks = (int)(want > cap ? cap : want);
   if (dtype == BSPEC_F32)
     BSPEC_LAUNCH((silu_mul_kernel<float>), blocks, threads, 0, stream, (const float*)u, (float*)m, inter, total, group);
   else
@@ -264,8 +265,20 @@ BSPEC_API int bspec_silu_mul(const void* u, void* m, int dtype, int n, int inter
 // write them, with the v heads, into the cache page of each token's position.
 // Cache layer layout: [pages][2 (k, v)][Hkv][page_size][hd].
 // Pairing: half-split (j, j + rot/2) or interleaved (2j, 2j+1); dims >= rot pass through.
-// angle = float(position) * inv_freq[j], all float32.
 constexpr int ROPE_HEADS_PER_BLOCK = 4;
+
+// Sine and cosine of position * frequency j.  The table holds every frequency as two floats, [rot/2] leading
+// parts then [rot/2] remainders, whose sum is the float64 frequency to 2^-48: the product and its reduction to
+// [-pi, pi] are float64, so the angle is right to ~2e-7 rad (the rounding of the reduced angle to float32) at
+// any position, where a float32 product would be off by position * 6e-8 rad (8e-3 rad at position 131,071).
+// Sine, cosine and the rotation are float32.  A block computes rot/2 of these per token, so the cost is nil.
+__device__ __forceinline__ void rope_sincos(int pos, const float* __restrict__ inv_freq, int half, int j, float* s,
+                                            float* c) {
+  const double f = (double)inv_freq[j] + (double)inv_freq[half + j];
+  double a = (double)pos * f;
+  a -= 6.283185307179586476925286766559 * rint(a * 0.15915494309189533576888376337251);
+  sincosf((float)a, s, c);
+}
 
 template <typename T>
 __global__ void rope_kv_append_kernel(T* __restrict__ qkv, int Hq, int Hkv, int hd, const float* __restrict__ inv_freq,
@@ -284,7 +297,7 @@ __global__ void rope_kv_append_kernel(T* __restrict__ qkv, int Hq, int Hkv, int 
   if (slot0 < Hq + Hkv) {
     for (int j = threadIdx.x; j < half; j += blockDim.x) {
       float s, c;
-      sincosf((float)pos * inv_freq[j], &s, &c);
+      rope_sincos(pos, inv_freq, half, j, &s, &c);
       cs[j] = c;
       cs[half + j] = s;
     }
@@ -356,7 +369,7 @@ rope_kv_append_vec_kernel(__nv_bfloat16* __restrict__ qkv, int Hq, int Hkv, int 
   const int pos = positions[t];
   for (int j = threadIdx.x; j < half; j += blockDim.x) {
     float s, c;
-    sincosf((float)pos * inv_freq[j], &s, &c);
+    rope_sincos(pos, inv_freq, half, j, &s, &c);
     cs[j] = c;
     cs[half + j] = s;
   }
@@ -447,7 +460,7 @@ __global__ void rope_inplace_kernel(T* __restrict__ x, long long row_stride, int
   const int pos = positions[t];
   for (int j = threadIdx.x; j < half; j += blockDim.x) {
     float s, c;
-    sincosf((float)pos * inv_freq[j], &s, &c);
+    rope_sincos(pos, inv_freq, half, j, &s, &c);
     cs[j] = c;
     cs[half + j] = s;
   }

@@ -434,7 +434,8 @@ BSPEC_API int bspec_gemm_stream(const void* X, const void* W, void* C, int M, in
   if (!make_map_2d_bf16(&map_w, W, N, K, TM, BK) || !make_map_2d_bf16(&map_x, X, M, K, p.bn, BK))
     return (int)cudaErrorInvalidValue;
   const size_t smem = stream_smem_bytes(p.bn, p.stages);
-  static size_t smem_set = 0;
+  static size_t smem_set_dev[bspec::kMaxDevices] = {};          // per device
+  size_t& smem_set = smem_set_dev[bspec::current_device()];
   if (smem > smem_set) {
     cudaError_t e = cudaFuncSetAttribute(gemm_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;

@@ -378,7 +378,8 @@ BSPEC_API int bspec_gemm_tc(const void* X, const void* W, void* C, int M, int N,
   if (!make_map_2d_bf16(&map_a, a_ptr, a_rows, K, TM, BK) || !make_map_2d_bf16(&map_b, b_ptr, b_rows, K, p.bn, BK))
     return (int)cudaErrorInvalidValue;
   const size_t smem = smem_bytes(p.bn, p.stages);
-  static size_t smem_set = 0;
+  static size_t smem_set_dev[bspec::kMaxDevices] = {};          // per device
+  size_t& smem_set = smem_set_dev[bspec::current_device()];
   if (smem > smem_set) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;

@@ -9,13 +9,16 @@ with a fresh upload per step.  The kernels read everything that changes from the
 buffer, never from launch arguments.  This replaces the reference's
 ``torch.compile`` of the step (batchspec/backends/standard_engine.py:103-106).
 
-Layout of the int32 metadata buffer for B entries and at most P pages per request
-(``dyn`` is uploaded every step, the tables only when a page was added):
+Layout of the int32 metadata buffer for B entries and at most P_g pages per request in
+cache group g (``dyn`` is uploaded every step, the tables only when a page was added):
 
-    dyn:    token_ids[B] positions[B] kv_len[B] state_slots[B] top_k[B]
-            temperature[B] (f32) top_p[B] (f32) stream_id[B] (i64) counter[B] (i64)
-    const:  tok_entry[B] qo_indptr[B+1] logit_rows[B] kv_indptr[B+1] (per group)
-    tables: kv_indices[B * P] per group
+    dyn:    the fields of ``step.CONTEXT_FIELDS`` for B entries of one token each, then
+            top_k[B] temperature[B] (f32) top_p[B] (f32) stream_id[B] (i64) counter[B] (i64)
+    const:  kv_indptr[B+1] per group
+    tables: kv_indices[B * P_g] per group
+
+The values of the context fields come from ``step.step_fields``, the same function that packs
+an ordinary step; rows beyond the live requests are its padding entries.
 """
 from __future__ import annotations
 
@@ -27,7 +30,7 @@ import numpy as np
 import torch
 
 from ..kernels import ops
-from .step import GroupTables, StepContext
+from .step import CONTEXT_FIELDS, GroupTables, StepContext, field_length, step_fields
 
 
 def _align(n: int, a: int = 4) -> int:
@@ -35,13 +38,18 @@ def _align(n: int, a: int = 4) -> int:
 
 
 class DecodeGraph:
-    def __init__(self, engine, batch: int, max_pages: int, max_kv_len: int):
-        self.engine, self.B, self.P = engine, int(batch), int(max_pages)
+    def __init__(self, engine, batch: int, max_kv_len: int):
+        self.engine, self.B = engine, int(batch)
         self.max_kv_len = int(max_kv_len)
         cache = engine.cache
-        B, P, ng = self.B, self.P, len(cache.groups)
+        B, ng = self.B, len(cache.groups)
+        self.P = [-(-self.max_kv_len // g.page_size) for g in cache.groups]      # table entries per row, per group
         off, o = {}, 0
-        for name in ("token_ids", "positions", "kv_len", "state_slots", "top_k", "temperature", "top_p"):
+        for name, kind in CONTEXT_FIELDS:
+            off[name] = o
+            o += _align(field_length(kind, B, B, B))
+        assert off["token_ids"] == 0                  # a step whose ids are on the device uploads from the next field on
+        for name in ("top_k", "temperature", "top_p"):
             off[name] = o
             o += _align(B)
         o = _align(o, 2)
@@ -49,26 +57,18 @@ class DecodeGraph:
             off[name] = o
             o += _align(2 * B)
         self.dyn_len = o
-        for name in ("tok_entry", "logit_rows"):
-            off[name] = o
-            o += _align(B)
-        off["qo_indptr"] = o
-        o += _align(B + 1)
         for g in range(ng):
             off[f"kv_indptr{g}"] = o
             o += _align(B + 1)
         self.table_begin = o
         for g in range(ng):
             off[f"kv_indices{g}"] = o
-            o += _align(B * P)
+            o += _align(B * self.P[g])
         self.total = o
         self.off = off
         self.meta = np.zeros(self.total, dtype=np.int32)                 # the authoritative host copy
-        self.meta[off["tok_entry"]:off["tok_entry"] + B] = np.arange(B)
-        self.meta[off["logit_rows"]:off["logit_rows"] + B] = np.arange(B)
-        self.meta[off["qo_indptr"]:off["qo_indptr"] + B + 1] = np.arange(B + 1)
         for g in range(ng):
-            self.meta[off[f"kv_indptr{g}"]:off[f"kv_indptr{g}"] + B + 1] = np.arange(B + 1) * P
+            self.meta[off[f"kv_indptr{g}"]:off[f"kv_indptr{g}"] + B + 1] = np.arange(B + 1) * self.P[g]
         self.ring = [torch.empty(self.total, dtype=torch.int32, pin_memory=True) for _ in range(4)]
         self.ring_events: List[Optional[torch.cuda.Event]] = [None] * 4
         self.turn = 0
@@ -87,30 +87,33 @@ class DecodeGraph:
         view = lambda name, n: d[off[name]:off[name] + n]
         f32 = lambda name: d[off[name]:off[name] + B].view(torch.float32)
         i64 = lambda name: d[off[name]:off[name] + 2 * B].view(torch.int64)
-        self.v_tokens = view("token_ids", B)
         self.v_temperature, self.v_top_p = f32("temperature"), f32("top_p")
         self.v_top_k = view("top_k", B)
         self.v_stream, self.v_counter = i64("stream_id"), i64("counter")
-        tables = [GroupTables(cache.page_size, view(f"kv_indptr{g}", B + 1), view(f"kv_indices{g}", B * P), None, None)
-                  for g in range(ng)]
-        self.ctx = StepContext(
-            n_tokens=B, n_entries=B, token_ids=self.v_tokens, positions=view("positions", B),
-            tok_entry=view("tok_entry", B), qo_indptr=view("qo_indptr", B + 1), kv_len=view("kv_len", B),
-            state_slots=view("state_slots", B), logit_rows=view("logit_rows", B), n_logit_rows=B, tables=tables,
-            max_q_len=1, max_kv_len=self.max_kv_len, h_qo_indptr=None, h_kv_len=None, h_state_slots=None,
-            h_positions=None, extras={"min_q_len": 1, "captured": True})
+        tables = [GroupTables(grp.page_size, view(f"kv_indptr{g}", B + 1), view(f"kv_indices{g}", B * self.P[g]), None, None)
+                  for g, grp in enumerate(cache.groups)]
+        views = {name: view(name, field_length(kind, B, B, B)) for name, kind in CONTEXT_FIELDS}
+        self.v_tokens = views["token_ids"]
+        self.ctx = StepContext(n_tokens=B, n_entries=B, n_logit_rows=B, tables=tables, max_q_len=1,
+                               max_kv_len=self.max_kv_len, host=None, extras={"min_q_len": 1, "captured": True}, **views)
 
     # -- host side -------------------------------------------------------------------
     _PAD = object()        # marks a table row that currently points at the scratch page
 
     def _fill(self, req_ids: Sequence, tokens: Optional[Sequence[int]], temperature, top_k, top_p, stream_ids,
               counters) -> None:
-        cache, off, B, P, m = self.engine.cache, self.off, self.B, self.P, self.meta
+        cache, off, B, m = self.engine.cache, self.off, self.B, self.meta
         n = len(req_ids)
         reqs = [cache.requests[r] for r in req_ids]
-        # rows n .. B-1 are padding: one token at position 0 of the scratch page, greedy, result ignored
-        lengths = np.zeros(B, dtype=np.int32)
-        lengths[:n] = [rc.length for rc in reqs]
+        # rows n .. B-1 are padding: one token at position 0 of the scratch page and the scratch state slot,
+        # greedy, result ignored
+        fields, _ = step_fields(cache, list(req_ids) + [None] * (B - n), [1] * B, [(0,)] * B,
+                                None if tokens is None else [[t] for t in tokens] + [[0]] * (B - n), with_tables=False)
+        for name, _kind in CONTEXT_FIELDS:
+            if name == "token_ids" and tokens is None:
+                continue
+            v = fields[name]
+            m[off[name]:off[name] + v.shape[0]] = v
 
         def put(name, values, view=None, width=1):
             dst = m[off[name]:off[name] + width * B]
@@ -119,11 +122,6 @@ class DecodeGraph:
             dst[:n] = values
             dst[n:] = 0
 
-        if tokens is not None:
-            put("token_ids", tokens)
-        m[off["positions"]:off["positions"] + B] = lengths
-        m[off["kv_len"]:off["kv_len"] + B] = lengths + 1
-        put("state_slots", [rc.slot for rc in reqs])
         put("top_k", top_k)
         put("temperature", temperature, np.float32)
         put("top_p", top_p, np.float32)
@@ -134,7 +132,7 @@ class DecodeGraph:
             for i in range(n, B):
                 if self.row_req[i] is not self._PAD:
                     for g, page in enumerate(scratch):
-                        m[off[f"kv_indices{g}"] + i * P] = page
+                        m[off[f"kv_indices{g}"] + i * self.P[g]] = page
                         self.row_pages[i][g] = 0
                     self.row_req[i] = self._PAD
                     self.tables_dirty = True
@@ -144,6 +142,7 @@ class DecodeGraph:
             fresh = self.row_req[i] != (rid, rc.serial)
             for g, table in enumerate(rc.tables):
                 have = 0 if fresh else self.row_pages[i][g]
+                P = self.P[g]
                 if len(table) > P:
                     raise RuntimeError(f"request {rid!r} holds {len(table)} pages, the captured step allows {P}")
                 if fresh or len(table) != have:
@@ -153,7 +152,7 @@ class DecodeGraph:
                     self.row_pages[i][g] = len(table)
                     self.tables_dirty = True
                 elif cache.groups[g].spec.policy == "window":
-                    base = off[f"kv_indices{g}"] + i * P        # released pages turn into -1 in place
+                    base = off[f"kv_indices{g}"] + i * P         # released pages turn into -1 in place
                     m[base:base + len(table)] = table
                     self.tables_dirty = True
             self.row_req[i] = (rid, rc.serial)
@@ -165,7 +164,7 @@ class DecodeGraph:
             self.ring_events[i].synchronize()
         host = self.ring[i]
         B = self.B
-        lo = 0 if with_tokens else _align(B)
+        lo = 0 if with_tokens else self.off["positions"]
         hi = self.total if (self.tables_dirty or not self.const_uploaded) else self.dyn_len
         host.numpy()[lo:hi] = self.meta[lo:hi]
         self.dev[lo:hi].copy_(host[lo:hi], non_blocking=True)

@@ -59,6 +59,7 @@ class Engine:
         self.max_seq_length = None
         self.decode_lookahead = True        # launch the next captured decode step before reading this one's tokens
         self._ahead = None
+        self._stateful = False
         self._tok_host = None               # two pinned buffers that captured steps' tokens are copied into in turn
         self._tok_turn = 0
         self.prefill_chunk_size = 128
@@ -84,10 +85,15 @@ class Engine:
         runtime = Runtime(self.dtype, self.device)
         if model_dir is not None:
             self.config = load_config(model_dir)
+            unread = getattr(self.config, "unread_keys", ())
+            if unread:
+                import warnings
+                warnings.warn(f"config.json of {model_dir} has keys this engine does not read: {', '.join(unread)}")
             self.model = get_model(self.config, runtime)
             s = self.model.spec
             tensors = load_weights(model_dir, self.model.param_specs(), self.dtype, self.device,
-                                   ignore_suffixes=s.ignore_suffixes, ignore_names=s.ignore_names)
+                                   ignore_suffixes=s.ignore_suffixes, ignore_names=s.ignore_names,
+                                   must_equal=s.must_equal)
         else:
             if config is None:
                 if config_name is None:
@@ -128,6 +134,9 @@ class Engine:
         self.cache = self.runner = None
         self.model.attach_caches([None] * len(self.model.spec.order))
         needs = self.model.cache_needs()
+        # A step launched ahead may be dropped and run again; that repeats cache writes harmlessly but would
+        # advance a mixer's per-request state twice, so models with state never launch ahead.
+        self._stateful = any(need.state is not None for need in needs)
         if torch.device(self.device).type == "cuda":
             torch.cuda.empty_cache()
             want = CacheManager(needs, page_size, num_pages, max_batch_size, self.dtype, self.device,
@@ -170,8 +179,7 @@ class Engine:
             bucket = max(batch, min(bucket, self.max_batch_size))
         if bucket not in self._graphs:
             from .decode_graph import DecodeGraph
-            max_pages = -(-self.max_seq_length // self.page_size)
-            self._graphs[bucket] = DecodeGraph(self, bucket, max_pages, self.max_seq_length)
+            self._graphs[bucket] = DecodeGraph(self, bucket, self.max_seq_length)
         return self._graphs[bucket]
 
     def decode_session(self, req_ids, first_tokens):
@@ -266,14 +274,15 @@ class Engine:
         # prompt, held up for pages that an ending request would free), nobody waits for admission (or no slot can
         # come free: all are taken and no request stops at an end-of-sequence token), nobody reaches a length limit
         # with this step's token, and the pages the next step needs are free.
-        if (sched is not None and self.decode_lookahead and cur["ids"] == ids and cur["graph"] is graph
+        if (sched is not None and self.decode_lookahead and not self._stateful and cur["ids"] == ids
+                and cur["graph"] is graph
                 and len(sched.running) == len(ids)
                 and (not sched.waiting_queue or (sched.ignore_eos and len(sched.running) >= sched.max_concurrency))
                 and self.tracer is None and not get_active_profiler().active
                 and all(len(s.output_ids) + 1 < s.max_new_tokens and s.total_len + 1 < sched.max_model_len
                         for s in seqs)):
-            need = sum(self.cache.pages_missing(rid, 1) for rid in ids)
-            if all(need <= g.pool.num_free for g in self.cache.groups):
+            need = [sum(col) for col in zip(*(self.cache.pages_missing(rid, 1) for rid in ids))]
+            if all(n <= g.pool.num_free for n, g in zip(need, self.cache.groups)):
                 self._ahead = self._launch_decode(graph, seqs, None, 1)
         cur["event"].synchronize()
         ops.raise_if_gave_up()
@@ -298,7 +307,7 @@ class Engine:
         steps = tokens_in = 0
         dec_steps = dec_tokens = dec_h2d = dec_d2h = 0
         dec_seconds = 0.0
-        step_ms = []
+        step_ms, dec_step_ms = [], []
         prof = get_active_profiler()
         while not sched.is_done():
             t_step = time.perf_counter()
@@ -339,11 +348,13 @@ class Engine:
                 dec_steps += 1
                 dec_tokens += len(work)
                 dec_seconds += time.perf_counter() - t_step
+                dec_step_ms.append(step_ms[-1])
                 dec_h2d += h2d
                 dec_d2h += 4 * len(work)
         self.last_stats = dict(steps=steps, tokens_fed=tokens_in, preemptions=sched.num_preemptions,
                                generated=sum(len(s.output_ids) for s in sched.completed),
-                               step_ms=step_ms, decode_steps=dec_steps, decode_tokens=dec_tokens, decode_seconds=dec_seconds,
+                               step_ms=step_ms, decode_step_ms=dec_step_ms, decode_steps=dec_steps,
+                               pages_high_water=[g.pool.high_water for g in self.cache.groups], decode_tokens=dec_tokens, decode_seconds=dec_seconds,
                                decode_h2d_bytes_per_step=dec_h2d // max(dec_steps, 1),
                                decode_d2h_bytes_per_step=dec_d2h // max(dec_steps, 1))
         return sched.completed

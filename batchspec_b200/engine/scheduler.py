@@ -77,11 +77,13 @@ class Scheduler:
     def is_done(self) -> bool:
         return len(self.completed) == self.total
 
-    def _pool_pages(self) -> int:
-        return min((g.pool.num_pages for g in self.cache.groups), default=1 << 60)
+    @staticmethod
+    def _fits(need: List[int], free: List[int]) -> bool:
+        return all(n <= f for n, f in zip(need, free))
 
-    def _free_pages(self) -> int:
-        return min((g.pool.num_free for g in self.cache.groups), default=1 << 60)
+    @staticmethod
+    def _take(need: List[int], free: List[int]) -> List[int]:
+        return [f - n for n, f in zip(need, free)]
 
     def _never_fits(self, s: Sequence) -> Optional[str]:
         if s.prompt_len < 1:
@@ -91,7 +93,8 @@ class Scheduler:
         if s.prompt_len + 1 > self.max_model_len:
             return f"prompt of {s.prompt_len} tokens does not fit the context of {self.max_model_len}"
         first = min(self.prefill_chunk_len, self.max_tokens_per_step, s.prompt_len)
-        if self._outgrows_a_pool(s.prompt_len + 1) or self.cache.pages_needed(0, first) > self._pool_pages():
+        if self._outgrows_a_pool(s.prompt_len + 1) or not self._fits(
+                self.cache.pages_needed(0, first), [g.pool.num_pages for g in self.cache.groups]):
             return f"prompt of {s.prompt_len} tokens needs more pages than the whole pool has"
         return None
 
@@ -123,7 +126,7 @@ class Scheduler:
             for s in [s for s in self.running if self._outgrows_a_pool(s.total_len)]:
                 self._retire(s, "cache")
             budget = self.max_tokens_per_step
-            free = self._free_pages()
+            free = cache.free_pages()
             work: List[Workload] = []
             starved = False
             # 1. decode entries first, in admission order
@@ -133,10 +136,10 @@ class Scheduler:
                 need = cache.pages_missing(s.seq_id, 1)
                 if budget < 1:
                     break
-                if need > free:
+                if not self._fits(need, free):
                     starved = True
                     break
-                free -= need
+                free = self._take(need, free)
                 budget -= 1
                 work.append(Workload(s, s.num_computed, 1, True))
             # 2. portions of requests that are already prefilling
@@ -147,7 +150,7 @@ class Scheduler:
                     n = self._portion(s, budget, free)
                     if n == 0:
                         continue
-                    free -= cache.pages_missing(s.seq_id, n)
+                    free = self._take(cache.pages_missing(s.seq_id, n), free)
                     budget -= n
                     work.append(Workload(s, s.num_computed, n, s.num_computed + n == s.total_len))
             # 3. admit waiting requests while slots, budget and pages allow
@@ -156,7 +159,7 @@ class Scheduler:
                        and cache.slots.num_free > 0 and budget >= 1):
                     s = self.waiting_queue[0]
                     n = min(self.prefill_chunk_len, s.total_len, budget)
-                    if cache.pages_needed(0, n) > free:      # the whole first portion must fit
+                    if not self._fits(cache.pages_needed(0, n), free):      # the whole first portion must fit
                         break
                     self.waiting_queue.popleft()
                     cache.admit(s.seq_id)
@@ -164,7 +167,7 @@ class Scheduler:
                     s.admitted_at = self._admissions
                     self._admissions += 1
                     self.running.append(s)
-                    free -= cache.pages_needed(0, n)
+                    free = self._take(cache.pages_needed(0, n), free)
                     budget -= n
                     work.append(Workload(s, 0, n, n == s.total_len))
             if work and not starved:
@@ -179,16 +182,14 @@ class Scheduler:
             # live requests cannot move: give the latest one's pages to the others
             self._preempt_latest()
 
-    def _portion(self, s: Sequence, budget: int, free_pages: int) -> int:
+    def _portion(self, s: Sequence, budget: int, free_pages: List[int]) -> int:
         """Largest portion of s's remaining known tokens within the chunk length,
-        the step's budget and the free pages."""
+        the step's budget and the free pages of every group."""
         remaining = s.total_len - s.num_computed
         n = min(self.prefill_chunk_len, remaining, budget)
         if n <= 0:
             return 0
-        ps = self.cache.page_size
-        room = free_pages * ps + (-s.num_computed) % ps      # tokens that fit without more pages than free
-        return max(0, min(n, room))
+        return max(0, min(n, self.cache.room_for(s.num_computed, free_pages)))
 
     # -- results -------------------------------------------------------------------
     def process_results(self, workloads: Seq[Workload], next_tokens: Dict[int, int]) -> None:

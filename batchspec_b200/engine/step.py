@@ -42,10 +42,67 @@ class GroupTables:
     h_kv_indices: np.ndarray
 
 
+# The int32 fields of a step's metadata, in packing order, each with the count that gives its length.  Both
+# ways of running a step (the packed buffer below, the fixed layout of a captured decode step) take this list
+# and ``step_fields``: a new field is added here, there and to ``StepContext``, nowhere else.
+CONTEXT_FIELDS = (("token_ids", "tokens"), ("positions", "tokens"), ("tok_entry", "tokens"), ("qo_indptr", "entries+1"),
+                  ("kv_len", "entries"), ("state_slots", "entries"), ("logit_rows", "rows"))
+
+
+def field_length(kind: str, n_tokens: int, n_entries: int, n_rows: int) -> int:
+    return {"tokens": n_tokens, "entries": n_entries, "entries+1": n_entries + 1, "rows": n_rows}[kind]
+
+
+def step_fields(cache: CacheManager, req_ids: Sequence, lens: Sequence[int], wants: Sequence[Sequence[int]],
+                tokens: Optional[Sequence[Sequence[int]]] = None, with_tables: bool = True):
+    """The values of ``CONTEXT_FIELDS`` for a step of these entries, and per cache group the entries' block
+    tables as CSR (indptr, indices).  ``req_ids[i]`` None is a padding entry: a request of length 0 in the
+    cache's scratch state slot whose table is the scratch page.  ``tokens`` None: the ids are already on the
+    device and ``token_ids`` comes back empty.  ``with_tables`` False: no tables (the caller keeps its own copy
+    of them up to date)."""
+    n = len(req_ids)
+    reqs = [cache.requests[r] if r is not None else None for r in req_ids]
+    lens = np.asarray(lens, dtype=np.int64).reshape(n)
+    before = np.fromiter((rc.length if rc is not None else 0 for rc in reqs), dtype=np.int64, count=n)
+    qo = np.zeros(n + 1, dtype=np.int32)
+    np.cumsum(lens, out=qo[1:])
+    nnz = int(qo[-1])
+    if tokens is not None:
+        ids = np.concatenate([np.asarray(t, dtype=np.int64).reshape(-1) for t in tokens]) if n else np.zeros(0, np.int64)
+    else:
+        ids = np.zeros(0, dtype=np.int64)
+    pad_slot = cache.scratch_slot()
+    rows: List[int] = []
+    for i, want in enumerate(wants):
+        for w in want:
+            if not 0 <= w < lens[i]:
+                raise ValueError(f"request {req_ids[i]!r}: wanted place {w} is outside its {lens[i]} tokens")
+            rows.append(int(qo[i]) + int(w))
+    fields = {
+        "token_ids": ids.astype(np.int32),
+        "positions": (np.arange(nnz, dtype=np.int64) - np.repeat(qo[:-1].astype(np.int64), lens)
+                      + np.repeat(before, lens)).astype(np.int32),
+        "tok_entry": np.repeat(np.arange(n, dtype=np.int32), lens),
+        "qo_indptr": qo,
+        "kv_len": (before + lens).astype(np.int32),
+        "state_slots": np.fromiter((rc.slot if rc is not None else (pad_slot or 0) for rc in reqs), dtype=np.int32, count=n),
+        "logit_rows": np.asarray(rows, dtype=np.int32),
+    }
+    scratch = cache.scratch_pages()
+    tables = []
+    for gi in range(len(cache.groups) if with_tables else 0):
+        tabs = [rc.tables[gi] if rc is not None else [scratch[gi]] for rc in reqs]
+        indptr = np.zeros(n + 1, dtype=np.int32)
+        np.cumsum([len(t) for t in tabs], out=indptr[1:])
+        tables.append((indptr, np.fromiter((p for t in tabs for p in t), dtype=np.int32, count=int(indptr[-1]))))
+    return fields, tables
+
+
 @dataclass
 class StepContext:
     """Everything the parts may read about the step.  Device tensors are int32
-    views into one buffer; ``h_*`` are the same values on the host."""
+    views into one buffer; ``host`` holds the same values on the host under the same names (None for a captured
+    step, whose values change from replay to replay), also readable as ``h_<name>``."""
     n_tokens: int
     n_entries: int
     token_ids: torch.Tensor            # [n_tokens]
@@ -59,11 +116,14 @@ class StepContext:
     tables: List[GroupTables]
     max_q_len: int
     max_kv_len: int
-    h_qo_indptr: np.ndarray
-    h_kv_len: np.ndarray
-    h_state_slots: np.ndarray
-    h_positions: np.ndarray
+    host: Optional[dict] = None
     extras: dict = field(default_factory=dict)
+
+    def __getattr__(self, name):
+        if name.startswith("h_"):
+            host = self.__dict__.get("host")
+            return None if host is None else host[name[2:]]
+        raise AttributeError(name)
 
 
 class _Staging:
@@ -121,37 +181,15 @@ class StepRunner:
         token values are not looked at, only their counts."""
         cache = self.cache
         n = len(entries)
-        lens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=n)
-        before = np.fromiter((cache.requests[e.req_id].length for e in entries), dtype=np.int64, count=n)
-        qo = np.zeros(n + 1, dtype=np.int32)
-        np.cumsum(lens, out=qo[1:])
-        nnz = int(qo[-1])
-        if device_tokens is None:
-            tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64).reshape(-1) for e in entries])
-            if tokens.size and (tokens.min() < 0 or tokens.max() >= self.vocab_size):
-                raise ValueError(f"token id outside [0, {self.vocab_size}) in the step")
-        else:
-            tokens = np.zeros(0, dtype=np.int64)
-        tok_entry = np.repeat(np.arange(n, dtype=np.int32), lens)
-        positions = (np.arange(nnz, dtype=np.int64) - np.repeat(qo[:-1].astype(np.int64), lens)
-                     + np.repeat(before, lens)).astype(np.int32)
-        kv_len = (before + lens).astype(np.int32)
-        slots = np.fromiter((cache.requests[e.req_id].slot for e in entries), dtype=np.int32, count=n)
-        rows: List[int] = []
-        for i, e in enumerate(entries):
-            for w in e.want:
-                if not 0 <= w < lens[i]:
-                    raise ValueError(f"request {e.req_id!r}: wanted place {w} is outside its {lens[i]} tokens")
-                rows.append(int(qo[i]) + int(w))
-        rows_np = np.asarray(rows, dtype=np.int32)
-        parts = [tokens.astype(np.int32), positions, tok_entry, qo, kv_len, slots, rows_np]
-        group_parts = []
-        for gi, g in enumerate(cache.groups):
-            tabs = [cache.requests[e.req_id].tables[gi] for e in entries]
-            indptr = np.zeros(n + 1, dtype=np.int32)
-            np.cumsum([len(t) for t in tabs], out=indptr[1:])
-            indices = np.fromiter((p for t in tabs for p in t), dtype=np.int32, count=int(indptr[-1]))
-            group_parts.append((indptr, indices))
+        lens = [len(e.tokens) for e in entries]
+        fields, group_tables = step_fields(cache, [e.req_id for e in entries], lens, [e.want for e in entries],
+                                           None if device_tokens is not None else [e.tokens for e in entries])
+        ids = fields["token_ids"]
+        if ids.size and (ids.min() < 0 or ids.max() >= self.vocab_size):
+            raise ValueError(f"token id outside [0, {self.vocab_size}) in the step")
+        names = [name for name, _ in CONTEXT_FIELDS]
+        parts = [fields[name] for name in names]
+        for indptr, indices in group_tables:
             parts += [indptr, indices]
         offsets, total = [], 0
         for p in parts:
@@ -163,16 +201,17 @@ class StepRunner:
         dev = self.staging.upload(packed)
         self.last_h2d_bytes = total * 4
         view = lambda k: dev[offsets[k]:offsets[k] + parts[k].shape[0]]
+        views = {name: view(k) for k, name in enumerate(names)}
+        if device_tokens is not None:
+            views["token_ids"] = device_tokens
         tables = []
         for gi, g in enumerate(cache.groups):
-            k = 7 + 2 * gi
-            tables.append(GroupTables(g.page_size, view(k), view(k + 1), group_parts[gi][0], group_parts[gi][1]))
+            k = len(names) + 2 * gi
+            tables.append(GroupTables(g.page_size, view(k), view(k + 1), group_tables[gi][0], group_tables[gi][1]))
         return StepContext(
-            n_tokens=nnz, n_entries=n, token_ids=view(0) if device_tokens is None else device_tokens,
-            positions=view(1), tok_entry=view(2), qo_indptr=view(3),
-            kv_len=view(4), state_slots=view(5), logit_rows=view(6), n_logit_rows=len(rows), tables=tables,
-            max_q_len=int(lens.max()), max_kv_len=int(kv_len.max()), h_qo_indptr=qo, h_kv_len=kv_len,
-            h_state_slots=slots, h_positions=positions, extras={"min_q_len": int(lens.min())})
+            n_tokens=int(fields["qo_indptr"][-1]), n_entries=n, n_logit_rows=int(fields["logit_rows"].shape[0]),
+            tables=tables, max_q_len=max(lens), max_kv_len=int(fields["kv_len"].max()), host=fields,
+            extras={"min_q_len": min(lens)}, **views)
 
     def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run the entries as one batch; float32 logits [sum of len(want), vocab] in
@@ -189,8 +228,10 @@ class StepRunner:
             seen.add(e.req_id)
             if not cache.is_live(e.req_id):
                 raise KeyError(f"request {e.req_id!r} is not live (admit it first)")
-        need = sum(cache.pages_missing(e.req_id, len(e.tokens)) for e in entries)   # pages held ahead count as held
-        if any(need > g.pool.num_free for g in cache.groups):
+        need = [0] * len(cache.groups)                    # per group; pages held ahead count as held
+        for e in entries:
+            need = [a + b for a, b in zip(need, cache.pages_missing(e.req_id, len(e.tokens)))]
+        if any(n > g.pool.num_free for n, g in zip(need, cache.groups)):
             from ..cache.manager import OutOfPages
             raise OutOfPages("the step needs more pages than are free; nothing was run")
         for e in entries:

@@ -237,7 +237,7 @@ def linear_glu(x: torch.Tensor, w13: torch.Tensor, group: int = GLU_GROUP) -> to
             return gemm_stream(x, w13, x.dtype, glu=True)
         out = torch.empty((M, inter), dtype=x.dtype, device=x.device)
         _check(load_library().bspec_gemm_tc(x.data_ptr(), w13.data_ptr(), out.data_ptr(), M, N, K, 0, 1,
-                                            _status_word(x.device).data_ptr(), _SM_COUNT, _stream()), "gemm_tc_glu")
+                                            _status_word(x.device).data_ptr(), sm_count(x.device), _stream()), "gemm_tc_glu")
         return out
     u = linear(x, w13)
     out = torch.empty((M, inter), dtype=x.dtype, device=x.device)
@@ -245,12 +245,23 @@ def linear_glu(x: torch.Tensor, w13: torch.Tensor, group: int = GLU_GROUP) -> to
     return out
 
 
+def rope_frequency_table(freqs: torch.Tensor, device) -> torch.Tensor:
+    """The form in which the rotary kernels take their frequencies: float32 [2, n], the leading parts of the
+    float64 values in row 0 and the remainders in row 1 (their sum is the float64 value to 2^-48).  The kernels
+    form the angle position * frequency in float64 from it."""
+    f = freqs.detach().to("cpu", torch.float64).reshape(-1)
+    hi = f.to(torch.float32)
+    lo = (f - hi.to(torch.float64)).to(torch.float32)
+    return torch.stack([hi, lo]).contiguous().to(device)
+
+
 def rope_kv_append(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                    inv_freq: Optional[torch.Tensor], rotary_dim: int, interleaved: bool, positions: torch.Tensor,
                    tok_entry: torch.Tensor, kv_indptr: torch.Tensor, kv_indices: torch.Tensor, cache: torch.Tensor,
                    page_size: int, write_kv: bool = True) -> None:
     """Rotate q (in place) and k, and write k and v of every token into the cache
-    page of its position.  ``cache``: one layer's pages, any shape with
+    page of its position.  ``inv_freq``: a ``rope_frequency_table`` of rotary_dim / 2 frequencies.
+    ``cache``: one layer's pages, any shape with
     2 * n_kv_heads * page_size * head_dim elements per page, laid out
     [page][k|v][kv head][row][dim]."""
     _require_cuda(qkv, positions, cache)
@@ -259,7 +270,7 @@ def rope_kv_append(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: i
     assert cache.dtype == qkv.dtype and cache.is_contiguous()
     assert positions.dtype == torch.int32 and tok_entry.dtype == torch.int32
     if rotary_dim:
-        assert inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2
+        assert inv_freq.dtype == torch.float32 and inv_freq.shape == (2, rotary_dim // 2) and inv_freq.is_contiguous()
     _check(load_library().bspec_rope_kv_append(
         qkv.data_ptr(), _dtype_code(qkv.dtype), n, n_heads, n_kv_heads, head_dim, _ptr(inv_freq), int(rotary_dim),
         int(bool(interleaved)), positions.data_ptr(), tok_entry.data_ptr(), kv_indptr.data_ptr(),
@@ -268,10 +279,12 @@ def rope_kv_append(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: i
 
 def rope_inplace(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int,
                  interleaved: bool = False) -> None:
-    """x: [n, H, hd] view whose last two dims are dense; rows may be strided."""
+    """x: [n, H, hd] view whose last two dims are dense; rows may be strided.  ``inv_freq``: a
+    ``rope_frequency_table``."""
     _require_cuda(x, positions, inv_freq)
     n, H, hd = x.shape
     assert x.stride(2) == 1 and x.stride(1) == hd and positions.dtype == torch.int32
+    assert inv_freq.dtype == torch.float32 and inv_freq.shape == (2, rotary_dim // 2) and inv_freq.is_contiguous()
     _check(load_library().bspec_rope_inplace(x.data_ptr(), _dtype_code(x.dtype), n, x.stride(0), H, hd,
                                              inv_freq.data_ptr(), int(rotary_dim), int(bool(interleaved)),
                                              positions.data_ptr(), _stream()), "rope_inplace")
@@ -283,7 +296,17 @@ USE_TMA_ATTENTION = os.environ.get("BSPEC_TMA_ATTENTION", "1") != "0"
 USE_TC_ATTENTION = os.environ.get("BSPEC_TC_ATTENTION", "1") != "0"    # tcgen05 kernel for long prompt portions
 BALANCED_ATTENTION = os.environ.get("BSPEC_BALANCED_ATTENTION", "1") != "0"   # equal chunks over a fixed grid for decode
 FORCE_GENERIC_ATTENTION = False      # tests set this to compare the tensor-core kernels with the generic one
-_SM_COUNT = 148
+_sm_counts = {}
+
+
+def sm_count(device=None) -> int:
+    """Number of SMs of ``device`` (default: the current one), asked once per device."""
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index
+    if idx is None:
+        idx = torch.cuda.current_device()
+    if idx not in _sm_counts:
+        _sm_counts[idx] = int(torch.cuda.get_device_properties(idx).multi_processor_count)
+    return _sm_counts[idx]
 
 
 _tile_counters = {}               # device -> zeroed int32 buffers kept alive (graphs hold their addresses)
@@ -302,7 +325,7 @@ def attention_splits(n_entries: int, n_kv_heads: int, group: int, max_q_len: int
         return 1
     row_tiles = -(-(max_q_len * group) // 16)
     base = max(1, n_entries * n_kv_heads * row_tiles)
-    slots = _SM_COUNT * ctas_per_sm
+    slots = sm_count() * ctas_per_sm
     fine = min(64, max(1, -(-max_kv_len // 128)))
     if base * fine <= slots:
         return fine
@@ -334,7 +357,7 @@ def _attention_plan(device, ctx, tables, n_heads: int, n_kv_heads: int, head_dim
     # then only the most partial results a row tile may be left in, and the scratch is indexed by request.
     balanced = int(tma and BALANCED_ATTENTION and ctx.n_entries <= 512 and not ctx.extras.get("attn_splits"))
     if balanced:
-        n_splits = min(64, max(16, -(-4 * _SM_COUNT // (ctx.n_entries * n_kv_heads)) + 2))
+        n_splits = min(64, max(16, -(-4 * sm_count(device) // (ctx.n_entries * n_kv_heads)) + 2))
     else:
         n_splits = ctx.extras.get("attn_splits") or attention_splits(ctx.n_entries, n_kv_heads, group, ctx.max_q_len,
                                                                      ctx.max_kv_len, 2 if tma else 3)
@@ -492,14 +515,14 @@ def gemm_stream(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, glu: b
     N = w.shape[0]
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
     plan = (c_int * 4)()
-    need = lib.bspec_gemm_stream_plan(M, N, K, _SM_COUNT, plan)
+    need = lib.bspec_gemm_stream_plan(M, N, K, sm_count(x.device), plan)
     if need < 0 or (glu and N % 128 != 0):
         raise KernelError(f"gemm_stream: sizes M={M} N={N} K={K} are not supported (M <= 128, K a multiple of 8)")
     scratch, counters = _stream_buffers(x.device, need, plan[3])
     out = torch.empty((M, N // 2 if glu else N), dtype=out_dtype, device=x.device)
     _check(lib.bspec_gemm_stream(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, int(out_dtype == torch.float32),
                                  int(glu), scratch.data_ptr(), counters.data_ptr(), _status_word(x.device).data_ptr(),
-                                 _SM_COUNT, _stream()), "gemm_stream")
+                                 sm_count(x.device), _stream()), "gemm_stream")
     return out
 
 
@@ -513,7 +536,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.T
         raise KernelError(f"gemm_tc: sizes M={M} N={N} K={K} are not supported (K must be a multiple of 8)")
     out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     _check(lib.bspec_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, int(out_dtype == torch.float32), 0,
-                             _status_word(x.device).data_ptr(), _SM_COUNT, _stream()), "gemm_tc")
+                             _status_word(x.device).data_ptr(), sm_count(x.device), _stream()), "gemm_tc")
     return out
 
 

@@ -11,7 +11,7 @@ from typing import Callable, Dict
 from ..parts.base import Runtime
 from .decoder import CacheNeed, DecoderModel, LayerCache
 from .llama import build_llama
-from .spec import LayerSpec, ModelSpec, RunEntry
+from .spec import LayerSpec, ModelSpec, RunEntry, prenorm_layer
 
 MODEL_REGISTRY: Dict[str, Callable] = {}
 
@@ -30,4 +30,4 @@ def get_model(config, runtime: Runtime) -> DecoderModel:
 register_model("LlamaForCausalLM", build_llama)
 
 __all__ = ["MODEL_REGISTRY", "register_model", "get_model", "DecoderModel", "LayerCache", "CacheNeed",
-           "ModelSpec", "LayerSpec", "RunEntry", "build_llama"]
+           "ModelSpec", "LayerSpec", "RunEntry", "prenorm_layer", "build_llama"]

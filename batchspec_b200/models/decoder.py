@@ -1,5 +1,6 @@
-"""Generic executor of a ``ModelSpec``: embedding, the listed runs of layers,
-final norm, head over the wanted rows only.
+"""Generic executor of a ``ModelSpec``: embedding (then the optional input part),
+the listed runs of layers, final norm, head over the wanted rows only (then the
+optional logits part).
 
 The reference computes logits for every token of the step and then selects the
 last row of each request (batchspec/models/standard_model.py:90-102,
@@ -13,15 +14,15 @@ import torch
 
 from ..kernels import ops
 from ..profiler import bucket
-from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, CacheSpec, ParamSpec, Runtime, StateSpec,
+from ..parts.base import (BLOCKS, INPUT_PARTS, LOGITS_PARTS, NORMS, CacheSpec, ParamSpec, Runtime, StateSpec,
                           build_part)
 from .spec import ModelSpec
 
 
 @dataclass
 class LayerCache:
-    """What one run of a layer sees of the cache.  ``kv``: [pages, 2, page_size,
-    *entry_shape] of its group's pool (None if the mixer asked for no pages);
+    """What one run of a layer sees of the cache.  ``kv``: [pages, tensors per token,
+    page_size * entry elements] of its group's pool (None if the mixer asked for no pages);
     ``group``: index of the block tables in the step context; ``state``:
     [max_requests, *state_shape] or None; ``owner``: False for a run that reads
     another run's cache."""
@@ -43,13 +44,18 @@ class DecoderModel:
     def __init__(self, spec: ModelSpec, runtime: Runtime):
         self.spec, self.runtime = spec, runtime
         self.blocks = []
-        for layer in spec.layers:
+        for i, layer in enumerate(spec.layers):
             if layer.block not in BLOCKS:
                 raise KeyError(f"block kind {layer.block!r} is not registered (known: {sorted(BLOCKS)})")
-            self.blocks.append(BLOCKS[layer.block](
-                build_part(NORMS, layer.norm1, runtime), build_part(MIXERS, layer.mixer, runtime),
-                build_part(NORMS, layer.norm2, runtime), build_part(FEED_FORWARDS, layer.ffn, runtime)))
+            kind = BLOCKS[layer.block]
+            if set(layer.parts) != set(kind.SLOTS):
+                raise ValueError(f"layer {i}: block {layer.block!r} has slots {list(kind.SLOTS)}, "
+                                 f"the description gives {list(layer.parts)}")
+            self.blocks.append(kind(**{slot: build_part(registry, layer.parts[slot], runtime)
+                                       for slot, registry in kind.SLOTS.items()}))
         self.final_norm = build_part(NORMS, spec.final_norm, runtime)
+        self.input_part = build_part(INPUT_PARTS, spec.input_part, runtime) if spec.input_part else None
+        self.logits_part = build_part(LOGITS_PARTS, spec.logits_part, runtime) if spec.logits_part else None
         for e, run in enumerate(spec.order):
             if not 0 <= run.layer < len(spec.layers):
                 raise ValueError(f"order[{e}] names layer {run.layer}, the model has {len(spec.layers)}")
@@ -62,29 +68,34 @@ class DecoderModel:
 
     @property
     def graph_safe(self) -> bool:
-        parts = [self.final_norm]
+        parts = [self.final_norm, self.input_part, self.logits_part]
         for b in self.blocks:
-            parts += [b.norm1, b.mixer, b.norm2, b.ffn, getattr(b.mixer, "position", None)]
+            for part in b.parts.values():
+                parts += [part, getattr(part, "position", None)]
         return all(getattr(p, "graph_safe", False) for p in parts if p is not None)
 
     # -- tensors ---------------------------------------------------------------
-    def _slots(self, i):
-        b = self.blocks[i]
-        return {"norm1": b.norm1, "mixer": b.mixer, "norm2": b.norm2, "ffn": b.ffn}
+    def _named_parts(self):
+        """(what it is, part, local name -> checkpoint name) of every part that holds tensors, in a fixed order."""
+        s = self.spec
+        if self.input_part is not None:
+            yield "input part", self.input_part, s.input_names
+        for i, layer in enumerate(s.layers):
+            for slot, part in self.blocks[i].parts.items():
+                yield f"layer {i}", part, {local: layer.names.get(f"{slot}.{local}") for local in part.param_specs()}, f"{slot}."
+        yield "final norm", self.final_norm, s.final_norm_names
+        if self.logits_part is not None:
+            yield "logits part", self.logits_part, s.logits_names
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         """checkpoint name -> ParamSpec, in a fixed order."""
         s = self.spec
         out = {s.embed_name: ParamSpec((s.vocab_size, s.hidden_size))}
-        for i, layer in enumerate(s.layers):
-            for slot, part in self._slots(i).items():
-                for local, ps in part.param_specs().items():
-                    key = f"{slot}.{local}"
-                    if key not in layer.names:
-                        raise KeyError(f"layer {i}: no checkpoint name given for '{key}'")
-                    out[layer.names[key]] = ps
-        for local, ps in self.final_norm.param_specs().items():
-            out[s.final_norm_names[local]] = ps
+        for where, part, names, *prefix in self._named_parts():
+            for local, ps in part.param_specs().items():
+                if names.get(local) is None:
+                    raise KeyError(f"{where}: no checkpoint name given for '{(prefix[0] if prefix else '') + local}'")
+                out[names[local]] = ps
         if s.lm_head_name is not None:
             out[s.lm_head_name] = ParamSpec((s.vocab_size, s.hidden_size))
         return out
@@ -92,17 +103,16 @@ class DecoderModel:
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         s = self.spec
         self.embed = tensors[s.embed_name]
-        for i, layer in enumerate(s.layers):
-            for slot, part in self._slots(i).items():
-                part.bind({local: tensors[layer.names[f"{slot}.{local}"]] for local in part.param_specs()})
-        self.final_norm.bind({local: tensors[s.final_norm_names[local]] for local in self.final_norm.param_specs()})
+        for where, part, names, *prefix in self._named_parts():
+            part.bind({local: tensors[names[local]] for local in part.param_specs()})
         self.head = self.embed if s.lm_head_name is None else tensors[s.lm_head_name]
 
     # -- cache -----------------------------------------------------------------
     def cache_needs(self) -> List[CacheNeed]:
         out = []
         for run in self.spec.order:
-            mixer = self.blocks[run.layer].mixer
+            block = self.blocks[run.layer]
+            mixer = getattr(block, block.MIXER_SLOT)
             out.append(CacheNeed(mixer.cache_spec(), mixer.state_spec(), run.cache_from))
         return out
 
@@ -119,6 +129,8 @@ class DecoderModel:
         resid = torch.empty((n, s.hidden_size), dtype=torch.float32, device=self.runtime.device)
         with bucket("embed"):
             ops.embed(ctx.token_ids, self.embed, resid, s.embed_scale)
+        if self.input_part is not None:
+            self.input_part.forward(resid, ctx)
         pending = None
         for e, run in enumerate(s.order):
             resid, pending = self.blocks[run.layer].forward(resid, pending, ctx, self.caches[e])
@@ -129,4 +141,7 @@ class DecoderModel:
         ops.gather_rows_add(resid, pending, ctx.logit_rows, picked)
         z = self.final_norm.forward(picked, None)
         with bucket("lm_head"):
-            return ops.linear(z, self.head, out_dtype=torch.float32)
+            logits = ops.linear(z, self.head, out_dtype=torch.float32)
+        if self.logits_part is not None:
+            self.logits_part.forward(logits, ctx)
+        return logits

@@ -9,7 +9,7 @@ from __future__ import annotations
 
 from ..config.model_config import LlamaConfig
 from ..parts.base import PartSpec
-from .spec import LayerSpec, ModelSpec, RunEntry
+from .spec import ModelSpec, RunEntry, prenorm_layer
 
 
 def build_llama(cfg: LlamaConfig) -> ModelSpec:
@@ -23,7 +23,7 @@ def build_llama(cfg: LlamaConfig) -> ModelSpec:
     layers = []
     for i in range(cfg.num_hidden_layers):
         p = f"model.layers.{i}."
-        layers.append(LayerSpec(norm, mixer, norm, ffn, names={
+        layers.append(prenorm_layer(norm, mixer, norm, ffn, names={
             "norm1.weight": p + "input_layernorm.weight",
             "mixer.q": p + "self_attn.q_proj.weight", "mixer.k": p + "self_attn.k_proj.weight",
             "mixer.v": p + "self_attn.v_proj.weight", "mixer.o": p + "self_attn.o_proj.weight",
@@ -38,5 +38,6 @@ def build_llama(cfg: LlamaConfig) -> ModelSpec:
         final_norm_names={"weight": "model.norm.weight"},
         lm_head_name=None if cfg.tie_word_embeddings else "lm_head.weight",
         ignore_suffixes=("rotary_emb.inv_freq",),
-        ignore_names=("lm_head.weight",) if cfg.tie_word_embeddings else (),
+        # a tied checkpoint may store the head a second time, but only as a copy of the embedding
+        must_equal={"lm_head.weight": "model.embed_tokens.weight"} if cfg.tie_word_embeddings else {},
     )

@@ -12,14 +12,17 @@ from ..parts.base import PartSpec
 
 @dataclass
 class LayerSpec:
-    """One layer: its parts and the checkpoint name of each local tensor name,
-    keyed ``"<slot>.<local>"`` with slot in norm1 / mixer / norm2 / ffn."""
-    norm1: PartSpec
-    mixer: PartSpec
-    norm2: PartSpec
-    ffn: PartSpec
+    """One layer: the kind of its block, one part per slot that the block kind
+    declares (``Block.SLOTS``), and the checkpoint name of each local tensor name,
+    keyed ``"<slot>.<local>"``."""
+    parts: Dict[str, PartSpec]
     names: Dict[str, str]
     block: str = "prenorm"
+
+
+def prenorm_layer(norm1: PartSpec, mixer: PartSpec, norm2: PartSpec, ffn: PartSpec, names: Dict[str, str]) -> LayerSpec:
+    """The pre-norm residual layer: norm -> mixer -> add, norm -> feed-forward -> add."""
+    return LayerSpec({"norm1": norm1, "mixer": mixer, "norm2": norm2, "ffn": ffn}, names, "prenorm")
 
 
 @dataclass
@@ -44,4 +47,11 @@ class ModelSpec:
     lm_head_name: Optional[str]          # None: the head is the embedding table (tied)
     ignore_suffixes: Tuple[str, ...] = ()
     ignore_names: Tuple[str, ...] = ()
+    must_equal: Dict[str, str] = field(default_factory=dict)   # tensor that may be absent -> the tensor it must copy
     embed_scale: float = 1.0
+    # optional parts that run once per step: after the embedding (registry INPUT_PARTS) and on the head's
+    # output (LOGITS_PARTS), each with the checkpoint names of its tensors
+    input_part: Optional[PartSpec] = None
+    input_names: Dict[str, str] = field(default_factory=dict)
+    logits_part: Optional[PartSpec] = None
+    logits_names: Dict[str, str] = field(default_factory=dict)

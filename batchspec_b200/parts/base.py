@@ -108,7 +108,8 @@ class PositionEncoding(Part):
     """``apply(q, k, ctx)`` rotates/offsets q [n, Hq, hd] and k [n, Hkv, hd] (views,
     in place) for the tokens' absolute positions ``ctx.positions``.  A part that
     can be folded into the attention mixer's fused rotate-and-append kernel also
-    offers ``rope_table()`` -> (inv_freq float32 [rotary_dim/2], rotary_dim)."""
+    offers ``rope_table()`` -> (``ops.rope_frequency_table`` of rotary_dim/2 frequencies, rotary_dim,
+    interleaved)."""
 
     def apply(self, q: torch.Tensor, k: torch.Tensor, ctx) -> None:
         raise NotImplementedError

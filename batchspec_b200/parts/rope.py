@@ -3,8 +3,9 @@
 Frequencies: f_j = theta^(-2j/rotary_dim) (batchspec/models/modules/rope.py:27-31),
 optionally rescaled by the llama3 rule whose constants the reference forwards
 (rope.py:33-44) or divided by a plain factor (``rope_scale``).  The table is built
-in float64 on the host and held in float32; the angle position * f_j, its sine and
-cosine and the rotation are float32 on the device.
+in float64 on the host and held as two float32 numbers per frequency; the kernels form
+the angle position * f_j in float64 and reduce it to [-pi, pi] there, so that it is
+right to 2e-7 rad at any position; sine, cosine and the rotation are float32.
 
 Pairing: the reference rotates adjacent pairs after permuting Wq/Wk rows offline
 (tools/prepare_model/convert_weights.py:112-128); this part keeps the
@@ -54,7 +55,8 @@ class RotaryEmbedding(PositionEncoding):
         if self.rotary_dim % 2 or self.rotary_dim > self.head_dim:
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and <= head_dim {self.head_dim}")
         self.interleaved = bool(interleaved)
-        self.inv_freq = rope_inv_freq(self.rotary_dim, theta, scaling).to(torch.float32).to(runtime.device)
+        self.frequencies = rope_inv_freq(self.rotary_dim, theta, scaling)            # float64, on the host
+        self.inv_freq = ops.rope_frequency_table(self.frequencies, runtime.device)
 
     def rope_table(self):
         return self.inv_freq, self.rotary_dim, self.interleaved

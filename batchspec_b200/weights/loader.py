@@ -25,9 +25,10 @@ from .safetensors_io import open_model_files, write_safetensors
 class WeightsError(ValueError):
     """Lists every missing tensor, unexpected tensor and wrong shape of a folder."""
 
-    def __init__(self, where, missing, unexpected, wrong_shape, wrong_dtype=()):
+    def __init__(self, where, missing, unexpected, wrong_shape, wrong_dtype=(), unequal=()):
         self.missing, self.unexpected = list(missing), list(unexpected)
         self.wrong_shape, self.wrong_dtype = list(wrong_shape), list(wrong_dtype)
+        self.unequal = list(unequal)
         lines = [f"weights in {where} do not match the model:"]
         if self.missing:
             lines.append(f"  missing tensors ({len(self.missing)}): " + ", ".join(self.missing))
@@ -39,6 +40,9 @@ class WeightsError(ValueError):
         if self.wrong_dtype:
             lines.append(f"  wrong dtypes ({len(self.wrong_dtype)}): " + ", ".join(
                 f"{n} is {got}" for n, got in self.wrong_dtype))
+        if self.unequal:
+            lines.append(f"  tensors that must be copies of another and are not ({len(self.unequal)}): " + ", ".join(
+                f"{n} differs from {other}" for n, other in self.unequal))
         super().__init__("\n".join(lines))
 
 
@@ -55,16 +59,24 @@ def _held_dtype(spec: ParamSpec, stored: torch.dtype, run_dtype: torch.dtype) ->
 
 
 def load_weights(model_dir, specs: Dict[str, ParamSpec], run_dtype: torch.dtype, device,
-                 ignore_suffixes=(), ignore_names=()) -> Dict[str, torch.Tensor]:
+                 ignore_suffixes=(), ignore_names=(), must_equal: Optional[Dict[str, str]] = None) -> Dict[str, torch.Tensor]:
+    """``must_equal``: name -> name of a wanted tensor.  Such a tensor may be absent; if the folder has it, it
+    has to be an exact copy of the other one (a tied head stored a second time), else that is an error."""
+    must_equal = dict(must_equal or {})
     files = open_model_files(model_dir)
     where: Dict[str, object] = {}
     for f in files:
         for name in f.entries:
             where[name] = f
     missing = [n for n in specs if n not in where]
-    unexpected = [n for n in where if n not in specs and n not in ignore_names
+    unexpected = [n for n in where if n not in specs and n not in ignore_names and n not in must_equal
                   and not any(n.endswith(s) for s in ignore_suffixes)]
-    wrong_shape, wrong_dtype = [], []
+    wrong_shape, wrong_dtype, unequal = [], [], []
+    for name, other in must_equal.items():
+        if name in where and other in where:
+            a, b = where[name].tensor(name), where[other].tensor(other)
+            if a.shape != b.shape or a.dtype != b.dtype or not torch.equal(a, b):
+                unequal.append((name, other))
     for name, spec in specs.items():
         if name not in where:
             continue
@@ -73,8 +85,8 @@ def load_weights(model_dir, specs: Dict[str, ParamSpec], run_dtype: torch.dtype,
             wrong_shape.append((name, shape, spec.shape))
         if (spec.role == "int" and dtype not in _INTS) or (spec.role != "int" and dtype not in _FLOATS):
             wrong_dtype.append((name, str(dtype).replace("torch.", "")))
-    if missing or unexpected or wrong_shape or wrong_dtype:
-        raise WeightsError(model_dir, missing, unexpected, wrong_shape, wrong_dtype)
+    if missing or unexpected or wrong_shape or wrong_dtype or unequal:
+        raise WeightsError(model_dir, missing, unexpected, wrong_shape, wrong_dtype, unequal)
     out = {}
     for name, spec in specs.items():
         t = where[name].tensor(name)

@@ -1,6 +1,7 @@
 """Makes ``reference_parts.json``: outputs of the reference project's OWN modules
 on the CPU, for the parts of it that run without a GPU, on tiny configuration A
-with this repository's seeded random weights.  ``tests/test_plain_reference.py``
+with weights from numpy's frozen ``RandomState`` stream (``make_reference_gpu.anchor_weights``:
+the same values on every torch build).  ``tests/test_plain_reference.py``
 checks the plain implementation against these numbers.
 
 Run once, from the repository root, with the reference on the path:
@@ -18,7 +19,6 @@ for those the plain implementation rests on the formulas cited in its docstrings
 """
 import json
 import sys
-import tempfile
 from pathlib import Path
 
 import torch
@@ -27,7 +27,10 @@ ROOT = Path(__file__).resolve().parents[2]
 sys.path.insert(0, str(ROOT))
 sys.path.insert(0, str(ROOT / "tests"))
 
+sys.path.insert(0, str(ROOT / "tests" / "golden"))
+
 import helpers as H                     # noqa: E402
+import make_reference_gpu as G          # noqa: E402
 import plain_llama as P                 # noqa: E402
 from batchspec.backends.utils.sampling import sample                      # noqa: E402  (the reference)
 from batchspec.models.configs.model_config import ModelArgs               # noqa: E402
@@ -37,9 +40,7 @@ from batchspec.models.standard_model import StandardTransformer           # noqa
 
 def main():
     cfgj = H.TINY_A
-    with tempfile.TemporaryDirectory() as tmp:
-        folder = H.make_folder(tmp, cfgj, seed=0, dtype=torch.float32)
-        cfg, w = P.read_model_folder(folder)
+    w = {k: v.double() for k, v in G.anchor_weights(cfgj, seed=0).items()}
     args = ModelArgs(block_size=cfgj["max_position_embeddings"], vocab_size=cfgj["vocab_size"],
                      n_layer=cfgj["num_hidden_layers"], n_head=cfgj["num_attention_heads"], dim=cfgj["hidden_size"],
                      intermediate_size=cfgj["intermediate_size"], n_local_heads=cfgj["num_key_value_heads"],
@@ -63,7 +64,7 @@ def main():
     model.load_state_dict({k: v.float() for k, v in sd.items()}, strict=True)
     model.eval()
     tokens = torch.tensor([5, 17, 400])
-    out = {"tokens": tokens.tolist(), "weight_check": float(w["model.layers.1.mlp.up_proj.weight"][3, 7])}
+    out = {"tokens": tokens.tolist()}
     with torch.no_grad():
         x = model.tok_embeddings(tokens)
         layer = model.layers[0]

@@ -200,15 +200,20 @@ def run_trace_subprocess(folder, dtype, steps, out_dir, max_tokens, extra_args=(
     return out
 
 
-def compare_with_oracle(got, folder, requests, dtype_name):
-    """Every produced row against the plain implementation; returns the worst
-    error and where it was, for the failure message."""
+def compare_with_oracle(got, folder, requests, dtype_name, expect=None):
+    """Every row against the plain implementation.  ``got`` has to hold exactly the rows ``expect`` (a set of
+    (request, position); default: every position of every request), so a row that never came back fails the
+    comparison instead of being skipped.  Returns the worst error and where it was."""
+    if expect is None:
+        expect = {(rid, p) for rid, toks in requests.items() for p in range(len(toks))}
+    assert set(got) == set(expect), (f"{len(set(expect) - set(got))} rows missing, {len(set(got) - set(expect))} "
+                                     f"unexpected, e.g. {sorted(set(expect) ^ set(got), key=str)[:4]}")
     worst = (0.0, None)
     for rid, toks in requests.items():
         ref = oracle_logits(folder, toks)
         scale = np.abs(ref).max()
         for p in range(len(toks)):
-            if (rid, p) not in got:
+            if (rid, p) not in expect:
                 continue
             err = float(np.abs(got[(rid, p)].astype(np.float64) - ref[p]).max() / scale)
             if err > worst[0]:

@@ -61,8 +61,8 @@ def test_groups_follow_the_needs():
 def test_reserve_commit_release_and_page_arithmetic():
     m = manager([CacheNeed(FULL, None, None)])
     m.admit("a")
-    assert m.pages_needed(0, 1) == 1 and m.pages_needed(3, 1) == 0 and m.pages_needed(4, 1) == 1
-    assert m.pages_needed(3, 6) == 2
+    assert m.pages_needed(0, 1) == [1] and m.pages_needed(3, 1) == [0] and m.pages_needed(4, 1) == [1]
+    assert m.pages_needed(3, 6) == [2]
     m.reserve("a", 5)
     m.commit("a", 5)
     assert len(m.requests["a"].tables[0]) == 2 and m.length("a") == 5
@@ -111,10 +111,42 @@ def test_state_is_zeroed_at_admission():
     assert rc2.slot == rc.slot and float(m.state_tensors[0][rc2.slot].abs().sum()) == 0
 
 
+def test_groups_with_pages_of_their_own_size_and_one_tensor_per_token():
+    """A mixer may store one tensor per token and choose its group's page size: the same request then has block
+    tables of different lengths, and every count of pages is per group."""
+    latent = CacheSpec("full", (12,), tensors=1, page_size=3)
+    m = CacheManager([CacheNeed(FULL, None, None), CacheNeed(latent, None, None), CacheNeed(FULL, None, None)],
+                     4, 6, 2, torch.float32, "cpu", scratch_page=True)
+    assert [g.page_size for g in m.groups] == [4, 3] and [g.runs for g in m.groups] == [[0, 2], [1]]
+    assert [g.pool.num_pages for g in m.groups] == [6, 8], "the same number of tokens in pages of either size"
+    assert m.groups[0].pages.shape == (2, 7, 2, 4 * 32) and m.groups[1].pages.shape == (1, 9, 1, 3 * 12)
+    assert m.layer_caches[1].kv.shape == (9, 1, 36)
+    m.admit("a")
+    assert m.pages_needed(0, 7) == [2, 3] and m.pages_missing("a", 7) == [2, 3]
+    m.reserve("a", 7)
+    m.commit("a", 7)
+    assert [len(t) for t in m.requests["a"].tables] == [2, 3]
+    assert m.pages_missing("a", 1) == [0, 0] and m.pages_missing("a", 2) == [1, 0] and m.pages_missing("a", 3) == [1, 1]
+    assert m.room_for(7, [1, 0]) == 2 and m.room_for(7, [0, 5]) == 1 and m.room_for(7, [2, 2]) == 8
+    assert m.peak_pages(10, 10) == [3, 4]
+    m.admit("b")
+    assert m.free_pages() == [4, 5]
+    assert m.can_reserve([(0, 15)]) and not m.can_reserve([(0, 15), (7, 2)])         # group 0: 4 + 1 > 4 free
+    assert not m.can_reserve([(0, 16)])                                              # group 1: 6 > 5 free
+    with pytest.raises(OutOfPages):
+        m.reserve("b", 16)                                                           # group 0 alone would have room
+    assert m.requests["b"].tables == [[], []], "all or nothing, over all groups"
+    m.check_invariants()
+    m.release_all()
+    assert m.free_pages() == [6, 8] and m.scratch_pages() == [6, 8] and m.scratch_slot() == 2
+
+
 @pytest.mark.parametrize("seed", range(6))
 def test_random_orders_keep_the_books(seed):
     rng = random.Random(seed)
-    needs = [CacheNeed(FULL, None, None), CacheNeed(WIN, None, None)]
+    needs = [CacheNeed(FULL, None, None), CacheNeed(WIN, None, None),
+             CacheNeed(CacheSpec("full", (5,), tensors=1, page_size=rng.choice([3, 16])), None, None),
+             CacheNeed(CacheSpec("window", (2, 8), window=7, page_size=2), None, None)]
     m = manager(needs, page_size=rng.choice([1, 4, 8]), num_pages=rng.randrange(6, 30), max_requests=5)
     live, next_id, refused = [], 0, 0
     for _ in range(600):

@@ -38,10 +38,25 @@ def test_defaults_derived_not_assumed():
     (dict(num_key_value_heads=3), "multiple"),
     (dict(hidden_size="64"), "integer"),
     (dict(head_dim=15), "even"),
+    (dict(model_type="mistral"), "model_type"),
+    (dict(sliding_window=4096), "sliding_window"),
+    (dict(attention_dropout=0.1), "attention_dropout"),
+    (dict(partial_rotary_factor=0.5), "partial_rotary_factor"),
+    (dict(rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                            original_max_position_embeddings=64, attention_factor=1.3)), "attention_factor"),
+    (dict(rope_scaling=dict(rope_type="linear", factor=2.0, low_freq_factor=1.0)), "low_freq_factor"),
 ])
 def test_rejects_what_it_cannot_run(patch, word):
     with pytest.raises(ConfigError, match=word):
         config_from_json_dict({**H.TINY_A, **patch})
+
+
+def test_keys_nothing_reads_are_listed_and_neutral_values_pass():
+    cfg = config_from_json_dict({**H.TINY_A, "sliding_window": None, "attention_dropout": 0.0, "use_cache": True,
+                                 "pretraining_tp": 1, "some_new_option": 3, "another": "x"})
+    assert cfg.unread_keys == ("another", "some_new_option")
+    assert config_from_json_dict(H.TINY_A).unread_keys == ()
+    assert "unread_keys" not in cfg.to_json_dict()
 
 
 def test_round_trip_through_a_folder(tmp_path):

@@ -58,7 +58,8 @@ def test_part_rope_matches_the_interleaved_reference_on_permuted_rows():
     sc = dict(cfg["rope_scaling"])
     part = build_part(POSITION_ENCODINGS, PartSpec("rope", dict(head_dim=32, theta=cfg["rope_theta"], scaling=sc)),
                       _runtime(torch.float32))
-    torch.testing.assert_close(part.inv_freq.cpu().double(), P.rope_frequencies(cfg), rtol=1e-6, atol=0)
+    torch.testing.assert_close(part.frequencies, P.rope_frequencies(cfg), rtol=1e-13, atol=0)
+    torch.testing.assert_close(part.inv_freq.cpu().double().sum(0), P.rope_frequencies(cfg), rtol=1e-13, atol=0)
     g = torch.Generator().manual_seed(1)
     Hn, hd, T = 3, 32, 5
     w = torch.randn(Hn * hd, 24, generator=g, dtype=torch.float64)
@@ -115,7 +116,7 @@ def test_part_attention_and_block(dtype, window):
     ffn.bind({n: t.to(DEV) for n, t in wf.items()})
     norm1.bind({"weight": wn1.to(DEV)})
     norm2.bind({"weight": wn2.to(DEV)})
-    block = BLOCKS["prenorm"](norm1, mixer, norm2, ffn)
+    block = BLOCKS["prenorm"](norm1=norm1, mixer=mixer, norm2=norm2, ffn=ffn)
     cache = CacheManager([CacheNeed(mixer.cache_spec(), None, None)], 4, 16, 2, dtype, DEV)
     runner = StepRunner(None, cache, 10, DEV)
     xs = {"a": torch.randn(11, d, generator=g), "b": torch.randn(7, d, generator=g)}
@@ -436,7 +437,7 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     from dataclasses import dataclass
     from batchspec_b200.config import config_from_json_dict, register_config_class
     from batchspec_b200.engine import Engine
-    from batchspec_b200.models import LayerSpec, ModelSpec, RunEntry, register_model
+    from batchspec_b200.models import ModelSpec, prenorm_layer, RunEntry, register_model
     from batchspec_b200.parts import MIXERS, Mixer, ParamSpec, PartSpec, StateSpec, register_part
 
     @register_part(MIXERS, "toy_decay")
@@ -493,10 +494,10 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
                      "ffn.up": f"l{i}.up", "ffn.down": f"l{i}.down"}
             if i % 2 == 0:
                 names["mixer.w"] = f"l{i}.toy"
-                layers.append(LayerSpec(norm, toy, norm, ffn, names))
+                layers.append(prenorm_layer(norm, toy, norm, ffn, names))
             else:
                 names.update({"mixer." + k: f"l{i}.{k}" for k in "qkvo"})
-                layers.append(LayerSpec(norm, att, norm, ffn, names))
+                layers.append(prenorm_layer(norm, att, norm, ffn, names))
         return ModelSpec(cfg.vocab_size, cfg.width, layers, [RunEntry(i) for i in range(cfg.depth)], norm,
                          "emb", {"weight": "final"}, None)
 
@@ -565,7 +566,7 @@ def test_run_order_shared_cache_window_and_toy_parts(tmp_path, dtype):
     from dataclasses import dataclass
     from batchspec_b200.config import config_from_json_dict, register_config_class
     from batchspec_b200.engine import Engine
-    from batchspec_b200.models import LayerSpec, ModelSpec, RunEntry, register_model
+    from batchspec_b200.models import ModelSpec, prenorm_layer, RunEntry, register_model
     from batchspec_b200.parts import (FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, ParamSpec, PartSpec,
                                       PositionEncoding, register_part)
     from batchspec_b200.weights import write_random_model
@@ -644,7 +645,7 @@ def test_run_order_shared_cache_window_and_toy_parts(tmp_path, dtype):
         names0.update({"mixer." + k: "a." + k for k in "qkvo"})
         names1 = {"norm1.weight": "b.n1", "norm2.weight": "b.n2", "ffn.router": "b.router", "ffn.w1": "b.w1", "ffn.w2": "b.w2"}
         names1.update({"mixer." + k: "b." + k for k in "qkvo"})
-        layers = [LayerSpec(norm, att0, norm, ffn0, names0), LayerSpec(norm, att1, norm, ffn1, names1)]
+        layers = [prenorm_layer(norm, att0, norm, ffn0, names0), prenorm_layer(norm, att1, norm, ffn1, names1)]
         order = [RunEntry(0), RunEntry(1), RunEntry(0), RunEntry(1, cache_from=1)]
         return ModelSpec(cfg.vocab_size, W, layers, order, norm, "emb", {"weight": "final"}, None)
 

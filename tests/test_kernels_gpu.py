@@ -97,8 +97,9 @@ def test_sgemm_is_true_float32(ops, M, N, K):
 
 
 def _rope_reference(x, pos, inv_freq, rot, interleaved):
-    ang = pos.float()[:, None] * inv_freq[None, :]
-    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    """float64 angle from the float32 frequencies given, float32 result."""
+    ang = pos.double()[:, None] * inv_freq.double()[None, :]
+    c, s = torch.cos(ang)[:, None, :].float(), torch.sin(ang)[:, None, :].float()
     out = x.clone()
     if interleaved:
         a, b = x[..., 0:rot:2], x[..., 1:rot:2]
@@ -120,6 +121,7 @@ def test_rope_and_cache_append(ops, dtype, Hq, Hkv, hd, rot, inter, ps, lens):
     n = sum(lens)
     qkv = torch.randn(n, (Hq + 2 * Hkv) * hd, device=DEV, generator=g).to(dtype)
     inv_freq = (10000.0 ** (-torch.arange(0, rot // 2, device=DEV).float() * 2 / rot))
+    table = ops.rope_frequency_table(inv_freq, DEV)
     pos = torch.cat([torch.arange(b, b + l) for l, b in zip(lens, before)]).to(DEV, torch.int32)
     ent = torch.cat([torch.full((l,), i) for i, l in enumerate(lens)]).to(DEV, torch.int32)
     pages_per = [-(-(b + l) // ps) for l, b in zip(lens, before)]
@@ -132,7 +134,7 @@ def test_rope_and_cache_append(ops, dtype, Hq, Hkv, hd, rot, inter, ps, lens):
     ref_k = _rope_reference(qkv[:, Hq * hd:(Hq + Hkv) * hd].float().view(n, Hkv, hd), pos, inv_freq, rot, inter).to(dtype)
     v = qkv[:, (Hq + Hkv) * hd:].view(n, Hkv, hd).clone()
     work = qkv.clone()
-    ops.rope_kv_append(work, Hq, Hkv, hd, inv_freq, rot, inter, pos, ent, indptr, indices, cache, ps)
+    ops.rope_kv_append(work, Hq, Hkv, hd, table, rot, inter, pos, ent, indptr, indices, cache, ps)
     torch.testing.assert_close(work[:, :Hq * hd].float().view(n, Hq, hd), ref_q.float(), **tol(dtype))
     want = torch.full_like(cache, 7.0)
     for t in range(n):
@@ -148,12 +150,78 @@ def test_rope_and_cache_append(ops, dtype, Hq, Hkv, hd, rot, inter, ps, lens):
     # read-only run (a layer that shares another layer's cache): q rotated, cache untouched
     cache2 = torch.full_like(cache, 7.0)
     work2 = qkv.clone()
-    ops.rope_kv_append(work2, Hq, Hkv, hd, inv_freq, rot, inter, pos, ent, indptr, indices, cache2, ps, write_kv=False)
+    ops.rope_kv_append(work2, Hq, Hkv, hd, table, rot, inter, pos, ent, indptr, indices, cache2, ps, write_kv=False)
     assert torch.equal(work2[:, :Hq * hd], work[:, :Hq * hd]) and bool((cache2 == 7.0).all())
     # the stand-alone rotation agrees with the fused one
     alone = qkv.clone()
-    ops.rope_inplace(alone[:, :Hq * hd].view(n, Hq, hd), pos, inv_freq, rot, inter)
+    ops.rope_inplace(alone[:, :Hq * hd].view(n, Hq, hd), pos, table, rot, inter)
     assert torch.equal(alone[:, :Hq * hd], work[:, :Hq * hd])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("inter", [False, True])
+@pytest.mark.parametrize("n", [9, 80])                 # the per-head kernel; the 16-byte bfloat16 kernel (n >= 64)
+def test_rope_at_large_positions(ops, dtype, inter, n):
+    """Positions up to 131,071 with the Llama-3 base and the llama3 rule: the angle is formed in float64 on the
+    device, so a float32 run stays within its own tolerance there (a float32 product position * frequency would
+    be off by up to 8e-3 rad).  Every rotary pair of q holds (1, 0): the output shows cos and sin of each angle."""
+    Hq, Hkv, hd, ps = 4, 2, 128, 16
+    import plain_llama as P
+    freqs = P.rope_frequencies(dict(head_dim=hd, rope_theta=500000.0, hidden_size=Hq * hd, num_attention_heads=Hq,
+                                    rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0,
+                                                      high_freq_factor=4.0, original_max_position_embeddings=8192)))
+    table = ops.rope_frequency_table(freqs, DEV)
+    marks = [0, 1, 8191, 8192, 32767, 32768, 131070, 131069]      # 131,071 itself only once, as the last token
+    positions = torch.tensor((marks * (n // len(marks) + 1))[:n - 1] + [131071], dtype=torch.int32)
+    g = torch.Generator().manual_seed(3)
+    qkv = torch.randn(n, (Hq + 2 * Hkv) * hd, generator=g, dtype=torch.float64)
+    q = qkv[:, :Hq * hd].view(n, Hq, hd)
+    q[:, 0] = 0
+    if inter:
+        q[:, 0, 0::2] = 1.0
+    else:
+        q[:, 0, :hd // 2] = 1.0
+    qkv = qkv.to(dtype)
+    ang = positions.double()[:, None] * freqs[None, :]
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+
+    def rotate(x):
+        x = x.double()
+        out = torch.empty_like(x)
+        if inter:
+            a, b = x[..., 0::2], x[..., 1::2]
+            out[..., 0::2], out[..., 1::2] = a * c - b * s, a * s + b * c
+        else:
+            a, b = x[..., :hd // 2], x[..., hd // 2:]
+            out[..., :hd // 2], out[..., hd // 2:] = a * c - b * s, a * s + b * c
+        return out
+
+    want_q = rotate(qkv[:, :Hq * hd].view(n, Hq, hd))
+    want_k = rotate(qkv[:, Hq * hd:(Hq + Hkv) * hd].view(n, Hkv, hd))
+    work = qkv.to(DEV)
+    pos = positions.to(DEV)
+    ent = torch.zeros(n, dtype=torch.int32, device=DEV)
+    # one request whose table gives every page that these positions touch a real page of its own
+    n_table = 131072 // ps
+    touched = sorted(set((positions // ps).tolist()))
+    indices = torch.zeros(n_table, dtype=torch.int32)
+    indices[touched] = torch.arange(1, len(touched) + 1, dtype=torch.int32)
+    indices = indices.to(DEV)
+    indptr = torch.tensor([0, n_table], dtype=torch.int32, device=DEV)
+    cache = torch.zeros(len(touched) + 1, 2, Hkv, ps, hd, device=DEV, dtype=dtype)
+    ops.rope_kv_append(work, Hq, Hkv, hd, table, hd, inter, pos, ent, indptr, indices, cache, ps)
+    alone = qkv.to(DEV)
+    ops.rope_inplace(alone[:, :Hq * hd].view(n, Hq, hd), pos, table, hd, inter)
+    got_q = work[:, :Hq * hd].view(n, Hq, hd).double().cpu()
+    assert torch.equal(alone[:, :Hq * hd], work[:, :Hq * hd])
+    # float32: the reduced angle is rounded to float32 (2e-7 rad) and sine / cosine are float32
+    tol = 1e-6 if dtype == torch.float32 else 2.0 ** -8
+    scale = qkv.abs().max().item()
+    assert (got_q[:, 0] - want_q[:, 0]).abs().max() <= tol, "the pairs that hold (1, 0) show the angle itself"
+    assert (got_q - want_q).abs().max() <= tol * scale
+    last = n - 1                                            # position 131,071: row 15 of the last touched page
+    got_k = cache[len(touched), 0, :, 15].double().cpu()
+    assert (got_k - want_k[last]).abs().max() <= tol * scale
 
 
 def _attention_case(ops, dtype, Hq, Hkv, hd, ps, q_lens, kv_lens, window=0, spike=None, seed=0, force_generic=False,
@@ -175,8 +243,8 @@ def _attention_case(ops, dtype, Hq, Hkv, hd, ps, q_lens, kv_lens, window=0, spik
         ks[e][key, head // G, 0] = 30.0
     q, ks, vs = q.to(dtype), [k.to(dtype) for k in ks], [v.to(dtype) for v in vs]
     pages_per = [-(-L // ps) for L in kv_lens]
-    n_pages = sum(pages_per) + 2
-    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(seed + 1))[:sum(pages_per)]
+    n_pages = sum(pages_per) + 3                                       # the last one is never a request's page
+    perm = torch.randperm(n_pages - 1, generator=torch.Generator().manual_seed(seed + 1))[:sum(pages_per)]
     cache = torch.randn(n_pages, 2, Hkv, ps, hd, device=DEV, generator=g).to(dtype)      # garbage where nothing lives
     indptr = [0] + list(np.cumsum(pages_per))
     for e, L in enumerate(kv_lens):
@@ -184,6 +252,16 @@ def _attention_case(ops, dtype, Hq, Hkv, hd, ps, q_lens, kv_lens, window=0, spik
             page = int(perm[indptr[e] + p // ps])
             cache[page, 0, :, p % ps] = ks[e][p]
             cache[page, 1, :, p % ps] = vs[e][p]
+    if window:
+        # Pages that lie wholly before the oldest key any query of the step reads are what the cache manager has
+        # given back by now.  Their table entries point at a page of huge (finite) numbers here: a kernel that
+        # reads one gets a wrong result, not a wild address.
+        poison = n_pages - 1
+        cache[poison] = 3.0e4
+        perm = perm.clone()
+        for e, (ql, L) in enumerate(zip(q_lens, kv_lens)):
+            dead = max(0, (L - ql) - window + 1) // ps
+            perm[indptr[e]:indptr[e] + dead] = poison
     qo = [0] + list(np.cumsum(q_lens))
     pos = torch.cat([torch.arange(L - ql, L) for ql, L in zip(q_lens, kv_lens)]).to(DEV, torch.int32)
     ent = torch.cat([torch.full((ql,), i) for i, ql in enumerate(q_lens)]).to(DEV, torch.int32)
@@ -255,6 +333,70 @@ def test_split_keys_agree_with_one_pass(ops, splits):
     torch.testing.assert_close(a, want, rtol=3e-2, atol=2e-2)
     b, _ = _attention_case(ops, torch.bfloat16, 8, 2, 128, 16, [1, 1, 2], [1000, 70, 513], force_generic=True, seed=7)
     torch.testing.assert_close(a, b, rtol=3e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("q_lens,kv_lens", [([257, 1024], [8192 + 257, 30000]), ([1024, 257], [8192, 30000 + 257]),
+                                            ([4096], [30000])])
+def test_prompt_portions_deep_inside_a_long_context(ops, q_lens, kv_lens):
+    """Portions of a prompt at cached lengths of 8,192 and 30,000 tokens on the tensor-core prompt kernel
+    (head_dim 128, page 16): hundreds of key tiles per query tile, the heaviest-first order of CTAs, pages looked
+    up far into a scrambled table.  Queries are scaled up so that the softmax is peaked (with unit-variance
+    scores over 30,000 keys every output would be near zero and any fault would hide inside the tolerance); one
+    query per request also has a single far key that must win.  Reference: float32 torch products on the GPU."""
+    Hq, Hkv, hd, ps = 32, 8, 128, 16
+    G = Hq // Hkv
+    g = torch.Generator(device=DEV).manual_seed(11)
+    n, scale = sum(q_lens), 1.0 / math.sqrt(hd)
+    q = (torch.randn(n, Hq * hd, device=DEV, generator=g) * 5.0)
+    ks = [torch.randn(L, Hkv, hd, device=DEV, generator=g) for L in kv_lens]
+    vs = [torch.randn(L, Hkv, hd, device=DEV, generator=g) for L in kv_lens]
+    qo = [0] + list(np.cumsum(q_lens))
+    far = []
+    for e, (ql, L) in enumerate(zip(q_lens, kv_lens)):          # the last query's head 5 looks at key 3 alone
+        t = qo[e + 1] - 1
+        q[t].view(Hq, hd)[5] = 0
+        q[t].view(Hq, hd)[5, 0] = 60.0
+        ks[e][:, 5 // G, 0].clamp_(-1, 1)
+        ks[e][3, 5 // G, 0] = 30.0
+        far.append((t, e))
+    q, ks, vs = q.bfloat16(), [k.bfloat16() for k in ks], [v.bfloat16() for v in vs]
+    pages_per = [-(-L // ps) for L in kv_lens]
+    n_pages = sum(pages_per) + 2
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(12))[:sum(pages_per)]
+    cache = torch.randn(n_pages, 2, Hkv, ps, hd, device=DEV, generator=g).bfloat16()
+    indptr = [0] + list(np.cumsum(pages_per))
+    for e, L in enumerate(kv_lens):
+        pad = pages_per[e] * ps - L
+        for which, src in ((0, ks[e]), (1, vs[e])):
+            full = torch.cat([src, cache[0, which, :, :pad].permute(1, 0, 2)]) if pad else src
+            cache[perm[indptr[e]:indptr[e + 1]].to(DEV), which] = full.view(pages_per[e], ps, Hkv, hd).permute(0, 2, 1, 3)
+    pos = torch.cat([torch.arange(L - ql, L) for ql, L in zip(q_lens, kv_lens)]).to(DEV, torch.int32)
+    ent = torch.cat([torch.full((ql,), i) for i, ql in enumerate(q_lens)]).to(DEV, torch.int32)
+    ctx = SimpleNamespace(qo_indptr=torch.tensor(qo, dtype=torch.int32, device=DEV), positions=pos, tok_entry=ent,
+                          n_entries=len(q_lens), n_tokens=n, max_q_len=max(q_lens), max_kv_len=max(kv_lens),
+                          extras={"min_q_len": min(q_lens)})
+    tables = SimpleNamespace(kv_indptr=torch.tensor(indptr, dtype=torch.int32, device=DEV),
+                             kv_indices=perm.to(DEV, torch.int32), page_size=ps)
+    out = torch.full((n, Hq * hd), float("nan"), device=DEV, dtype=torch.bfloat16)
+    before = ops.launch_count()
+    ops.paged_attention(q, out, cache, ctx, tables, Hq, Hkv, hd, scale, 0)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert ops.launch_count() - before == 1, "only the tensor-core prompt kernel runs for these portions"
+    assert not torch.isnan(out.float()).any()
+    for e, (ql, L) in enumerate(zip(q_lens, kv_lens)):
+        k, v = ks[e].float().permute(1, 0, 2), vs[e].float().permute(1, 0, 2)               # [Hkv, L, hd]
+        key = torch.arange(L, device=DEV)[None, None, :]
+        for b in range(0, ql, 256):                                                        # 256 queries at a time
+            rows = slice(qo[e] + b, qo[e] + min(ql, b + 256))
+            qq = q[rows].float().view(-1, Hkv, G, hd)
+            sc = torch.einsum("qkgd,kld->kgql", qq, k) * scale
+            p_ = pos[rows].long()[None, None, :, None]
+            pr = torch.softmax(sc.masked_fill(key[None] > p_, float("-inf")), dim=-1)
+            want = torch.einsum("kgql,kld->qkgd", pr, v).reshape(-1, Hq * hd)
+            torch.testing.assert_close(out[rows].float(), want, rtol=3e-2, atol=2e-2)
+    for t, e in far:
+        torch.testing.assert_close(out[t].float().view(Hq, hd)[5], vs[e][3, 5 // G].float(), rtol=3e-2, atol=2e-2)
 
 
 RAGGED = [

@@ -153,7 +153,7 @@ def test_generation_with_a_windows_group_under_random_pressure(tmp_path):
     from dataclasses import dataclass
     from batchspec_b200.config import config_from_json_dict, register_config_class
     from batchspec_b200.engine import Sequence
-    from batchspec_b200.models import LayerSpec, ModelSpec, RunEntry, register_model
+    from batchspec_b200.models import ModelSpec, prenorm_layer, RunEntry, register_model
     from batchspec_b200.parts import PartSpec
     from batchspec_b200.weights import write_random_model
     W, HD, HQ, HKV, VOC = 32, 16, 2, 1, 97
@@ -186,8 +186,8 @@ def test_generation_with_a_windows_group_under_random_pressure(tmp_path):
                  "ffn.down": p + ".down"}
             n.update({"mixer." + k: p + "." + k for k in "qkvo"})
             return n
-        layers = [LayerSpec(norm, full, norm, ffn, names("a")), LayerSpec(norm, near, norm, ffn, names("b")),
-                  LayerSpec(norm, near, norm, ffn, names("c"))]
+        layers = [prenorm_layer(norm, full, norm, ffn, names("a")), prenorm_layer(norm, near, norm, ffn, names("b")),
+                  prenorm_layer(norm, near, norm, ffn, names("c"))]
         return ModelSpec(cfg.vocab_size, W, layers, [RunEntry(0), RunEntry(1), RunEntry(2)], norm, "emb",
                          {"weight": "final"}, None)
 

@@ -156,7 +156,7 @@ def test_random_workloads_finish_with_clean_books(seed):
             assert 1 <= len(s.output_ids) <= s.max_new_tokens and s.total_len <= 64
             assert s.finish_reason in ("eos", "length", "context", "cache")
             if s.finish_reason == "cache":
-                assert cache.pages_needed(0, s.total_len) > cache.groups[0].pool.num_pages
+                assert cache.pages_needed(0, s.total_len)[0] > cache.groups[0].pool.num_pages
             if s.finish_reason == "eos":
                 assert s.output_ids[-1] == 3 and 3 not in s.output_ids[:-1]
     assert cache.groups[0].pool.num_free == cache.groups[0].pool.num_pages
@@ -213,4 +213,34 @@ def test_random_workloads_with_a_windows_pool_finish_with_clean_books(seed):
             (s.seq_id, s.status, s.finish_reason, page, window, win_pages, chunk, budget)
     assert cache.groups[1].pool.high_water <= win_pages
     assert all(g.pool.num_free == g.pool.num_pages for g in cache.groups)
+    cache.check_invariants()
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_groups_with_different_page_sizes_under_pressure(seed):
+    """Two groups whose pages hold 4 and 3 tokens, pools of different sizes: every plan fits both pools, requests
+    wait or are preempted for pages of either group, and all of them finish with the books clean."""
+    rng = random.Random(seed)
+    needs = [CacheNeed(FULL, None, None), CacheNeed(CacheSpec("full", (8,), tensors=1, page_size=3), None, None)]
+    cache = CacheManager(needs, 4, [rng.randrange(8, 14), rng.randrange(10, 18)], 4, torch.float32, "cpu", allocate=False)
+    sched = Scheduler(cache, 4, 12, 6, 1000, (), False)
+    seqs = [Sequence(i, [1] * rng.randrange(1, 24), rng.randrange(1, 9)) for i in range(20)]
+    sched.add_sequences(seqs)
+    tight = [0, 0]
+    while not sched.is_done():
+        work = sched.plan()
+        assert work, "unfinished requests, no work"
+        free = cache.free_pages()
+        sched.process_results(work, fake_step(cache, work))
+        for g in range(2):
+            tight[g] += cache.groups[g].pool.num_free == 0 or free[g] == 0
+    assert len(sched.completed) == 20
+    for s in sched.completed:
+        if s.status is Status.COMPLETE and s.finish_reason == "length":
+            assert len(s.output_ids) == s.max_new_tokens
+        else:
+            needs_pages = cache.peak_pages(s.prompt_len + 1, 1)
+            assert s.status is Status.FAILED or s.finish_reason == "cache"
+            assert any(n > g.pool.num_pages for n, g in zip(needs_pages, cache.groups)) or s.finish_reason == "cache"
+    assert cache.free_pages() == [g.pool.num_pages for g in cache.groups]
     cache.check_invariants()

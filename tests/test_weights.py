@@ -88,7 +88,15 @@ def test_tied_head_and_missing_files(tmp_path):
     tensors = random_weights(specs, 1, torch.float32, "cpu")
     tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()     # some checkpoints store it anyway
     write_safetensors(tmp_path / "model.safetensors", tensors.items())
-    load_weights(tmp_path, specs, torch.float32, "cpu", ignore_names=model.spec.ignore_names)
+    load_weights(tmp_path, specs, torch.float32, "cpu", must_equal=model.spec.must_equal)
+    # ... but a stored head that is not the embedding contradicts tie_word_embeddings: an error, not a choice
+    other = tmp_path / "unequal"
+    other.mkdir()
+    tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"] + 1e-3
+    write_safetensors(other / "model.safetensors", tensors.items())
+    with pytest.raises(WeightsError, match="lm_head.weight differs from model.embed_tokens.weight") as err:
+        load_weights(other, specs, torch.float32, "cpu", must_equal=model.spec.must_equal)
+    assert err.value.unequal == [("lm_head.weight", "model.embed_tokens.weight")]
     with pytest.raises(FileNotFoundError):
         load_weights(tmp_path / "nowhere", specs, torch.float32, "cpu")
     untied, uspecs = _specs(H.TINY_A)
