@@ -16,6 +16,11 @@
 //            partial tile in its own shared memory and, after a cluster barrier, adds up its share of the tokens
 //            over all slices, in slice order, reading the peers through distributed shared memory.
 //
+// Epilogues of the weights-on-rows arrangement: plain store; silu(gate) * up for the fused gate/up projection; and,
+// for the fused q/k/v projection of an attention layer whose head size is the tile's 128 rows, rotary encoding of
+// the q and k heads (angle in float64, rotation in float32, on the float32 accumulators) with k and v written
+// straight into their cache pages: one kernel instead of three, and one rounding to bfloat16 instead of two.
+//
 // Every wait on an mbarrier is bounded: when it runs out the CTA records a code in `status`, stops issuing work,
 // gives its TMEM back and returns.
 #include "common.cuh"
@@ -42,7 +47,23 @@ struct GemmParams {
   int stages;
   int glu;               // rows of W come in groups of 128 = 64 gate rows + their 64 up rows; C[M, N/2] = silu(gate) * up
   int prefetch_kb;       // K blocks of weights (beyond the stages) to pull into the L2 before waiting on the predecessor
+  // fused q/k/v projection (rope_freq != nullptr): tile t of W is head t (q heads, then k heads, then v heads)
+  const float* rope_freq;    // [2][64] frequencies as two floats each (see elementwise.cu, rope_sincos)
+  const int* positions;      // [M]
+  const int* tok_entry;      // [M]
+  const int* kv_indptr;      // block tables of the step, CSR
+  const int* kv_indices;
+  __nv_bfloat16* cache;      // this layer's pages [page][k|v][Hkv][page_size][128]
+  int Hq, Hkv, page_size, interleaved, write_kv;
 };
+
+// cos and sin of position * frequency j, the angle formed and reduced to [-pi, pi] in float64 (as elementwise.cu).
+__device__ __forceinline__ void rope_sincos64(int pos, const float* __restrict__ freq, int j, float* s, float* c) {
+  const double f = (double)freq[j] + (double)freq[64 + j];
+  double a = (double)pos * f;
+  a -= 6.283185307179586476925286766559 * rint(a * 0.15915494309189533576888376337251);
+  sincosf((float)a, s, c);
+}
 
 __device__ __forceinline__ void store_out(void* C, int out_f32, size_t idx, float v) {
   if (out_f32) reinterpret_cast<float*>(C)[idx] = v;
@@ -208,7 +229,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (n0 + j < p.N) store_out(p.C, p.out_f32, base + j, __uint_as_float(v[j]));
             }
           }
-        } else if (p.splits == 1 && !p.glu) {
+        } else if (p.splits == 1 && !p.glu && p.rope_freq == nullptr) {
           // rows = outputs (ra < N), columns = tokens: consecutive lanes write consecutive outputs of one token
           if (ra < p.N) {
 #pragma unroll
@@ -225,7 +246,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     }
   }
-  if (p.swap && (p.splits > 1 || p.glu)) {
+  if (p.swap && (p.splits > 1 || p.glu || p.rope_freq != nullptr)) {
     // join the K slices inside the cluster: CTA r adds tokens r, r + splits, ... over all slices in slice order
     tc_fence_before();
     __syncthreads();
@@ -265,18 +286,64 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
             }
           }
+          float res[4];
 #pragma unroll
           for (int t = 0; t < 4; ++t) {
-            if (!live[t]) continue;
             float acc = 0.f, acc_u = 0.f;
+            if (live[t]) {
 #pragma unroll
-            for (int s = 0; s < 8; ++s)
-              if (s < p.splits) {                          // slice order
-                acc += v[t][s];
-                if (p.glu) acc_u += u[t][s];
+              for (int s = 0; s < 8; ++s)
+                if (s < p.splits) {                          // slice order
+                  acc += v[t][s];
+                  if (p.glu) acc_u += u[t][s];
+                }
+              if (p.glu) acc = acc / (1.f + expf(-acc)) * acc_u;
+            }
+            res[t] = acc;
+          }
+          if (p.rope_freq == nullptr) {
+#pragma unroll
+            for (int t = 0; t < 4; ++t)
+              if (live[t])
+                store_out(p.C, p.out_f32, (size_t)(tile_b * p.bn + j0 + t * p.splits) * n_out + ra, res[t]);
+          } else {
+            // This tile is one head (128 rows): thread `row` holds dim `row` of the head for up to four tokens
+            // and needs its rotary partner's value, which another thread of this CTA holds.  All 128 threads of
+            // the four epilogue warps get here (N is a multiple of 128), so they can meet at a named barrier.
+            float* xchg = part + (size_t)p.bn * TM;                 // [4][128], behind the partial tile
+            const int head = tile_a;
+            const bool is_v = head >= p.Hq + p.Hkv;
+#pragma unroll
+            for (int t = 0; t < 4; ++t) xchg[t * TM + row] = res[t];
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int partner = p.interleaved ? (row ^ 1) : (row ^ 64);
+            const bool first = p.interleaved ? ((row & 1) == 0) : (row < 64);
+            const int fj = p.interleaved ? (row >> 1) : (row & 63);
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              if (!live[t]) continue;
+              const int tok = tile_b * p.bn + j0 + t * p.splits;
+              const int pos = p.positions[tok];
+              float val = res[t];
+              if (!is_v) {
+                float sn, cs;
+                rope_sincos64(pos, p.rope_freq, fj, &sn, &cs);
+                const float other = xchg[t * TM + partner];
+                val = first ? res[t] * cs - other * sn : other * sn + res[t] * cs;
               }
-            if (p.glu) acc = acc / (1.f + expf(-acc)) * acc_u;
-            store_out(p.C, p.out_f32, (size_t)(tile_b * p.bn + j0 + t * p.splits) * n_out + ra, acc);
+              const __nv_bfloat16 b = __float2bfloat16_rn(val);
+              if (head < p.Hq) {
+                reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)tok * p.N + ra] = b;
+              } else if (p.write_kv) {
+                const int e = p.tok_entry[tok];
+                const long long page = p.kv_indices[p.kv_indptr[e] + pos / p.page_size];
+                const int kvh = is_v ? head - p.Hq - p.Hkv : head - p.Hq;
+                const size_t at = (((size_t)page * 2 + (is_v ? 1 : 0)) * p.Hkv + kvh) * p.page_size * TM +
+                                  (size_t)(pos % p.page_size) * TM + row;
+                p.cache[at] = b;
+              }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");         // before the next four tokens reuse xchg
           }
         }
       }
@@ -348,11 +415,18 @@ BSPEC_API long long bspec_gemm_tc_plan(int M, int N, int K, int sm_count, int* p
   return 0;
 }
 
-// C = X W^T.  `status`: one int on the device, 0 unless a bounded wait ran out.
-// glu != 0: the rows of W come in groups of 128 (64 gate rows, then the 64 matching up rows; N a multiple of 128) and
-// C is [M, N/2] = silu(gate) * up.
-BSPEC_API int bspec_gemm_tc(const void* X, const void* W, void* C, int M, int N, int K, int out_f32, int glu,
-                            int* status, int sm_count, cudaStream_t stream) {
+struct RopeEpilogue {
+  const float* freq;
+  const int* positions;
+  const int* tok_entry;
+  const int* kv_indptr;
+  const int* kv_indices;
+  void* cache;
+  int Hq, Hkv, page_size, interleaved, write_kv;
+};
+
+static int launch_gemm(const void* X, const void* W, void* C, int M, int N, int K, int out_f32, int glu, int* status,
+                       int sm_count, const RopeEpilogue* rope, cudaStream_t stream) {
   int plan[5];
   if (bspec_gemm_tc_plan(M, N, K, sm_count, plan) < 0) return (int)cudaErrorInvalidValue;
   if (glu && (N % 128 != 0)) return (int)cudaErrorInvalidValue;
@@ -361,6 +435,19 @@ BSPEC_API int bspec_gemm_tc(const void* X, const void* W, void* C, int M, int N,
   p.C = C; p.status = status;
   p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.glu = glu ? 1 : 0;
   p.swap = plan[0]; p.bn = plan[1]; p.splits = plan[2]; p.stages = plan[3];
+  p.rope_freq = nullptr; p.positions = p.tok_entry = p.kv_indptr = p.kv_indices = nullptr; p.cache = nullptr;
+  p.Hq = p.Hkv = p.page_size = p.interleaved = p.write_kv = 0;
+  if (rope != nullptr) {
+    // one 128-row tile per head, on the weights-on-rows arrangement, bfloat16 out, room behind the partial tile
+    const int stage_bytes = TM * BK * 2 + ((p.bn * BK * 2 + 1023) & ~1023);
+    if (!p.swap || glu || out_f32 || N != (rope->Hq + 2 * rope->Hkv) * TM || rope->page_size < 1 ||
+        (size_t)(p.bn + 4) * TM * 4 > (size_t)p.stages * stage_bytes)
+      return (int)cudaErrorInvalidValue;
+    p.rope_freq = rope->freq; p.positions = rope->positions; p.tok_entry = rope->tok_entry;
+    p.kv_indptr = rope->kv_indptr; p.kv_indices = rope->kv_indices; p.cache = (__nv_bfloat16*)rope->cache;
+    p.Hq = rope->Hq; p.Hkv = rope->Hkv; p.page_size = rope->page_size; p.interleaved = rope->interleaved;
+    p.write_kv = rope->write_kv;
+  }
   const int kb_total = (K + BK - 1) / BK;
   p.kblocks_per_split = (kb_total + p.splits - 1) / p.splits;
   {
@@ -404,6 +491,29 @@ BSPEC_API int bspec_gemm_tc(const void* X, const void* W, void* C, int M, int N,
   const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel, map_a, map_b, p);
   if (e != cudaSuccess) return (int)e;
   return BSPEC_LAUNCH_CHECK();
+}
+
+// C = X W^T.  `status`: one int on the device, 0 unless a bounded wait ran out.
+// glu != 0: the rows of W come in groups of 128 (64 gate rows, then the 64 matching up rows; N a multiple of 128) and
+// C is [M, N/2] = silu(gate) * up.
+BSPEC_API int bspec_gemm_tc(const void* X, const void* W, void* C, int M, int N, int K, int out_f32, int glu,
+                            int* status, int sm_count, cudaStream_t stream) {
+  return launch_gemm(X, W, C, M, N, K, out_f32, glu, status, sm_count, nullptr, stream);
+}
+
+// The fused q/k/v projection of an attention layer with head size 128 for a step of at most 128 tokens:
+// W = [Wq; Wk; Wv] with Hq + 2 Hkv heads of 128 rows, C [M, N] bfloat16.  The q heads are rotated and stored to C
+// (the k and v columns of C are left untouched); the k heads are rotated and, with the v heads, written into the
+// cache page of each token's position (`write_kv` 0: not written).  freq: [2][64] float (leading parts, then
+// remainders, of the 64 frequencies); pairing (j, j + 64), or (2j, 2j + 1) with `interleaved`.
+// Returns cudaErrorInvalidValue for sizes this epilogue does not take; nothing is launched then.
+BSPEC_API int bspec_gemm_tc_qkv_rope(const void* X, const void* W, void* C, int M, int N, int K, int* status, int sm_count,
+                                     const float* freq, const int* positions, const int* tok_entry,
+                                     const int* kv_indptr, const int* kv_indices, void* cache, int Hq, int Hkv,
+                                     int page_size, int interleaved, int write_kv, cudaStream_t stream) {
+  const RopeEpilogue rope = {freq, positions, tok_entry, kv_indptr, kv_indices, cache, Hq, Hkv, page_size,
+                             interleaved, write_kv};
+  return launch_gemm(X, W, C, M, N, K, 0, 0, status, sm_count, &rope, stream);
 }
 
 // Switch programmatic dependent launch on (default) or off for every kernel of this library.

@@ -12,7 +12,7 @@ mode can slip in.
 from __future__ import annotations
 
 import ctypes
-import os
+import sys
 import threading
 from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
 from typing import Optional
@@ -53,9 +53,8 @@ _SIGNATURES = {
                              c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "bspec_gemm_tc_plan": [c_int, c_int, c_int, c_int, c_void_p],
     "bspec_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
-    "bspec_gemm_stream_plan": [c_int, c_int, c_int, c_int, c_void_p],
-    "bspec_gemm_stream": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                          c_int, c_void_p],
+    "bspec_gemm_tc_qkv_rope": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                               c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "bspec_attention_prefill_tc": [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                                    c_void_p],
@@ -81,16 +80,10 @@ def load_library():
         for name, argtypes in _SIGNATURES.items():
             fn = getattr(lib, name)
             fn.argtypes = argtypes
-            fn.restype = c_longlong if name in ("bspec_gemm_tc_plan", "bspec_gemm_stream_plan") else c_int
+            fn.restype = c_longlong if name == "bspec_gemm_tc_plan" else c_int
         _lib = lib
-        if os.environ.get("BSPEC_PDL", "1") == "0":
-            set_pdl(False)
-        if os.environ.get("BSPEC_GEMM_CTAS_PER_SM"):
-            lib.bspec_gemm_stream_ctas_per_sm.argtypes = [c_int]
-            lib.bspec_gemm_stream_ctas_per_sm(int(os.environ["BSPEC_GEMM_CTAS_PER_SM"]))
-        if os.environ.get("BSPEC_GEMM_SPLITS"):
-            lib.bspec_gemm_tc_force_splits.argtypes = [c_int]
-            lib.bspec_gemm_tc_force_splits(int(os.environ["BSPEC_GEMM_SPLITS"]))
+        from . import debug
+        debug.apply_environment(sys.modules[__name__], lib)
     return _lib
 
 
@@ -103,8 +96,7 @@ def set_pdl(on: bool) -> None:
 
 
 _TRACE_SETTERS = ["bspec_trace_set_attention_tcgen05", "bspec_trace_set_elementwise", "bspec_trace_set_attention_generic", "bspec_trace_set_attention_bf16",
-                  "bspec_trace_set_gemm_fp32", "bspec_trace_set_sampling", "bspec_trace_set_gemm_tcgen05",
-                  "bspec_trace_set_gemm_stream"]
+                  "bspec_trace_set_gemm_fp32", "bspec_trace_set_sampling", "bspec_trace_set_gemm_tcgen05"]
 TRACE_KERNEL_NAMES = {1: "embed", 2: "add_rmsnorm", 3: "gather_rows_add", 4: "silu_mul", 5: "rope_kv_append",
                       6: "rope_inplace", 7: "attn_generic", 8: "attn_decode", 9: "attn_prefill", 10: "sgemm",
                       11: "sample_threshold", 12: "sample_pick", 13: "sample_final", 20: "gemm_tcgen05", 30: "attn_prefill_tc"}
@@ -204,7 +196,7 @@ def gather_rows_add(resid: torch.Tensor, pending: Optional[torch.Tensor], rows: 
                                                 out.shape[0], out.shape[1], _stream()), "gather_rows_add")
 
 
-GLU_FUSION = os.environ.get("BSPEC_GLU_FUSION", "1") != "0"
+GLU_FUSION = True
 GLU_GROUP = 64     # gate/up interleave of weights prepared for the fused-epilogue GEMM: 64 gate rows, 64 up rows
 
 
@@ -233,8 +225,6 @@ def linear_glu(x: torch.Tensor, w13: torch.Tensor, group: int = GLU_GROUP) -> to
     inter = N // 2
     if (GLU_FUSION and x.dtype == torch.bfloat16 and K % 8 == 0 and M > 0 and group == GLU_GROUP
             and x.is_contiguous() and (TC_GEMM == "all" or (TC_GEMM == "auto" and M <= TC_GEMM_MAX_M))):
-        if STREAM_GEMM and M <= STREAM_GEMM_MAX_M and N % 128 == 0 and w13.is_contiguous():
-            return gemm_stream(x, w13, x.dtype, glu=True)
         out = torch.empty((M, inter), dtype=x.dtype, device=x.device)
         _check(load_library().bspec_gemm_tc(x.data_ptr(), w13.data_ptr(), out.data_ptr(), M, N, K, 0, 1,
                                             _status_word(x.device).data_ptr(), sm_count(x.device), _stream()), "gemm_tc_glu")
@@ -292,9 +282,10 @@ def rope_inplace(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tenso
 
 # ---------------------------------------------------------------------------- attention
 
-USE_TMA_ATTENTION = os.environ.get("BSPEC_TMA_ATTENTION", "1") != "0"
-USE_TC_ATTENTION = os.environ.get("BSPEC_TC_ATTENTION", "1") != "0"    # tcgen05 kernel for long prompt portions
-BALANCED_ATTENTION = os.environ.get("BSPEC_BALANCED_ATTENTION", "1") != "0"   # equal chunks over a fixed grid for decode
+# Which attention kernels may run; tests switch these to compare kernels with each other (see also kernels/debug.py)
+USE_TMA_ATTENTION = True
+USE_TC_ATTENTION = True         # tcgen05 kernel for long prompt portions
+BALANCED_ATTENTION = True       # equal shares of key tiles over a fixed grid for decode
 FORCE_GENERIC_ATTENTION = False      # tests set this to compare the tensor-core kernels with the generic one
 _sm_counts = {}
 
@@ -430,8 +421,8 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, c
 # on the accumulator rows, K slices joined inside a cluster, the gate/up activation in its epilogue, weight tiles
 # fetched before the wait on the kernel before) beats the vendor library by 2 to 12 %; from 16 tokens on the library
 # wins, by 1 to 15 % (the join of the slices grows with the tokens), so larger steps go to the library.
-TC_GEMM = os.environ.get("BSPEC_TC_GEMM", "auto")
-TC_GEMM_MAX_M = int(os.environ.get("BSPEC_TC_GEMM_MAX_M", "8"))
+TC_GEMM = "auto"
+TC_GEMM_MAX_M = 8
 _status = {}
 
 
@@ -450,7 +441,7 @@ def _raise_status(dev, code: int) -> None:
     raise KernelError(f"a kernel on {dev} gave up a bounded wait (code {code}: GEMM 1 = stage never freed, "
                       f"2 = operands never arrived, 3 = accumulator never completed; decode attention 11/13 = stage "
                       f"never freed, 12/14 = keys never arrived; prompt attention 21/22 the same, 31-38 = a role of "
-                      f"the tensor-core prompt kernel; 41-45 = the equal-shares GEMM).  The results of the steps "
+                      f"the tensor-core prompt kernel).  The results of the steps "
                       f"since the last check are not valid.")
 
 
@@ -486,46 +477,6 @@ def raise_if_gave_up() -> None:
             _raise_status(dev, code)
 
 
-# BSPEC_STREAM_GEMM=1 sends decode-sized products (at most STREAM_GEMM_MAX_M tokens) to the kernel that gives every
-# CTA an equal share of the weights' (tile, K block) units instead of the one-tile-per-CTA kernel.  Measured on
-# B200 it streams the weights at the memory's rate but pays more for joining the tiles that CTAs share (a fence,
-# an atomic and a read of the partial tiles in global memory against a cluster barrier and distributed shared
-# memory): 1 to 6 % slower per decode step of 1B to 8B models at 8 to 64 requests.  Off by default.
-STREAM_GEMM = os.environ.get("BSPEC_STREAM_GEMM", "0") != "0"
-STREAM_GEMM_MAX_M = 128
-_stream_scratch = {}
-
-
-def _stream_buffers(device, scratch_bytes: int, tiles: int):
-    """Scratch for partial tiles and the zeroed tile counters.  Buffers only grow, and the old ones stay alive:
-    a captured graph may still point at them."""
-    bufs = _stream_scratch.setdefault(device, {"scratch": [], "counters": []})
-    if not bufs["scratch"] or bufs["scratch"][-1].numel() * 4 < scratch_bytes:
-        bufs["scratch"].append(torch.empty((max(scratch_bytes // 4, 1 << 20),), dtype=torch.float32, device=device))
-    if not bufs["counters"] or bufs["counters"][-1].numel() < 2 * tiles:
-        bufs["counters"].append(torch.zeros((max(2 * tiles, 8192),), dtype=torch.int32, device=device))
-    return bufs["scratch"][-1], bufs["counters"][-1]
-
-
-def gemm_stream(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, glu: bool = False) -> torch.Tensor:
-    """x [M <= 128, K] @ w[N, K]^T on the equal-shares tcgen05 kernel (bfloat16 operands, float32 accumulation);
-    ``glu``: w interleaved by ``interleave_gate_up``, result silu(gate) * up of width N / 2."""
-    lib = load_library()
-    M, K = x.shape
-    N = w.shape[0]
-    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
-    plan = (c_int * 4)()
-    need = lib.bspec_gemm_stream_plan(M, N, K, sm_count(x.device), plan)
-    if need < 0 or (glu and N % 128 != 0):
-        raise KernelError(f"gemm_stream: sizes M={M} N={N} K={K} are not supported (M <= 128, K a multiple of 8)")
-    scratch, counters = _stream_buffers(x.device, need, plan[3])
-    out = torch.empty((M, N // 2 if glu else N), dtype=out_dtype, device=x.device)
-    _check(lib.bspec_gemm_stream(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, int(out_dtype == torch.float32),
-                                 int(glu), scratch.data_ptr(), counters.data_ptr(), _status_word(x.device).data_ptr(),
-                                 sm_count(x.device), _stream()), "gemm_stream")
-    return out
-
-
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """x [M, K] @ w[N, K]^T on the tcgen05 kernel (bfloat16 operands, float32 accumulation)."""
     lib = load_library()
@@ -537,6 +488,36 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.T
     out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     _check(lib.bspec_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, int(out_dtype == torch.float32), 0,
                              _status_word(x.device).data_ptr(), sm_count(x.device), _stream()), "gemm_tc")
+    return out
+
+
+FUSE_QKV_ROPE = True       # decode-sized steps: rotary encoding and the cache append in the q/k/v product's epilogue
+
+
+def linear_qkv_rope(x: torch.Tensor, wqkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                    inv_freq: torch.Tensor, rotary_dim: int, interleaved: bool, positions: torch.Tensor,
+                    tok_entry: torch.Tensor, kv_indptr: torch.Tensor, kv_indices: torch.Tensor, cache: torch.Tensor,
+                    page_size: int, write_kv: bool = True) -> Optional[torch.Tensor]:
+    """x [M, K] @ [Wq; Wk; Wv]^T with the rotary encoding of q and k and the write of k and v into their cache
+    pages done in the product's epilogue, for bfloat16 steps of at most ``TC_GEMM_MAX_M`` tokens and heads of
+    128 rotated over their whole width.  Returns [M, (Hq + 2 Hkv) * 128] whose q columns hold the rotated queries
+    (its k and v columns are not written), or None when the sizes are not these: the caller then runs the product,
+    ``rope_kv_append`` and so on one after the other."""
+    M, K = x.shape
+    N = wqkv.shape[0]
+    if not (FUSE_QKV_ROPE and TC_GEMM != "none" and x.dtype == torch.bfloat16
+            and cache.dtype == torch.bfloat16 and head_dim == 128 and rotary_dim == 128 and 0 < M <= TC_GEMM_MAX_M
+            and K % 8 == 0 and N == (n_heads + 2 * n_kv_heads) * 128 and x.is_contiguous() and wqkv.is_contiguous()):
+        return None
+    _require_cuda(x, wqkv, cache, positions)
+    assert inv_freq.dtype == torch.float32 and inv_freq.shape == (2, 64) and inv_freq.is_contiguous()
+    assert cache.is_contiguous() and positions.dtype == torch.int32 and tok_entry.dtype == torch.int32
+    out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    _check(load_library().bspec_gemm_tc_qkv_rope(
+        x.data_ptr(), wqkv.data_ptr(), out.data_ptr(), M, N, K, _status_word(x.device).data_ptr(), sm_count(x.device),
+        inv_freq.data_ptr(), positions.data_ptr(), tok_entry.data_ptr(), kv_indptr.data_ptr(), kv_indices.data_ptr(),
+        cache.data_ptr(), n_heads, n_kv_heads, int(page_size), int(bool(interleaved)), int(bool(write_kv)), _stream()),
+        "gemm_tc_qkv_rope")
     return out
 
 
@@ -555,8 +536,6 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
         return out
     if (K % 8 == 0 and M > 0 and x.is_contiguous() and w.is_contiguous()
             and (TC_GEMM == "all" or (TC_GEMM == "auto" and M <= TC_GEMM_MAX_M))):
-        if STREAM_GEMM and M <= STREAM_GEMM_MAX_M:
-            return gemm_stream(x, w, out_dtype)
         return gemm_tc(x, w, out_dtype)
     if out_dtype == x.dtype:
         return torch.mm(x, w.t())

@@ -56,21 +56,29 @@ class Attention(Mixer):
     def forward(self, x, ctx, cache):
         n = x.shape[0]
         Hq, Hkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
-        with bucket("attn.qkv_proj"):
-            qkv = ops.linear(x, self.wqkv)
         tables = ctx.tables[cache.group]
         table = self.position.rope_table()
-        if table is None:
-            q = qkv[:, :Hq * hd].view(n, Hq, hd)
-            k = qkv[:, Hq * hd:(Hq + Hkv) * hd].view(n, Hkv, hd)
-            self.position.apply(q, k, ctx)
-            inv_freq, rotary_dim, interleaved = None, 0, False
-        else:
-            inv_freq, rotary_dim, interleaved = table
-        with bucket("attn.rope"):
-            ops.rope_kv_append(qkv, Hq, Hkv, hd, inv_freq, rotary_dim, interleaved, ctx.positions, ctx.tok_entry,
-                               tables.kv_indptr, tables.kv_indices, cache.kv, tables.page_size,
-                               write_kv=cache.owner)
+        qkv = None
+        if table is not None:
+            # decode-sized bfloat16 steps with heads of 128: one kernel projects, rotates and appends to the cache
+            with bucket("attn.qkv_proj"):
+                qkv = ops.linear_qkv_rope(x, self.wqkv, Hq, Hkv, hd, table[0], table[1], table[2], ctx.positions,
+                                          ctx.tok_entry, tables.kv_indptr, tables.kv_indices, cache.kv,
+                                          tables.page_size, write_kv=cache.owner)
+        if qkv is None:
+            with bucket("attn.qkv_proj"):
+                qkv = ops.linear(x, self.wqkv)
+            if table is None:
+                q = qkv[:, :Hq * hd].view(n, Hq, hd)
+                k = qkv[:, Hq * hd:(Hq + Hkv) * hd].view(n, Hkv, hd)
+                self.position.apply(q, k, ctx)
+                inv_freq, rotary_dim, interleaved = None, 0, False
+            else:
+                inv_freq, rotary_dim, interleaved = table
+            with bucket("attn.rope"):
+                ops.rope_kv_append(qkv, Hq, Hkv, hd, inv_freq, rotary_dim, interleaved, ctx.positions, ctx.tok_entry,
+                                   tables.kv_indptr, tables.kv_indices, cache.kv, tables.page_size,
+                                   write_kv=cache.owner)
         out = torch.empty((n, Hq * hd), dtype=x.dtype, device=x.device)
         with bucket("attn.compute"):
             ops.paged_attention(qkv, out, cache.kv, ctx, tables, Hq, Hkv, hd, self.scale, self.window)

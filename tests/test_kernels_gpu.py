@@ -158,6 +158,77 @@ def test_rope_and_cache_append(ops, dtype, Hq, Hkv, hd, rot, inter, ps, lens):
     assert torch.equal(alone[:, :Hq * hd], work[:, :Hq * hd])
 
 
+@pytest.mark.parametrize("inter", [False, True])
+@pytest.mark.parametrize("M,Hq,Hkv,K", [(1, 32, 8, 4096), (8, 32, 8, 4096), (3, 5, 1, 512), (7, 4, 2, 328), (8, 24, 8, 3072)])
+def test_qkv_projection_with_rope_and_cache_append_in_its_epilogue(ops, M, Hq, Hkv, K, inter):
+    """The fused kernel of decode-sized steps against float64 arithmetic: rotated q in the output, rotated k and
+    plain v in the right rows of the right pages, nothing else in the cache touched; one K slice and several."""
+    hd, ps = 128, 16
+    g = torch.Generator(device=DEV).manual_seed(M + Hq)
+    N = (Hq + 2 * Hkv) * hd
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) / math.sqrt(K)).bfloat16()
+    import plain_llama as P
+    freqs = P.rope_frequencies(dict(head_dim=hd, rope_theta=500000.0, hidden_size=Hq * hd, num_attention_heads=Hq,
+                                    rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0,
+                                                      high_freq_factor=4.0, original_max_position_embeddings=8192)))
+    table = ops.rope_frequency_table(freqs, DEV)
+    kv_before = [5, 130, 31, 64, 1000, 15, 16, 99999][:M]          # one new token per request, at these positions
+    positions = torch.tensor(kv_before, dtype=torch.int32, device=DEV)
+    ent = torch.arange(M, dtype=torch.int32, device=DEV)
+    pages_per = [-(-(b + 1) // ps) for b in kv_before]
+    # a table as long as each request, whose last entry is the request's own page (the only one written)
+    indptr = torch.tensor([0] + list(np.cumsum(pages_per)), dtype=torch.int32, device=DEV)
+    indices = torch.zeros(sum(pages_per), dtype=torch.int32)
+    own = torch.randperm(M + 2, generator=torch.Generator().manual_seed(9))[:M] + 1
+    for e in range(M):
+        indices[int(indptr[e + 1]) - 1] = own[e]
+    indices = indices.to(DEV)
+    cache = torch.full((M + 3, 2, Hkv, ps, hd), 7.0, device=DEV, dtype=torch.bfloat16)
+    got = ops.linear_qkv_rope(x, w, Hq, Hkv, hd, table, hd, inter, positions, ent, indptr, indices, cache, ps)
+    assert got is not None, "these sizes are the fused kernel's"
+    torch.cuda.synchronize()
+    ops.check_status()
+    qkv = (x.double() @ w.double().T).cpu()
+    ang = positions.cpu().double()[:, None] * freqs[None, :]
+    c, s_ = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+
+    def rotate(t):
+        out = torch.empty_like(t)
+        if inter:
+            a, b = t[..., 0::2], t[..., 1::2]
+            out[..., 0::2], out[..., 1::2] = a * c - b * s_, a * s_ + b * c
+        else:
+            a, b = t[..., :hd // 2], t[..., hd // 2:]
+            out[..., :hd // 2], out[..., hd // 2:] = a * c - b * s_, a * s_ + b * c
+        return out
+
+    want_q = rotate(qkv[:, :Hq * hd].view(M, Hq, hd))
+    want_k = rotate(qkv[:, Hq * hd:(Hq + Hkv) * hd].view(M, Hkv, hd))
+    want_v = qkv[:, (Hq + Hkv) * hd:].view(M, Hkv, hd)
+    tol = dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(got[:, :Hq * hd].view(M, Hq, hd).double().cpu(), want_q, **tol)
+    touched = torch.zeros(M + 3, ps, dtype=torch.bool)
+    for e in range(M):
+        page, row = int(own[e]), kv_before[e] % ps
+        touched[page, row] = True
+        torch.testing.assert_close(cache[page, 0, :, row].double().cpu(), want_k[e], **tol)
+        torch.testing.assert_close(cache[page, 1, :, row].double().cpu(), want_v[e], **tol)
+    untouched = cache.cpu().permute(0, 3, 1, 2, 4)[~touched]
+    assert bool((untouched == 7.0).all()), "only the new tokens' rows are written"
+    # a run that only reads the cache (a layer that shares another layer's) writes nothing
+    cache2 = torch.full_like(cache, 7.0)
+    got2 = ops.linear_qkv_rope(x, w, Hq, Hkv, hd, table, hd, inter, positions, ent, indptr, indices, cache2, ps,
+                               write_kv=False)
+    assert torch.equal(got2[:, :Hq * hd], got[:, :Hq * hd]) and bool((cache2 == 7.0).all())
+    # and it agrees with the three kernels it replaces
+    plain = ops.linear(x, w)
+    cache3 = torch.full_like(cache, 7.0)
+    ops.rope_kv_append(plain, Hq, Hkv, hd, table, hd, inter, positions, ent, indptr, indices, cache3, ps)
+    torch.testing.assert_close(got[:, :Hq * hd].float(), plain[:, :Hq * hd].float(), **tol)
+    torch.testing.assert_close(cache.float(), cache3.float(), **tol)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("inter", [False, True])
 @pytest.mark.parametrize("n", [9, 80])                 # the per-head kernel; the 16-byte bfloat16 kernel (n >= 64)
@@ -587,50 +658,6 @@ def test_gate_up_gemm_with_the_activation_in_its_epilogue(ops, M, I, K):
         finally:
             ops.TC_GEMM = old
     ops.check_status()
-
-
-STREAM_SHAPES = [
-    # M <= 128, N, K: one tile, tiles cut between CTAs, ragged edges, many tiles, long K
-    (1, 128, 64), (8, 6144, 4096), (3, 200, 72), (16, 1000, 264), (17, 333, 1024), (64, 4096, 14336),
-    (100, 130, 520), (128, 256, 128), (48, 5120, 3072), (8, 100000, 256), (128, 3072, 8192), (2, 128, 16384),
-]
-
-
-@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("M,N,K", STREAM_SHAPES)
-def test_equal_shares_gemm(ops, M, N, K, out_dtype):
-    g = torch.Generator(device=DEV).manual_seed(M * 7 + N)
-    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
-    w = (torch.randn(N, K, device=DEV, generator=g) / K ** 0.5).bfloat16()
-    got = ops.gemm_stream(x, w, out_dtype)
-    torch.cuda.synchronize()
-    ops.check_status()
-    want = x.float() @ w.float().T
-    if out_dtype == torch.float32:
-        torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-4)
-    else:
-        torch.testing.assert_close(got.float(), want.bfloat16().float(), rtol=2e-2, atol=2e-2)
-    again = ops.gemm_stream(x, w, out_dtype)          # the tile counters were left at zero, the sums keep their order
-    assert torch.equal(got, again)
-    ops.check_status()
-
-
-@pytest.mark.parametrize("M,I,K", [(1, 64, 64), (8, 14336, 4096), (5, 192, 72), (64, 256, 96), (128, 128, 264),
-                                   (48, 8192, 3072), (100, 1088, 520)])
-def test_equal_shares_gate_up_gemm(ops, M, I, K):
-    g = torch.Generator(device=DEV).manual_seed(M + I)
-    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
-    wg = (torch.randn(I, K, device=DEV, generator=g) / K ** 0.5).bfloat16()
-    wu = (torch.randn(I, K, device=DEV, generator=g) / K ** 0.5).bfloat16()
-    w13 = ops.interleave_gate_up(wg, wu)
-    got = ops.gemm_stream(x, w13, torch.bfloat16, glu=True)
-    torch.cuda.synchronize()
-    ops.check_status()
-    gate, up = x.float() @ wg.float().T, x.float() @ wu.float().T
-    want = gate * torch.sigmoid(gate) * up
-    assert got.shape == (M, I)
-    torch.testing.assert_close(got.float(), want, rtol=3e-2, atol=3e-2)
-    assert torch.equal(got, ops.gemm_stream(x, w13, torch.bfloat16, glu=True))
 
 
 def test_silu_mul_layouts(ops):
