@@ -45,7 +45,7 @@ struct GemmParams {
   int splits;
   int kblocks_per_split;
   int stages;
-  int glu;               // rows of W come in groups of 128 = 64 gate rows + their 64 up rows; C[M, N/2] = silu(gate) * up
+  int glu;               // rows of W come in groups of 16 = 8 gate rows + their 8 up rows; C[M, N/2] = silu(gate) * up
   int prefetch_kb;       // K blocks of weights (beyond the stages) to pull into the L2 before waiting on the predecessor
   // fused q/k/v projection (rope_freq != nullptr): tile t of W is head t (q heads, then k heads, then v heads)
   const float* rope_freq;    // [2][64] frequencies as two floats each (see elementwise.cu, rope_sincos)
@@ -191,22 +191,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tc_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
         tc_wait_ld();
         if (!p.swap && p.glu) {
-          // rows = tokens, columns = outputs in groups of 64 gate + 64 up: this chunk of gate columns and its partner
-          if ((c0 & 64) == 0) {
-            uint32_t vu[16];
-            tc_ld16(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c0 + 64), vu);
-            tc_wait_ld();
-            const int n0 = tile_b * p.bn + c0;                       // gate column; output column below
-            const int o0 = (n0 >> 7) * 64 + (n0 & 63);
-            if (ra < p.M) {
+          // rows = tokens, columns = outputs in groups of 8 gate + 8 up: this chunk of 16 holds 8 outputs whole
+          const int n0 = tile_b * p.bn + c0;                         // gate column; output column n0 / 2
+          if (ra < p.M) {
 #pragma unroll
-              for (int j = 0; j < 16; ++j)
-                if (n0 + j < p.N) {
-                  const float gte = __uint_as_float(v[j]);
-                  store_out(p.C, p.out_f32, (size_t)ra * (p.N / 2) + o0 + j,
-                            gte / (1.f + expf(-gte)) * __uint_as_float(vu[j]));
-                }
-            }
+            for (int j = 0; j < 8; ++j)
+              if (n0 + 8 + j < p.N) {
+                const float gte = __uint_as_float(v[j]);
+                store_out(p.C, p.out_f32, (size_t)ra * (p.N / 2) + (n0 >> 1) + j,
+                          gte / (1.f + expf(-gte)) * __uint_as_float(v[8 + j]));
+              }
           }
         } else if (!p.swap) {
           // rows = tokens (ra < M), columns = outputs
@@ -255,10 +249,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (threadIdx.x == 64) bspec::trace_mark(22, t_trace);      // partial tiles of the cluster visible
     if (warp >= 2 && !*abort_flag) {
       const int row = (warp & 3) * 32 + lane;
-      // plain: this thread owns output row `row` of the tile.  glu: threads 0..63 own gate row `row` and up row
-      // `row + 64` and produce output tile_a * 64 + row of the N / 2 outputs.
-      const bool active = p.glu ? row < 64 : true;
-      const int ra = p.glu ? tile_a * 64 + row : tile_a * TM + row;
+      // plain: this thread owns output row `row` of the tile.  glu: the threads of gate rows (row & 8 == 0) own that
+      // row and the up row 8 further and produce output tile_a * 64 + (row / 16) * 8 + row % 8 of the N / 2 outputs.
+      const bool active = p.glu ? (row & 8) == 0 : true;
+      const int ra = p.glu ? tile_a * 64 + (row >> 4) * 8 + (row & 7) : tile_a * TM + row;
       const int n_out = p.glu ? p.N / 2 : p.N;
       if (active && ra < n_out) {
         // addresses of this thread's row(s) in every peer's partial tile
@@ -282,7 +276,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               for (int s = 0; s < 8; ++s)
                 if (s < p.splits) {
                   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[t][s]) : "r"(peer[s] + off));
-                  if (p.glu) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(u[t][s]) : "r"(peer[s] + off + 256u));
+                  if (p.glu) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(u[t][s]) : "r"(peer[s] + off + 32u));
                 }
             }
           }
@@ -429,8 +423,7 @@ static int launch_gemm(const void* X, const void* W, void* C, int M, int N, int 
                        int sm_count, const RopeEpilogue* rope, cudaStream_t stream) {
   int plan[5];
   if (bspec_gemm_tc_plan(M, N, K, sm_count, plan) < 0) return (int)cudaErrorInvalidValue;
-  if (glu && (N % 128 != 0)) return (int)cudaErrorInvalidValue;
-  if (glu && !plan[0] && plan[1] < 128) plan[1] = 128;     // a gate/up group must lie inside one tile
+  if (glu && (N % 16 != 0)) return (int)cudaErrorInvalidValue;
   GemmParams p;
   p.C = C; p.status = status;
   p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.glu = glu ? 1 : 0;
@@ -494,7 +487,7 @@ static int launch_gemm(const void* X, const void* W, void* C, int M, int N, int 
 }
 
 // C = X W^T.  `status`: one int on the device, 0 unless a bounded wait ran out.
-// glu != 0: the rows of W come in groups of 128 (64 gate rows, then the 64 matching up rows; N a multiple of 128) and
+// glu != 0: the rows of W come in groups of 16 (8 gate rows, then the 8 matching up rows; N a multiple of 16) and
 // C is [M, N/2] = silu(gate) * up.
 BSPEC_API int bspec_gemm_tc(const void* X, const void* W, void* C, int M, int N, int K, int out_f32, int glu,
                             int* status, int sm_count, cudaStream_t stream) {

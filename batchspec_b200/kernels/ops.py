@@ -197,7 +197,7 @@ def gather_rows_add(resid: torch.Tensor, pending: Optional[torch.Tensor], rows: 
 
 
 GLU_FUSION = True
-GLU_GROUP = 64     # gate/up interleave of weights prepared for the fused-epilogue GEMM: 64 gate rows, 64 up rows
+GLU_GROUP = 8      # gate/up interleave of weights prepared for the fused epilogues: 8 gate rows, then their 8 up rows
 
 
 def silu_mul(u: torch.Tensor, out: torch.Tensor, group: int = 0) -> None:

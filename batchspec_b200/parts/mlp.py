@@ -1,7 +1,7 @@
 """SwiGLU feed-forward part (batchspec/models/modules/feedforward.py:25-27,62):
 u = x W13^T with W13 = [gate; up] fused at load (feedforward.py:35-38),
 m = silu(u[:, :I]) * u[:, I:], out = m W2^T.  No biases.  In bfloat16 the fused matrix is stored with gate and up
-rows interleaved in groups of 64 and decode-sized steps apply the activation inside the GEMM."""
+rows interleaved in groups of 8 (8 gate rows, then their 8 up rows) and decode-sized steps apply the activation inside the product."""
 from __future__ import annotations
 
 from typing import Dict

@@ -636,14 +636,14 @@ def test_tcgen05_gemm(ops, M, N, K, out_dtype):
 
 
 @pytest.mark.parametrize("M,I,K", [(1, 64, 64), (8, 14336, 4096), (5, 192, 72), (64, 256, 96), (128, 128, 264),
-                                   (300, 320, 128), (2048, 1024, 512)])
+                                   (300, 320, 128), (2048, 1024, 512), (3, 176, 64), (200, 1000, 96)])
 def test_gate_up_gemm_with_the_activation_in_its_epilogue(ops, M, I, K):
     g = torch.Generator(device=DEV).manual_seed(M + I)
     x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
     wg = (torch.randn(I, K, device=DEV, generator=g) / K ** 0.5).bfloat16()
     wu = (torch.randn(I, K, device=DEV, generator=g) / K ** 0.5).bfloat16()
     w13 = ops.interleave_gate_up(wg, wu)
-    assert torch.equal(w13[:64], wg[:64]) and torch.equal(w13[64:128], wu[:64])
+    assert torch.equal(w13[:8], wg[:8]) and torch.equal(w13[8:16], wu[:8]) and torch.equal(w13[16:24], wg[8:16])
     got = ops.linear_glu(x, w13)
     torch.cuda.synchronize()
     ops.check_status()
@@ -668,7 +668,8 @@ def test_silu_mul_layouts(ops):
         want = (gate.float() * torch.sigmoid(gate.float()) * up.float()).to(dtype)
         halves = torch.cat([gate, up], dim=1).contiguous()
         grouped = torch.stack([gate.view(7, 3, 64), up.view(7, 3, 64)], dim=2).reshape(7, 384).contiguous()
-        for u, group in ((halves, 0), (grouped, 64)):
+        eights = torch.stack([gate.view(7, 24, 8), up.view(7, 24, 8)], dim=2).reshape(7, 384).contiguous()
+        for u, group in ((halves, 0), (grouped, 64), (eights, 8)):
             out = torch.empty(7, 192, device=DEV, dtype=dtype)
             ops.silu_mul(u, out, group)
             torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
