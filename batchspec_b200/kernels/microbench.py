@@ -127,10 +127,10 @@ def bench_small(cfg, ms, timer, pk, dev):
         print(f"{'add_rmsnorm':16s} {M:5d} | {t:8.4f} {M * d * 12 / t / 1e6:7.0f}")
         u = torch.randn(M, 2 * I, device=dev).bfloat16()
         m = torch.empty(M, I, device=dev, dtype=torch.bfloat16)
-        t = timer.time(lambda: ops.silu_mul(u, m))
+        t = timer.time(lambda: ops.silu_mul(u, m, ops.GLU_GROUP))
         print(f"{'silu_mul':16s} {M:5d} | {t:8.4f} {M * I * 6 / t / 1e6:7.0f}")
         qkv = torch.randn(M, (Hq + 2 * Hkv) * hd, device=dev).bfloat16()
-        inv = torch.rand(hd // 2, device=dev)
+        inv = ops.rope_frequency_table(500000.0 ** (-torch.arange(hd // 2, dtype=torch.float64) * 2 / hd), dev)
         pos = torch.arange(M, device=dev, dtype=torch.int32)
         ent = torch.zeros(M, device=dev, dtype=torch.int32)
         n_pages = -(-M // 16)

@@ -721,3 +721,16 @@ def test_run_order_shared_cache_window_and_toy_parts(tmp_path, dtype):
         for p_ in range(len(toks)):
             assert H.rel_err(got[(rid, p_)], ref[p_]) <= tol, (rid, p_, dtype)
     eng.cache.check_invariants()
+
+
+def test_kernel_microbenchmarks_run():
+    """The microbenchmarks of kernels/microbench.py on a small configuration: they use the kernels' current
+    interfaces (a changed signature shows here, not on the day a profile is wanted)."""
+    import subprocess
+    import sys
+    root = __import__("pathlib").Path(__file__).resolve().parent.parent
+    out = subprocess.run([sys.executable, "-m", "batchspec_b200.kernels.microbench", "--config", "llama-3.2-1b", "--what",
+                          "gemm", "attention", "small", "--m", "8", "64"], cwd=root, capture_output=True, text=True,
+                         timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert "add_rmsnorm" in out.stdout and "rope_kv_append" in out.stdout
