@@ -304,3 +304,104 @@ def test_a_graph_safe_mixer_with_state_under_padded_captured_steps(tmp_path):
         if graphs:
             assert eng.model.graph_safe and 4 in eng._graphs and eng._graphs[4].uses >= 10, "decode ran through a padded graph"
     assert outs[True] == outs[False]
+
+
+# --------------------------------------------------------- a window at the head size of the fast bfloat16 kernels
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_window_layer_at_head_size_128_with_released_pages(tmp_path, dtype):
+    """A two-layer description made here: layer 0 sees all keys, layer 1 a window of 40, heads of 128 numbers and
+    pages of 16 tokens, i.e. the sizes at which bfloat16 steps go to the TMA decode kernels and the tensor-core prompt
+    kernel.  Requests of 150 to 230 tokens are decoded far past the window, so block-table entries of pages that
+    the window has passed (-1) and pages taken over by other requests reach those kernels in every way of cutting:
+    whole, the tail decoded, in portions, and mixed in a pool so small that the window's pages are used again.  A
+    key from outside the window that was still read (a released page, or another request's tokens in it) would
+    change the average over 40 keys by far more than the tolerance."""
+    from batchspec_b200.config import config_from_json_dict, register_config_class
+    from batchspec_b200.engine import Engine
+    from batchspec_b200.models import ModelSpec, RunEntry, prenorm_layer, register_model
+    from batchspec_b200.parts import PartSpec
+    from batchspec_b200.weights import write_random_model
+
+    DIM, HQ, HKV, HEAD, WINDOW, INNER, VOC, THETA = 96, 4, 2, 128, 40, 80, 211, 10000.0
+
+    @dataclass(frozen=True)
+    class WinConfig:
+        architecture: str
+        vocab_size: int
+        eps: float
+
+        @classmethod
+        def from_json_dict(cls, d):
+            return cls(d["architectures"][0], d["vocab_size"], d["eps"])
+
+        def to_json_dict(self):
+            return dict(architectures=[self.architecture], vocab_size=self.vocab_size, eps=self.eps)
+
+    def build(cfg):
+        norm = PartSpec("rmsnorm", dict(dim=DIM, eps=cfg.eps))
+        pos = PartSpec("rope", dict(head_dim=HEAD, theta=THETA))
+        layers = []
+        for i, window in enumerate((None, WINDOW)):
+            att = PartSpec("attention", dict(dim=DIM, n_heads=HQ, n_kv_heads=HKV, head_dim=HEAD, position=pos,
+                                             **({"window": window} if window else {})))
+            ffn = PartSpec("swiglu", dict(dim=DIM, intermediate=INNER))
+            names = {"norm1.weight": f"l{i}.n1", "norm2.weight": f"l{i}.n2", "ffn.gate": f"l{i}.gate",
+                     "ffn.up": f"l{i}.up", "ffn.down": f"l{i}.down"}
+            names.update({"mixer." + k: f"l{i}." + k for k in "qkvo"})
+            layers.append(prenorm_layer(norm, att, norm, ffn, names))
+        return ModelSpec(cfg.vocab_size, DIM, layers, [RunEntry(0), RunEntry(1)], norm, "emb", {"weight": "final"}, "head")
+
+    register_config_class("ToyWindow128LM", WinConfig)
+    register_model("ToyWindow128LM", build)
+    cfg = config_from_json_dict(dict(architectures=["ToyWindow128LM"], vocab_size=VOC, eps=1e-5))
+    folder = write_random_model(cfg, tmp_path, seed=31, dtype=torch.float32 if dtype == "float32" else torch.bfloat16,
+                                std=0.08, norm_std=0.1)
+    _, w = P.read_model_folder(folder)
+
+    def rope(t, T):
+        f = THETA ** (-2.0 * torch.arange(HEAD // 2, dtype=torch.float64) / HEAD)
+        ang = torch.arange(T, dtype=torch.float64)[:, None] * f[None]
+        c, sn = torch.cos(ang)[:, None], torch.sin(ang)[:, None]
+        h = HEAD // 2
+        return torch.cat([t[..., :h] * c - t[..., h:] * sn, t[..., :h] * sn + t[..., h:] * c], -1)
+
+    def oracle(tokens):
+        T = len(tokens)
+        x = w["emb"][torch.tensor(tokens)]
+        for i, window in enumerate((None, WINDOW)):
+            a = P.rms_norm(x, w[f"l{i}.n1"], cfg.eps)
+            q = rope((a @ w[f"l{i}.q"].T).reshape(T, HQ, HEAD), T)
+            k = rope((a @ w[f"l{i}.k"].T).reshape(T, HKV, HEAD), T)
+            v = (a @ w[f"l{i}.v"].T).reshape(T, HKV, HEAD)
+            h = x + P.causal_attention(q, k, v, window=window).reshape(T, HQ * HEAD) @ w[f"l{i}.o"].T
+            x = h + P.swiglu(P.rms_norm(h, w[f"l{i}.n2"], cfg.eps), torch.cat([w[f"l{i}.gate"], w[f"l{i}.up"]]),
+                             w[f"l{i}.down"])
+        return (P.rms_norm(x, w["final"], cfg.eps) @ w["head"].T).numpy()
+
+    reqs = {f"w{i}": H.random_tokens(n, VOC, 50 + i) for i, n in enumerate((230, 150, 190, 170))}
+    refs = {rid: oracle(toks) for rid, toks in reqs.items()}
+    tol = H.TOL[dtype]
+
+    def check(got, rids):
+        assert set(got) == {(rid, p) for rid in rids for p in range(len(reqs[rid]))}
+        for rid in rids:
+            for p in range(len(reqs[rid])):
+                assert H.rel_err(got[(rid, p)], refs[rid][p]) <= tol, (rid, p, dtype)
+
+    eng = Engine(dtype=dtype, device="cuda:0")
+    eng.load_model(model_dir=folder)
+    eng.setup_caches(max_batch_size=4, max_seq_length=256, page_size=16, num_pages=[64, 24])
+    assert [g.spec.policy for g in eng.cache.groups] == ["full", "window"]
+    for rid, toks in reqs.items():
+        for sched in (H.whole(rid, toks), H.tail_decoded(rid, toks, tail=64),
+                      H.portions(rid, toks, [70, 2, 33, 16, 5, 48, 3])):
+            check(H.run_steps_in_process(eng, sched), [rid])
+    # all four live at once, decoded tokens of some beside portions of others, in a window pool that could not hold
+    # one request whole (230 tokens are 15 pages; four requests share 22): the window's pages go round
+    steps = H.mixed(reqs, seed=6, max_live=4, sizes=(60, 1, 1, 17, 1, 2, 33, 1, 1, 9, 1, 1))
+    eng.setup_caches(max_batch_size=4, max_seq_length=256, page_size=16, num_pages=[H.max_live_tokens(steps, 16) // 16, 22])
+    check(H.run_steps_in_process(eng, steps), list(reqs))
+    window_pool = eng.cache.groups[1].pool
+    assert window_pool.high_water <= 22 and window_pool.num_held == 0
+    assert sum(-(-len(t) // 16) for t in reqs.values()) > 2 * 22, "the pool is far smaller than the requests"
