@@ -58,6 +58,8 @@ class Engine:
         self.max_batch_size = None
         self.max_seq_length = None
         self.decode_lookahead = True        # launch the next captured decode step before reading this one's tokens
+        self.time_decode_on_device = False  # CUDA events around every captured decode step (last_stats: decode_step_device_ms)
+        self._last_device_ms = None
         self._ahead = None
         self._stateful = False
         self._tok_host = None               # two pinned buffers that captured steps' tokens are copied into in turn
@@ -234,6 +236,10 @@ class Engine:
         ids = [s.seq_id for s in seqs]
         for rid in ids:
             self.cache.reserve(rid, 1)
+        timed = self.time_decode_on_device
+        if timed:
+            begin = torch.cuda.Event(enable_timing=True)
+            begin.record()
         out = graph.run(ids, tokens,
                         [d.temperature if s.temperature is None else s.temperature for s in seqs],
                         [d.top_k if s.top_k is None else s.top_k for s in seqs],
@@ -245,9 +251,9 @@ class Engine:
         host = self._tok_host[k][:len(ids)]
         host.copy_(out, non_blocking=True)
         ops.status_to_host_async()
-        ev = torch.cuda.Event()
+        ev = torch.cuda.Event(enable_timing=timed)
         ev.record()
-        return dict(graph=graph, ids=ids, host=host, event=ev, h2d=graph.last_h2d_bytes)
+        return dict(graph=graph, ids=ids, host=host, event=ev, begin=begin if timed else None, h2d=graph.last_h2d_bytes)
 
     def _graph_decode_step(self, graph, work: List[Workload], sched: Optional[Scheduler] = None) -> List[int]:
         """A pure decode step through the captured graph: host token ids in, host token ids out.
@@ -286,6 +292,9 @@ class Engine:
                 self._ahead = self._launch_decode(graph, seqs, None, 1)
         cur["event"].synchronize()
         ops.raise_if_gave_up()
+        # the step's own time on the device (its upload, kernels and the copy of its tokens), without whatever
+        # the stream waited for the host before it
+        self._last_device_ms = cur["begin"].elapsed_time(cur["event"]) if cur["begin"] is not None else None
         toks = cur["host"].tolist()
         self._last_h2d = cur["h2d"]
         if cur["ids"] == ids:
@@ -307,7 +316,7 @@ class Engine:
         steps = tokens_in = 0
         dec_steps = dec_tokens = dec_h2d = dec_d2h = 0
         dec_seconds = 0.0
-        step_ms, dec_step_ms = [], []
+        step_ms, dec_step_ms, dec_device_ms = [], [], []
         prof = get_active_profiler()
         while not sched.is_done():
             t_step = time.perf_counter()
@@ -324,6 +333,8 @@ class Engine:
                 if graph is not None:
                     toks = self._graph_decode_step(graph, work, sched)
                     h2d = self._last_h2d
+                    if self._last_device_ms is not None:
+                        dec_device_ms.append(self._last_device_ms)
                 else:
                     self._ahead = None        # a step launched ahead stands for the very next step or for none
                     entries = [StepEntry(w.seq.seq_id, w.seq.known_tokens(w.start, w.start + w.n_tokens),
@@ -353,7 +364,8 @@ class Engine:
                 dec_d2h += 4 * len(work)
         self.last_stats = dict(steps=steps, tokens_fed=tokens_in, preemptions=sched.num_preemptions,
                                generated=sum(len(s.output_ids) for s in sched.completed),
-                               step_ms=step_ms, decode_step_ms=dec_step_ms, decode_steps=dec_steps,
+                               step_ms=step_ms, decode_step_ms=dec_step_ms, decode_step_device_ms=dec_device_ms,
+                               decode_steps=dec_steps,
                                pages_high_water=[g.pool.high_water for g in self.cache.groups], decode_tokens=dec_tokens, decode_seconds=dec_seconds,
                                decode_h2d_bytes_per_step=dec_h2d // max(dec_steps, 1),
                                decode_d2h_bytes_per_step=dec_d2h // max(dec_steps, 1))

@@ -198,12 +198,20 @@ def run_e2e(eng, cfg, batch, steps, warmup, page_size=16):
     prompts = prompts_for(batch, cfg.vocab_size, 3)
     # before that: the same call on the same prompts, a few tokens (loads kernels, captures the decode graph)
     eng.generate([Sequence(i, p, max_new_tokens=4) for i, p in enumerate(prompts)])
+    eng.time_decode_on_device = True
     eng.generate([Sequence(i, p, max_new_tokens=warm + steps + 1) for i, p in enumerate(prompts)])
+    eng.time_decode_on_device = False
     st = eng.last_stats
     ms = st["decode_step_ms"]
     assert len(ms) == warm + steps, (len(ms), warm, steps)
     timed = ms[warm:]
+    # the same steps by CUDA events around each of them: what the GPU took for them at the clock it had then
+    # (the clock moves between 1.3 and 1.9 GHz under the power cap and the step follows it), so that what the
+    # host adds can be told from what the clock did between this region and the device-timed one
+    on_device = st["decode_step_device_ms"][warm:]
     return dict(value=round(batch * steps / (sum(timed) * 1e-3), 2), unit="tok/s",
+                same_steps_on_device_ms=round(sum(on_device) / len(on_device), 3),
+                of_same_steps_on_device=round(sum(on_device) / sum(timed), 4),
                 h2d_bytes_per_step=st["decode_h2d_bytes_per_step"], d2h_bytes_per_step=st["decode_d2h_bytes_per_step"],
                 decode_steps=steps, warmup_steps=warm, step_p50_ms=round(pct(timed, 0.5), 3),
                 step_mean_ms=round(sum(timed) / len(timed), 3), step_max_ms=round(max(timed), 3),
