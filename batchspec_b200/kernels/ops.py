@@ -56,8 +56,8 @@ _SIGNATURES = {
     "bspec_gemm_tc_qkv_rope": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "bspec_attention_prefill_tc": [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
-                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
-                                   c_void_p],
+                                   c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_float,
+                                   c_int, c_int, c_void_p, c_void_p],
     "bspec_sgemm_tn": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p],
     "bspec_pick_slices": [c_int],
     "bspec_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -330,6 +330,15 @@ def attention_splits(n_entries: int, n_kv_heads: int, group: int, max_q_len: int
     return best
 
 
+_work_counters = {}               # device -> two zeroed ints: the prompt attention kernel's item counter
+
+
+def _work_counter(device) -> torch.Tensor:
+    if device not in _work_counters:
+        _work_counters[device] = torch.zeros((2,), dtype=torch.int32, device=device)
+    return _work_counters[device]
+
+
 def _counters(device, n: int) -> torch.Tensor:
     bufs = _tile_counters.setdefault(device, [])
     if not bufs or bufs[-1].numel() < n:
@@ -394,8 +403,10 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, c
             # long portions on the tcgen05 kernel; what is left for the call below are the short requests
             _check(lib.bspec_attention_prefill_tc(
                 qkv.data_ptr(), qkv.stride(0), out.data_ptr(), status, cache.shape[0], cache.data_ptr(), qo, pos,
-                kv_indptr, kv_indices, ctx.n_entries, ctx.max_q_len, n_heads, n_kv_heads, head_dim, tables.page_size,
-                float(scale), int(window), short + 1, _stream()), "attention_prefill_tc")
+                kv_indptr, kv_indices, ctx.n_entries, qkv.shape[0], ctx.max_q_len, n_heads, n_kv_heads, head_dim,
+                tables.page_size,
+                float(scale), int(window), short + 1, _work_counter(qkv.device).data_ptr(), _stream()),
+                "attention_prefill_tc")
             run_prefill = 0
             if not run_decode:
                 return
@@ -438,6 +449,8 @@ def _raise_status(dev, code: int) -> None:
         for bufs in _tile_counters.values():
             for b in bufs:
                 b.zero_()
+        for b in _work_counters.values():
+            b.zero_()
     raise KernelError(f"a kernel on {dev} gave up a bounded wait (code {code}: GEMM 1 = stage never freed, "
                       f"2 = operands never arrived, 3 = accumulator never completed; decode attention 11/13 = stage "
                       f"never freed, 12/14 = keys never arrived; prompt attention 21/22 the same, 31-38 = a role of "
