@@ -3,19 +3,21 @@
 //
 // A CTA owns 256 rows, (token, query head of one kv group) pairs of one request and one kv head, as two Q tiles
 // of 128 rows with a softmax warpgroup each, and walks the visible keys in tiles of 64:
-//   warp 0    TMA: K and V pages of the key tile into a three-stage ring (one box per page and 64-column half,
-//             128-byte swizzle, completion on an mbarrier);
+//   warp 0    TMA: K and V pages of the key tile into a four-stage ring (one box per page and 64-column half,
+//             128-byte swizzle, completion on an mbarrier), and the Q tiles;
 //   warps 1, 10   one thread each issues tcgen05.mma for Q tile 0 / 1:  S = Q K^T  (128 x 64 x 128, operands
 //             K-major in shared memory) into one of the tile's two S buffers in tensor memory, and  O += P V
-//             (A = P in shared memory, B = V read MN-major straight from the loaded pages) into the tile's O
-//             accumulator.  S runs two key tiles ahead; P V of tile j is issued the moment P_j is announced.
+//             (A = P read from tensor memory, B = V read MN-major straight from the loaded pages) into the
+//             tile's O accumulator.  S runs two key tiles ahead; P V of tile j is issued the moment P_j is announced.
 //   warps 2-5 / 6-9   Q tile 0 / 1, one thread per row: read its S row from tensor memory, scale, mask, online
-//             softmax in float32 (two values per instruction where sm_100 has a packed form; a quarter of the
-//             exponentials as a cubic on the FMA pipe, the rest on the special-function unit), write P (bfloat16) into
-//             one of the tile's two P buffers in shared memory in the operand layout, rescale its O row in tensor
+//             softmax in float32 (two values per instruction where sm_100 has a packed form), write P (bfloat16)
+//             back into tensor memory over the first half of the S buffer it came from, rescale its O row in tensor
 //             memory when its scale moved, and at the end normalise and store O.
-// The softmax of a tile never waits for the tensor core in the steady state: S of the next key tile is ready, and
-// its P goes to the buffer that the P V before last has long released.  The issuing threads are two, in different
+// The operands of a tcgen05.mma come out of shared memory at 128 bytes per clock, which is what such a product
+// takes here (M = 128, K = 16: 48 clocks at N = 64, 64 at N = 128): with P in tensor memory the P V product
+// fetches only V (32 clocks per instruction instead of 64), and the softmax threads write no shared memory.
+// The softmax of a tile never waits for the tensor core in the steady state: S of the next key tile is ready.
+// The issuing threads are two, in different
 // warps, because they share their schedulers with softmax warps whose long runs of independent instructions keep
 // them waiting some 300 cycles at every mbarrier they look at: with one thread for both Q tiles those waits and
 // the (blocking) issues of both tiles stood in one line, and that line was the kernel's critical path.
@@ -32,11 +34,7 @@ constexpr int HD = 128;
 constexpr int ROWS = 128;            // rows per Q tile = accumulator lanes
 constexpr int QT = 2;                // Q tiles per CTA
 constexpr int KT = 64;               // keys per tile
-constexpr int STAGES = 3;
-#ifndef BSPEC_ATTN_EMU
-#define BSPEC_ATTN_EMU 4
-#endif
-constexpr int EMU = BSPEC_ATTN_EMU;   // every EMU-th pair of exponentials on the FMA pipe (0: none)
+constexpr int STAGES = 4;
 constexpr int MMA_WARP_1 = 2 + 4 * QT;                 // the second Q tile's MMA warp: after the softmax warps
 constexpr int THREADS = 32 * (3 + 4 * QT);
 constexpr int SUBQ = ROWS * 64;      // elements of a [128][64] sub-tile (16 KB): Q halves, P
@@ -55,6 +53,14 @@ __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum) : "memory");
+}
+// the A operand read from tensor memory (rows on the lanes, two bfloat16 per 32-bit column)
+__device__ __forceinline__ void tc_mma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accum) : "memory");
 }
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile(
@@ -83,18 +89,6 @@ __device__ __forceinline__ float ex2(float x) {          // 2^x on the special-f
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// 2^x without the special-function unit: round x to the nearest integer n by adding 1.5 * 2^23 (n then sits in the
-// sum's low mantissa bits), a cubic for 2^(x - n) on [-0.5, 0.5] (relative error 7.5e-5, far below bfloat16's
-// step), and n added to the exponent.  x <= 8 here; below -126 the result is about 1e-38.
-__device__ __forceinline__ float ex2_fma(float x) {
-  x = fmaxf(x, -126.f);
-  const float t = x + 12582912.f;
-  const float f = x - (t - 12582912.f);
-  float p = fmaf(0.05517165f, f, 0.24261113f);
-  p = fmaf(p, f, 0.69326097f);
-  p = fmaf(p, f, 0.99992806f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
-}
 // Two float32 operations per instruction (sm_100 has packed forms of add, mul and fma) and a maximum of three:
 // the softmax is bound by the number of instructions it issues, not by the arithmetic pipes.
 __device__ __forceinline__ uint64_t pack2(float a, float b) {
@@ -119,23 +113,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
-}
-// ex2_fma for two values at once.
-__device__ __forceinline__ void ex2_fma2(uint64_t x2, float& p0, float& p1) {
-  float x0, x1;
-  unpack2(x2, x0, x1);
-  x2 = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
-  const uint64_t t2 = add2(x2, pack2(12582912.f, 12582912.f));
-  const uint64_t u2 = add2(t2, pack2(-12582912.f, -12582912.f));
-  const uint64_t f2 = fma2(u2, pack2(-1.f, -1.f), x2);
-  uint64_t q2 = fma2(pack2(0.05517165f, 0.05517165f), f2, pack2(0.24261113f, 0.24261113f));
-  q2 = fma2(q2, f2, pack2(0.69326097f, 0.69326097f));
-  q2 = fma2(q2, f2, pack2(0.99992806f, 0.99992806f));
-  float t0, t1, q0, q1;
-  unpack2(t2, t0, t1);
-  unpack2(q2, q0, q1);
-  p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
-  p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -244,8 +221,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem);                  // QT x [128][128]
-  __nv_bfloat16* Ps = Qs + QT * QTILE;                                         // QT x 2 buffers x [128][64]
-  __nv_bfloat16* KV = Ps + QT * 2 * SUBQ;                                      // STAGES x (K tile, V tile)
+  __nv_bfloat16* Os = Qs + QT * QTILE;                                         // QT x [128][64]: O on its way out
+  __nv_bfloat16* KV = Os + QT * SUBQ;                                          // STAGES x (K tile, V tile)
   uint64_t* bars = reinterpret_cast<uint64_t*>(KV + STAGES * 2 * KTILE);
   uint64_t* kv_full = bars;                        // [STAGES]
   uint64_t* kv_empty = kv_full + STAGES;           // [STAGES]
@@ -451,13 +428,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_
             if (!ok) break;
           }
           tc_fence_after();
-          const uint64_t pdesc = desc_kmajor(Ps + (tt * 2 + bf) * SUBQ);
+          const uint32_t p_tmem = tmem + (uint32_t)(tt * 128) + bf * 64u;     // P: the first 32 columns of its S buffer
           const uint64_t vdesc = desc_mnmajor(KV + (size_t)st * 2 * KTILE + KTILE);
           const uint32_t d = tmem + (uint32_t)(256 + tt * 128);
 #pragma unroll
-          for (int kk = 0; kk < KT / 16; ++kk)          // 16 keys: 32 bytes along P's rows, 16 rows of V
-            tc_mma(d, pdesc + (uint64_t)(2 * kk), vdesc + (uint64_t)(kk * ((16 * 128) >> 4)), id_o,
-                   (j > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < KT / 16; ++kk)          // 16 keys: 8 columns of P, 16 rows of V
+            tc_mma_a_tmem(d, p_tmem + (uint32_t)(8 * kk), vdesc + (uint64_t)(kk * ((16 * 128) >> 4)), id_o,
+                          (j > 0 || kk > 0) ? 1u : 0u);
           tc_commit(pv_done + 2 * tt + bf);              // O holds key tiles 0..j, this P buffer may be overwritten
           tc_commit(kv_empty + st);                      // this Q tile no longer reads K_j and V_j
           // S of key tile j + 2 (its K was fetched into the stage that the P V of tile j - 1 released)
@@ -475,7 +452,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_
     const int row = quad * 32 + lane;                        // row of the Q tile = TMEM lane
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
     const uint32_t tmem_o = tmem + (uint32_t)(256 + tt * 128) + lane_addr;
-    unsigned char* pdst0 = reinterpret_cast<unsigned char*>(Ps + tt * 2 * SUBQ) + row * 128;
+    unsigned char* stage = reinterpret_cast<unsigned char*>(Os + tt * SUBQ) + row * 128;   // this thread's row
     uint32_t sq = 0;             // key tiles of this Q tile before this item
     bool ok = true;
     while (ok && NEXT_ITEM()) {
@@ -568,23 +545,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_
               packed[16 * c + (i >> 1)] = *reinterpret_cast<uint32_t*>(&hh);
             }
         } else {
-          // The special-function unit makes 16 exponentials per clock and SM, which is as long as the tensor core
-          // needs for the two products of the tile: every EMU-th pair of exponentials goes to the FMA pipe instead.
-          // Scaling, the cubic and the row sum handle two values per instruction (fma/add.f32x2).
+          // Scaling and the row sum handle two values per instruction (fma/add.f32x2); the exponentials all go
+          // to the special-function unit (with P in shared memory a quarter of them, computed as a cubic on the
+          // FMA pipe, paid; with P in tensor memory the softmax is bound by the instructions it issues).
 #pragma unroll
           for (int c = 0; c < 2; ++c)
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-              const uint64_t x2 = fma2(pack2(__uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1])), scale2, neg_m2);
-              const bool emu = EMU > 0 && ((i >> 1) % EMU) == EMU - 1;
               float p0, p1;
-              if (emu) {
-                ex2_fma2(x2, p0, p1);
-              } else {
-                unpack2(x2, p0, p1);
-                p0 = ex2(p0);
-                p1 = ex2(p1);
-              }
+              unpack2(fma2(pack2(__uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1])), scale2, neg_m2), p0, p1);
+              p0 = ex2(p0);
+              p1 = ex2(p1);
               l2[(i >> 1) & 1] = add2(l2[(i >> 1) & 1], pack2(p0, p1));
               __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
               packed[16 * c + (i >> 1)] = *reinterpret_cast<uint32_t*>(&hh);
@@ -593,16 +564,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_
         float la, lb;
         unpack2(add2(l2[0], l2[1]), la, lb);
         l += la + lb;
-        // this tile's P buffer was last read by the P V of the key tile two before it (of this item or the last)
-        if (n >= 2) {
-          ok = mbar_wait(pv_done + 2 * tt + b, ((n - 2) >> 1) & 1u, abort_flag, status, 37);
-          if (!ok) break;
-        }
-        unsigned char* pdst = pdst0 + b * (SUBQ * 2);
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch)
-          *reinterpret_cast<uint4*>(pdst + ((ch ^ (row & 7)) << 4)) =
-              make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
+        // P goes back into tensor memory, over the first half of the S buffer this thread has just read: the P V
+        // product takes its A operand from there.  What the columns held before (P of the key tile two before
+        // this one) was read by a product that was issued, and so completed, before this S.
+        tc_st32(s_addr, packed);
         // rescale this row of O if its scale moved (the warp decides together: the TMEM access is warp-wide); the
         // P V of key tile j - 1 must have completed before O is touched
         if (j >= 1 && __any_sync(0xffffffffu, corr != 1.f)) {
@@ -618,9 +583,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_
             for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
             tc_st32(tmem_o + 32u * c, v);
           }
-          tc_wait_st();
         }
-        fence_async_smem();
+        tc_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(p_ready + 2 * tt + b);
@@ -630,50 +594,52 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_
       if (ok) ok = mbar_wait(pv_done + 2 * tt + (n_last & 1u), (n_last >> 1) & 1u, abort_flag, status, 38);
       tc_fence_after();
       if (ok) {
-        // O: tensor memory -> registers (normalised, bfloat16) -> this warp's own rows of the two P buffers (no
-        // product reads them any more, and only this warp writes them) -> global memory in whole 256-byte rows,
-        // 16 lanes per row.  A thread storing its own row would touch 32 different lines per instruction.
+        // O: tensor memory -> registers (normalised, bfloat16) -> this warp's own 32 rows of a staging tile in
+        // shared memory -> global memory in runs of 128 bytes, 8 lanes per row, 64 columns at a time.  A thread
+        // storing its own row would touch 32 different lines per instruction.
         const float inv = l > 0.f ? 1.f / l : 0.f;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tc_ld32(tmem_o + 32u * c, v);
-          tc_wait_ld();
-          if (c == 3) {
-            // O is in registers: the next item's first P V may overwrite it
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(o_free + tt);
-          }
-          unsigned char* stage = pdst0 + (c >> 1) * (SUBQ * 2);      // columns 0..63 in buffer 0, 64..127 in buffer 1
-#pragma unroll
-          for (int k4 = 0; k4 < 4; ++k4) {
-            uint32_t w[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(v[8 * k4 + 2 * i]) * inv,
-                                                        __uint_as_float(v[8 * k4 + 2 * i + 1]) * inv);
-              w[i] = *reinterpret_cast<uint32_t*>(&hh);
-            }
-            const int ch = 4 * (c & 1) + k4;                         // 16-byte chunk of the 64-column half
-            *reinterpret_cast<uint4*>(stage + ((ch ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-        }
-        __syncwarp();
-        const unsigned char* wbase = reinterpret_cast<const unsigned char*>(Ps + tt * 2 * SUBQ) + (quad * 32) * 128;
-        const int sub = lane >> 4, ch16 = lane & 15;                 // two rows per pass, 16 chunks of a row
+        const unsigned char* wbase = reinterpret_cast<const unsigned char*>(Os + tt * SUBQ) + (quad * 32) * 128;
+        const int sub = lane >> 3, ch8 = lane & 7;                   // four rows per pass, 8 chunks of a half row
         const int r_warp = it.row0 + tt * ROWS + quad * 32;
-#pragma unroll 4
-        for (int i = 0; i < 16; ++i) {
-          const int rl = 2 * i + sub, rr = r_warp + rl;
-          if (rr < t.rows_total) {
-            const uint4 v4 = *reinterpret_cast<const uint4*>(wbase + (ch16 >> 3) * (SUBQ * 2) + rl * 128 +
-                                                             (((ch16 & 7) ^ (rl & 7)) << 4));
-            const int qr = rr / t.G, hr = g * t.G + (rr - qr * t.G);
-            *reinterpret_cast<uint4*>(out + ((size_t)(t.q_begin + qr) * Hq + hr) * HD + 8 * ch16) = v4;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+#pragma unroll
+          for (int c2 = 0; c2 < 2; ++c2) {
+            const int c = 2 * half + c2;
+            uint32_t v[32];
+            tc_ld32(tmem_o + 32u * c, v);
+            tc_wait_ld();
+            if (c == 3) {
+              // O is in registers: the next item's first P V may overwrite it
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(o_free + tt);
+            }
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4) {
+              uint32_t w[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(v[8 * k4 + 2 * i]) * inv,
+                                                          __uint_as_float(v[8 * k4 + 2 * i + 1]) * inv);
+                w[i] = *reinterpret_cast<uint32_t*>(&hh);
+              }
+              const int ch = 4 * c2 + k4;                            // 16-byte chunk of the 64-column half
+              *reinterpret_cast<uint4*>(stage + ((ch ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
           }
+          __syncwarp();
+#pragma unroll 4
+          for (int i = 0; i < 8; ++i) {
+            const int rl = 4 * i + sub, rr = r_warp + rl;
+            if (rr < t.rows_total) {
+              const uint4 v4 = *reinterpret_cast<const uint4*>(wbase + rl * 128 + ((ch8 ^ (rl & 7)) << 4));
+              const int qr = rr / t.G, hr = g * t.G + (rr - qr * t.G);
+              *reinterpret_cast<uint4*>(out + ((size_t)(t.q_begin + qr) * Hq + hr) * HD + 64 * half + 8 * ch8) = v4;
+            }
+          }
+          __syncwarp();                                              // before the rows are written again
         }
-        __syncwarp();                                                // before this warp writes P again
       }
       sq += (uint32_t)my_tiles;
     }
@@ -693,7 +659,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_
 }
 
 size_t smem_bytes() {
-  return 1024 + (size_t)(QT * QTILE + QT * 2 * SUBQ + STAGES * 2 * KTILE) * 2 + (2 * STAGES + 9 * QT + ITEM_RING) * 8 + 64 + ITEM_RING * sizeof(Item);
+  return 1024 + (size_t)(QT * QTILE + QT * SUBQ + STAGES * 2 * KTILE) * 2 + (2 * STAGES + 9 * QT + ITEM_RING) * 8 + 64 + ITEM_RING * sizeof(Item);
 }
 
 // The q rows of a step as (64 columns of a head, heads, tokens): one box is half a Q tile, [128 / G tokens][G heads
