@@ -406,15 +406,21 @@ def test_split_keys_agree_with_one_pass(ops, splits):
     torch.testing.assert_close(a, b, rtol=3e-2, atol=2e-2)
 
 
-@pytest.mark.parametrize("q_lens,kv_lens", [([257, 1024], [8192 + 257, 30000]), ([1024, 257], [8192, 30000 + 257]),
-                                            ([4096], [30000])])
-def test_prompt_portions_deep_inside_a_long_context(ops, q_lens, kv_lens):
+@pytest.mark.parametrize("Hq,Hkv,q_lens,kv_lens", [(32, 8, [257, 1024], [8192 + 257, 30000]),
+                                                   (32, 8, [1024, 257], [8192, 30000 + 257]), (32, 8, [4096], [30000]),
+                                                   # 3 query heads per kv head: rows do not align with tokens, so
+                                                   # the softmax threads fetch Q themselves; 168 items on 148 CTAs,
+                                                   # a third of them naming no work (the shorter request)
+                                                   (6, 2, [3500, 2200], [3700, 9000]),
+                                                   (8, 8, [1500, 2500], [6000, 2500])])
+def test_prompt_portions_deep_inside_a_long_context(ops, Hq, Hkv, q_lens, kv_lens):
     """Portions of a prompt at cached lengths of 8,192 and 30,000 tokens on the tensor-core prompt kernel
-    (head_dim 128, page 16): hundreds of key tiles per query tile, the heaviest-first order of CTAs, pages looked
-    up far into a scrambled table.  Queries are scaled up so that the softmax is peaked (with unit-variance
+    (head_dim 128, page 16): hundreds of key tiles per query tile, several items per persistent CTA drawn
+    heaviest first, pages looked up far into a scrambled table.  Queries are scaled up so that the softmax is peaked (with unit-variance
     scores over 30,000 keys every output would be near zero and any fault would hide inside the tolerance); one
-    query per request also has a single far key that must win.  Reference: float32 torch products on the GPU."""
-    Hq, Hkv, hd, ps = 32, 8, 128, 16
+    query per request also has a single far key that must win.  Reference: float32 torch products on the GPU.
+    A second launch gives the same bits, whichever CTA draws which item."""
+    hd, ps = 128, 16
     G = Hq // Hkv
     g = torch.Generator(device=DEV).manual_seed(11)
     n, scale = sum(q_lens), 1.0 / math.sqrt(hd)
@@ -455,6 +461,11 @@ def test_prompt_portions_deep_inside_a_long_context(ops, q_lens, kv_lens):
     ops.check_status()
     assert ops.launch_count() - before == 1, "only the tensor-core prompt kernel runs for these portions"
     assert not torch.isnan(out.float()).any()
+    again = torch.full_like(out, float("nan"))
+    ops.paged_attention(q, again, cache, ctx, tables, Hq, Hkv, hd, scale, 0)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert torch.equal(out, again)
     for e, (ql, L) in enumerate(zip(q_lens, kv_lens)):
         k, v = ks[e].float().permute(1, 0, 2), vs[e].float().permute(1, 0, 2)               # [Hkv, L, hd]
         key = torch.arange(L, device=DEV)[None, None, :]
