@@ -21,7 +21,7 @@ attn_generic_kernel(const T* __restrict__ q, long long q_row_stride, T* __restri
                     const T* __restrict__ cache, const int* __restrict__ qo_indptr,
                     const int* __restrict__ positions, const int* __restrict__ kv_indptr,
                     const int* __restrict__ kv_indices, int Hq, int Hkv, int hd, int page_size, float scale,
-                    int window) {
+                    int window, long long n_pages) {
   bspec::pdl_prologue(7);
   __shared__ float qs[WARPS][MAX_HD];
   const int e = blockIdx.y, h = blockIdx.z;
@@ -51,9 +51,10 @@ attn_generic_kernel(const T* __restrict__ q, long long q_row_stride, T* __restri
   float m = -INFINITY, l = 0.f;
   for (int kb = (lo / 32) * 32; kb <= hi; kb += 32) {
     const int key = kb + lane;
-    const bool valid = key >= lo && key <= hi;
+    bool valid = key >= lo && key <= hi;
     long long koff = 0;
     float s = -INFINITY;
+    if (valid && !bspec::in_range(table[key / page_size], n_pages, 107)) valid = false;
     if (valid) {
       const int page = table[key / page_size];
       koff = (long long)((size_t)page * 2 * page_elems + head_off + (size_t)(key % page_size) * hd);
@@ -98,7 +99,8 @@ attn_generic_kernel(const T* __restrict__ q, long long q_row_stride, T* __restri
 BSPEC_API int bspec_attention_generic(const void* q, long long q_row_stride, void* out, const void* cache, int dtype,
                                       const int* qo_indptr, const int* positions, const int* kv_indptr,
                                       const int* kv_indices, int n_entries, int max_q_len, int Hq, int Hkv, int hd,
-                                      int page_size, float scale, int window, cudaStream_t stream) {
+                                      int page_size, float scale, int window, long long n_pages,
+                                      cudaStream_t stream) {
   if (n_entries <= 0 || max_q_len <= 0) return 0;
   if (hd > MAX_HD || hd <= 0 || Hq % Hkv != 0) return (int)cudaErrorInvalidValue;
   dim3 grid((max_q_len + WARPS - 1) / WARPS, n_entries, Hq);
@@ -106,12 +108,13 @@ BSPEC_API int bspec_attention_generic(const void* q, long long q_row_stride, voi
   if (dtype == BSPEC_F32)
     BSPEC_LAUNCH((attn_generic_kernel<float>), grid, WARPS * 32, 0, stream, 
         (const float*)q, q_row_stride, (float*)out, (const float*)cache, qo_indptr, positions, kv_indptr, kv_indices,
-        Hq, Hkv, hd, page_size, scale, window);
+        Hq, Hkv, hd, page_size, scale, window, n_pages);
   else
     BSPEC_LAUNCH((attn_generic_kernel<__nv_bfloat16>), grid, WARPS * 32, 0, stream, 
         (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)cache, qo_indptr, positions,
-        kv_indptr, kv_indices, Hq, Hkv, hd, page_size, scale, window);
+        kv_indptr, kv_indices, Hq, Hkv, hd, page_size, scale, window, n_pages);
   return BSPEC_LAUNCH_CHECK();
 }
 
 BSPEC_DEFINE_TRACE_SETTER(bspec_trace_set_attention_generic)
+BSPEC_DEFINE_BOUNDS_REPORT(bspec_bounds_report_attention_generic)

@@ -26,6 +26,16 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompil
               "--expt-relaxed-constexpr"]
 
 
+def bounds_requested() -> bool:
+    """``BSPEC_BOUNDS=1`` in the environment: the checked build (``-DBSPEC_BOUNDS``: indices that come from data are
+    compared with their ranges, recorded and skipped when outside), kept in a build folder of its own."""
+    return os.environ.get("BSPEC_BOUNDS", "0") == "1"
+
+
+def _flags() -> List[str]:
+    return NVCC_FLAGS + (["-DBSPEC_BOUNDS"] if bounds_requested() else [])
+
+
 def _log(msg: str) -> None:
     print(f"[batchspec_b200 build] {msg}", file=sys.stderr, flush=True)
 
@@ -48,7 +58,7 @@ def _source_hash() -> str:
     for p in sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))):
         h.update(p.name.encode())
         h.update(p.read_bytes())
-    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
+    h.update(" ".join(ARCH_FLAGS + _flags()).encode())
     return h.hexdigest()
 
 
@@ -58,7 +68,7 @@ def _build_dir() -> Path:
         d = Path(override)
         d.mkdir(parents=True, exist_ok=True)
         return d
-    d = CSRC / "_build"
+    d = CSRC / ("_build_checked" if bounds_requested() else "_build")
     try:
         d.mkdir(exist_ok=True)
         probe = d / f".w{os.getpid()}"
@@ -66,7 +76,7 @@ def _build_dir() -> Path:
         probe.unlink()
         return d
     except OSError:
-        d = Path(tempfile.gettempdir()) / f"batchspec_b200_build_{os.getuid()}"
+        d = Path(tempfile.gettempdir()) / f"batchspec_b200_build_{os.getuid()}{'_checked' if bounds_requested() else ''}"
         d.mkdir(parents=True, exist_ok=True)
         return d
 
@@ -95,7 +105,7 @@ def _compile(bdir: Path, lib: Path) -> None:
     procs = []
     for src in srcs:
         obj = bdir / (src.stem + ".o")
-        cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc, *ARCH_FLAGS, *_flags(), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
         procs.append((src, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, env=env)))
     pending = list(procs)
     last = time.time()

@@ -89,6 +89,28 @@ __device__ __forceinline__ void trace_mark(int kid, unsigned long long t_from) {
     }
   }
 }
+// Checked build (-DBSPEC_BOUNDS; set BSPEC_BOUNDS=1 in the environment when the library is built): indices that
+// come from data (token ids, row numbers, block-table slots and the page ids in them) are compared with their
+// ranges before they address memory with plain loads and stores.  The first one found outside is recorded as
+// {code, value, limit, block} and the access is skipped: a wrong table then costs a wrong result and a report,
+// not a fault.  Each translation unit has its own record; BSPEC_DEFINE_BOUNDS_REPORT exports its reader.
+// Codes: 101 token id (embedding), 102 row (gather), 103 block-table slot and 104 page id (rotary + cache append),
+// 105 / 106 the same in the q/k/v product's epilogue, 107 page id (attention over plain loads).  Copies through
+// TMA need no such check: the tensor map clips them.
+#ifdef BSPEC_BOUNDS
+static __device__ int g_bounds[4] = {0, 0, 0, 0};
+__device__ __forceinline__ bool in_range(long long v, long long n, int code) {
+  if (v >= 0 && v < n) return true;
+  if (atomicCAS(&g_bounds[0], 0, code) == 0) {
+    g_bounds[1] = (int)max(-2147483647ll, min(2147483647ll, v));
+    g_bounds[2] = (int)min(2147483647ll, n);
+    g_bounds[3] = (int)blockIdx.x;
+  }
+  return false;
+}
+#else
+__device__ __forceinline__ bool in_range(long long, long long, int) { return true; }
+#endif
 __device__ __forceinline__ void pdl_prologue(int kid = 0) {
   const unsigned long long t0 = g_trace_buf != nullptr ? global_timer() : 0ull;
   pdl_launch_dependents();
@@ -142,6 +164,23 @@ inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
 #define BSPEC_LAUNCH(kernel, grid, block, smem, stream, ...) \
   (void)bspec::launch(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, __VA_ARGS__)
 #define BSPEC_LAUNCH_CHECK() (int)cudaGetLastError()
+// Reads (and clears) the translation unit's record of the checked build into out4; returns 1 in a checked build,
+// 0 otherwise (out4 zeroed), a negative CUDA error on failure.  Waits for the device.
+#ifdef BSPEC_BOUNDS
+#define BSPEC_DEFINE_BOUNDS_REPORT(name)                                                           \
+  BSPEC_API int name(int* out4) {                                                                  \
+    const int zero[4] = {0, 0, 0, 0};                                                              \
+    cudaError_t e = cudaMemcpyFromSymbol(out4, bspec::g_bounds, sizeof(zero));                     \
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(bspec::g_bounds, zero, sizeof(zero));             \
+    return e == cudaSuccess ? 1 : -(int)e;                                                         \
+  }
+#else
+#define BSPEC_DEFINE_BOUNDS_REPORT(name)                                                           \
+  BSPEC_API int name(int* out4) {                                                                  \
+    out4[0] = out4[1] = out4[2] = out4[3] = 0;                                                     \
+    return 0;                                                                                      \
+  }
+#endif
 #define BSPEC_DEFINE_TRACE_SETTER(name)                                                            \
   BSPEC_API int name(unsigned long long* buf, unsigned int* cnt) {                                 \
     cudaError_t e = cudaMemcpyToSymbol(bspec::g_trace_buf, &buf, sizeof(buf));                     \

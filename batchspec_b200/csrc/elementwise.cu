@@ -14,6 +14,7 @@ __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ 
   const int t = blockIdx.x;
   int id = ids[t];
   const bool ok = id >= 0 && id < vocab;
+  (void)bspec::in_range(id, vocab, 101);
   const T* row = table + (size_t)(ok ? id : 0) * d;
   float* o = out + (size_t)t * d;
   for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = ok ? to_f32(row[i]) * scale : 0.f;
@@ -165,8 +166,9 @@ BSPEC_API int bspec_add_rmsnorm(float* resid, const void* delta, int delta_dtype
 // ---------------------------------------------------------------- row gather (+ pending add)
 template <typename TD>
 __global__ void gather_rows_add_kernel(const float* __restrict__ resid, const TD* __restrict__ pending,
-                                       const int* __restrict__ rows, float* __restrict__ out, int d) {
+                                       const int* __restrict__ rows, float* __restrict__ out, int d, int n_src) {
   bspec::pdl_prologue(3);
+  if (!bspec::in_range(rows[blockIdx.x], n_src, 102)) return;
   const size_t src = (size_t)rows[blockIdx.x] * d, dst = (size_t)blockIdx.x * d;
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     float v = resid[src + i];
@@ -176,12 +178,12 @@ __global__ void gather_rows_add_kernel(const float* __restrict__ resid, const TD
 }
 
 BSPEC_API int bspec_gather_rows_add(const float* resid, const void* pending, int pending_dtype, const int* rows,
-                                    float* out, int n_out, int d, cudaStream_t stream) {
+                                    float* out, int n_out, int d, int n_src, cudaStream_t stream) {
   if (n_out <= 0) return 0;
   if (pending_dtype == BSPEC_F32)
-    BSPEC_LAUNCH((gather_rows_add_kernel<float>), n_out, 256, 0, stream, resid, (const float*)pending, rows, out, d);
+    BSPEC_LAUNCH((gather_rows_add_kernel<float>), n_out, 256, 0, stream, resid, (const float*)pending, rows, out, d, n_src);
   else
-    BSPEC_LAUNCH((gather_rows_add_kernel<__nv_bfloat16>), n_out, 256, 0, stream, resid, (const __nv_bfloat16*)pending, rows, out, d);
+    BSPEC_LAUNCH((gather_rows_add_kernel<__nv_bfloat16>), n_out, 256, 0, stream, resid, (const __nv_bfloat16*)pending, rows, out, d, n_src);
   return BSPEC_LAUNCH_CHECK();
 }
 
@@ -285,7 +287,7 @@ __global__ void rope_kv_append_kernel(T* __restrict__ qkv, int Hq, int Hkv, int 
                                       int rot, int interleaved, const int* __restrict__ positions,
                                       const int* __restrict__ tok_entry, const int* __restrict__ kv_indptr,
                                       const int* __restrict__ kv_indices, T* __restrict__ cache, int page_size,
-                                      int write_kv) {
+                                      int write_kv, long long n_pages) {
   bspec::pdl_prologue(5);
   extern __shared__ float cs[];  // [rot/2] cos, [rot/2] sin
   const int t = blockIdx.x;
@@ -308,12 +310,17 @@ __global__ void rope_kv_append_kernel(T* __restrict__ qkv, int Hq, int Hkv, int 
   T* vdst = nullptr;
   if (write_kv && slot1 > Hq) {
     const int e = tok_entry[t];
-    const int page = kv_indices[kv_indptr[e] + pos / page_size];
-    const int r = pos % page_size;
-    const size_t page_elems = (size_t)Hkv * page_size * hd;
-    kdst = cache + ((size_t)page * 2) * page_elems + (size_t)r * hd;
-    vdst = kdst + page_elems;
+    if (bspec::in_range(pos / page_size, kv_indptr[e + 1] - kv_indptr[e], 103)) {
+      const int page = kv_indices[kv_indptr[e] + pos / page_size];
+      if (bspec::in_range(page, n_pages, 104)) {
+        const int r = pos % page_size;
+        const size_t page_elems = (size_t)Hkv * page_size * hd;
+        kdst = cache + ((size_t)page * 2) * page_elems + (size_t)r * hd;
+        vdst = kdst + page_elems;
+      }
+    }
   }
+  write_kv = kdst != nullptr;
   const int hp = hd / 2;  // work items per head: one per pair of dims
   for (int w = threadIdx.x; w < (slot1 - slot0) * hp; w += blockDim.x) {
     const int h = slot0 + w / hp, j = w % hp;
@@ -362,7 +369,7 @@ __global__ void __launch_bounds__(256)
 rope_kv_append_vec_kernel(__nv_bfloat16* __restrict__ qkv, int Hq, int Hkv, int hd, const float* __restrict__ inv_freq,
                           const int* __restrict__ positions, const int* __restrict__ tok_entry,
                           const int* __restrict__ kv_indptr, const int* __restrict__ kv_indices,
-                          __nv_bfloat16* __restrict__ cache, int page_size, int write_kv) {
+                          __nv_bfloat16* __restrict__ cache, int page_size, int write_kv, long long n_pages) {
   bspec::pdl_prologue(5);
   extern __shared__ float cs[];  // [hd/2] cos, [hd/2] sin
   const int t = blockIdx.x, half = hd / 2;
@@ -380,10 +387,15 @@ rope_kv_append_vec_kernel(__nv_bfloat16* __restrict__ qkv, int Hq, int Hkv, int 
   __nv_bfloat16* vdst = nullptr;
   if (write_kv) {
     const int e = tok_entry[t];
-    const int page = kv_indices[kv_indptr[e] + pos / page_size];
-    const size_t page_elems = (size_t)Hkv * page_size * hd;
-    kdst = cache + ((size_t)page * 2) * page_elems + (size_t)(pos % page_size) * hd;
-    vdst = kdst + page_elems;
+    if (bspec::in_range(pos / page_size, kv_indptr[e + 1] - kv_indptr[e], 103)) {
+      const int page = kv_indices[kv_indptr[e] + pos / page_size];
+      if (bspec::in_range(page, n_pages, 104)) {
+        const size_t page_elems = (size_t)Hkv * page_size * hd;
+        kdst = cache + ((size_t)page * 2) * page_elems + (size_t)(pos % page_size) * hd;
+        vdst = kdst + page_elems;
+      }
+    }
+    write_kv = kdst != nullptr;
   }
   const int per_rot = half / 8;                 // items per rotated head: eight pairs each
   const int n_rot = (Hq + Hkv) * per_rot;
@@ -425,7 +437,7 @@ rope_kv_append_vec_kernel(__nv_bfloat16* __restrict__ qkv, int Hq, int Hkv, int 
 BSPEC_API int bspec_rope_kv_append(void* qkv, int dtype, int n, int Hq, int Hkv, int hd, const float* inv_freq, int rot,
                                    int interleaved, const int* positions, const int* tok_entry, const int* kv_indptr,
                                    const int* kv_indices, void* cache, int page_size, int write_kv,
-                                   cudaStream_t stream) {
+                                   long long n_pages, cudaStream_t stream) {
   if (n <= 0) return 0;
   const int threads = 128;
   const size_t smem = (size_t)(rot > 0 ? rot : 0) * sizeof(float);
@@ -433,7 +445,7 @@ BSPEC_API int bspec_rope_kv_append(void* qkv, int dtype, int n, int Hq, int Hkv,
       (reinterpret_cast<uintptr_t>(qkv) & 15) == 0 && (reinterpret_cast<uintptr_t>(cache) & 15) == 0) {
     // many tokens: one block per token (or two while they are few) with 16-byte accesses
     BSPEC_LAUNCH((rope_kv_append_vec_kernel), dim3(n, n >= 512 ? 1 : 2), 256, smem, stream, (__nv_bfloat16*)qkv, Hq, Hkv, hd,
-                 inv_freq, positions, tok_entry, kv_indptr, kv_indices, (__nv_bfloat16*)cache, page_size, write_kv);
+                 inv_freq, positions, tok_entry, kv_indptr, kv_indices, (__nv_bfloat16*)cache, page_size, write_kv, n_pages);
     return BSPEC_LAUNCH_CHECK();
   }
   dim3 grid(n, (Hq + 2 * Hkv + ROPE_HEADS_PER_BLOCK - 1) / ROPE_HEADS_PER_BLOCK);
@@ -441,11 +453,11 @@ BSPEC_API int bspec_rope_kv_append(void* qkv, int dtype, int n, int Hq, int Hkv,
   if (dtype == BSPEC_F32)
     BSPEC_LAUNCH((rope_kv_append_kernel<float>), grid, threads, smem, stream, (float*)qkv, Hq, Hkv, hd, inv_freq, rot, interleaved,
                                                                  positions, tok_entry, kv_indptr, kv_indices,
-                                                                 (float*)cache, page_size, write_kv);
+                                                                 (float*)cache, page_size, write_kv, n_pages);
   else
     BSPEC_LAUNCH((rope_kv_append_kernel<__nv_bfloat16>), grid, threads, smem, stream, 
         (__nv_bfloat16*)qkv, Hq, Hkv, hd, inv_freq, rot, interleaved, positions, tok_entry, kv_indptr, kv_indices,
-        (__nv_bfloat16*)cache, page_size, write_kv);
+        (__nv_bfloat16*)cache, page_size, write_kv, n_pages);
   return BSPEC_LAUNCH_CHECK();
 }
 
@@ -489,3 +501,4 @@ BSPEC_API int bspec_rope_inplace(void* x, int dtype, int n, long long row_stride
 }
 
 BSPEC_DEFINE_TRACE_SETTER(bspec_trace_set_elementwise)
+BSPEC_DEFINE_BOUNDS_REPORT(bspec_bounds_report_elementwise)

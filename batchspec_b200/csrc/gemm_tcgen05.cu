@@ -55,6 +55,7 @@ struct GemmParams {
   const int* kv_indices;
   __nv_bfloat16* cache;      // this layer's pages [page][k|v][Hkv][page_size][128]
   int Hq, Hkv, page_size, interleaved, write_kv;
+  long long n_pages;         // pages of the cache layer (read by the checked build only)
 };
 
 // cos and sin of position * frequency j, the angle formed and reduced to [-pi, pi] in float64 (as elementwise.cu).
@@ -330,7 +331,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)tok * p.N + ra] = b;
               } else if (p.write_kv) {
                 const int e = p.tok_entry[tok];
+                if (!bspec::in_range(pos / p.page_size, p.kv_indptr[e + 1] - p.kv_indptr[e], 105)) continue;
                 const long long page = p.kv_indices[p.kv_indptr[e] + pos / p.page_size];
+                if (!bspec::in_range(page, p.n_pages, 106)) continue;
                 const int kvh = is_v ? head - p.Hq - p.Hkv : head - p.Hq;
                 const size_t at = (((size_t)page * 2 + (is_v ? 1 : 0)) * p.Hkv + kvh) * p.page_size * TM +
                                   (size_t)(pos % p.page_size) * TM + row;
@@ -417,6 +420,7 @@ struct RopeEpilogue {
   const int* kv_indices;
   void* cache;
   int Hq, Hkv, page_size, interleaved, write_kv;
+  long long n_pages;
 };
 
 static int launch_gemm(const void* X, const void* W, void* C, int M, int N, int K, int out_f32, int glu, int* status,
@@ -430,6 +434,7 @@ static int launch_gemm(const void* X, const void* W, void* C, int M, int N, int 
   p.swap = plan[0]; p.bn = plan[1]; p.splits = plan[2]; p.stages = plan[3];
   p.rope_freq = nullptr; p.positions = p.tok_entry = p.kv_indptr = p.kv_indices = nullptr; p.cache = nullptr;
   p.Hq = p.Hkv = p.page_size = p.interleaved = p.write_kv = 0;
+  p.n_pages = 0;
   if (rope != nullptr) {
     // one 128-row tile per head, on the weights-on-rows arrangement, bfloat16 out, room behind the partial tile
     const int stage_bytes = TM * BK * 2 + ((p.bn * BK * 2 + 1023) & ~1023);
@@ -440,6 +445,7 @@ static int launch_gemm(const void* X, const void* W, void* C, int M, int N, int 
     p.kv_indptr = rope->kv_indptr; p.kv_indices = rope->kv_indices; p.cache = (__nv_bfloat16*)rope->cache;
     p.Hq = rope->Hq; p.Hkv = rope->Hkv; p.page_size = rope->page_size; p.interleaved = rope->interleaved;
     p.write_kv = rope->write_kv;
+    p.n_pages = rope->n_pages;
   }
   const int kb_total = (K + BK - 1) / BK;
   p.kblocks_per_split = (kb_total + p.splits - 1) / p.splits;
@@ -503,9 +509,10 @@ BSPEC_API int bspec_gemm_tc(const void* X, const void* W, void* C, int M, int N,
 BSPEC_API int bspec_gemm_tc_qkv_rope(const void* X, const void* W, void* C, int M, int N, int K, int* status, int sm_count,
                                      const float* freq, const int* positions, const int* tok_entry,
                                      const int* kv_indptr, const int* kv_indices, void* cache, int Hq, int Hkv,
-                                     int page_size, int interleaved, int write_kv, cudaStream_t stream) {
+                                     int page_size, int interleaved, int write_kv, long long n_pages,
+                                     cudaStream_t stream) {
   const RopeEpilogue rope = {freq, positions, tok_entry, kv_indptr, kv_indices, cache, Hq, Hkv, page_size,
-                             interleaved, write_kv};
+                             interleaved, write_kv, n_pages};
   return launch_gemm(X, W, C, M, N, K, 0, 0, status, sm_count, &rope, stream);
 }
 
@@ -513,3 +520,4 @@ BSPEC_API int bspec_gemm_tc_qkv_rope(const void* X, const void* W, void* C, int 
 BSPEC_API void bspec_set_pdl(int on) { bspec::pdl_enabled() = on != 0; }
 
 BSPEC_DEFINE_TRACE_SETTER(bspec_trace_set_gemm_tcgen05)
+BSPEC_DEFINE_BOUNDS_REPORT(bspec_bounds_report_gemm_tcgen05)

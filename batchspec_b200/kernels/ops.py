@@ -41,20 +41,21 @@ def _dtype_code(t: torch.dtype) -> int:
 _SIGNATURES = {
     "bspec_embed": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
     "bspec_add_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
-    "bspec_gather_rows_add": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "bspec_gather_rows_add": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "bspec_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "bspec_rope_kv_append": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
-                             c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+                             c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p],
     "bspec_rope_inplace": [c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "bspec_attention_generic": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                                c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+                                c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_longlong, c_void_p],
     "bspec_attention_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong,
                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                              c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "bspec_gemm_tc_plan": [c_int, c_int, c_int, c_int, c_void_p],
     "bspec_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
     "bspec_gemm_tc_qkv_rope": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
-                               c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                               c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_longlong,
+                               c_void_p],
     "bspec_attention_prefill_tc": [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_float,
                                    c_int, c_int, c_void_p, c_void_p],
@@ -84,7 +85,13 @@ def load_library():
         _lib = lib
         from . import debug
         debug.apply_environment(sys.modules[__name__], lib)
+        global _BOUNDS_ACTIVE
+        from ..csrc.build import bounds_requested
+        _BOUNDS_ACTIVE = bounds_requested()
     return _lib
+
+
+_BOUNDS_ACTIVE = False
 
 
 def set_pdl(on: bool) -> None:
@@ -193,7 +200,8 @@ def gather_rows_add(resid: torch.Tensor, pending: Optional[torch.Tensor], rows: 
     assert resid.is_contiguous() and out.is_contiguous() and (pending is None or pending.is_contiguous())
     pd = _dtype_code(pending.dtype) if pending is not None else F32
     _check(load_library().bspec_gather_rows_add(resid.data_ptr(), _ptr(pending), pd, rows.data_ptr(), out.data_ptr(),
-                                                out.shape[0], out.shape[1], _stream()), "gather_rows_add")
+                                                out.shape[0], out.shape[1], resid.shape[0], _stream()),
+           "gather_rows_add")
 
 
 GLU_FUSION = True
@@ -264,7 +272,8 @@ def rope_kv_append(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: i
     _check(load_library().bspec_rope_kv_append(
         qkv.data_ptr(), _dtype_code(qkv.dtype), n, n_heads, n_kv_heads, head_dim, _ptr(inv_freq), int(rotary_dim),
         int(bool(interleaved)), positions.data_ptr(), tok_entry.data_ptr(), kv_indptr.data_ptr(),
-        kv_indices.data_ptr(), cache.data_ptr(), int(page_size), int(bool(write_kv)), _stream()), "rope_kv_append")
+        kv_indices.data_ptr(), cache.data_ptr(), int(page_size), int(bool(write_kv)), cache.shape[0], _stream()),
+        "rope_kv_append")
 
 
 def rope_inplace(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int,
@@ -422,7 +431,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, c
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), cache.data_ptr(), _dtype_code(qkv.dtype),
         ctx.qo_indptr.data_ptr(), ctx.positions.data_ptr(), tables.kv_indptr.data_ptr(), tables.kv_indices.data_ptr(),
         ctx.n_entries, ctx.max_q_len, n_heads, n_kv_heads, head_dim, tables.page_size, float(scale), int(window),
-        _stream()), "attention_generic")
+        cache.shape[0], _stream()), "attention_generic")
 
 
 # ---------------------------------------------------------------------------- matrix products
@@ -459,11 +468,56 @@ def _raise_status(dev, code: int) -> None:
 
 
 def check_status() -> None:
-    """Raise if a kernel of this package gave up on a bounded wait (synchronises)."""
+    """Raise if a kernel of this package gave up on a bounded wait (synchronises); in a checked build
+    (``BSPEC_BOUNDS=1``) also if an index was found outside its range."""
     for dev, t in _status.items():
         code = int(t.item())
         if code:
             _raise_status(dev, code)
+    check_bounds()
+
+
+_BOUNDS_REPORTS = ["bspec_bounds_report_elementwise", "bspec_bounds_report_gemm_tcgen05",
+                   "bspec_bounds_report_attention_generic"]
+BOUNDS_CODES = {101: "token id (embedding)", 102: "row (gather)", 103: "block-table slot (rotary + cache append)",
+                104: "page id (rotary + cache append)", 105: "block-table slot (q/k/v product's epilogue)",
+                106: "page id (q/k/v product's epilogue)", 107: "page id (attention over plain loads)"}
+
+
+def bounds_reports() -> list:
+    """Checked build only (the library built with ``BSPEC_BOUNDS=1`` in the environment): what the kernels of the
+    current device recorded since the last call, as (source file, what, value, limit, block); the records are
+    cleared.  Empty in an ordinary build.  Waits for the device."""
+    lib = load_library()
+    found = []
+    for name in _BOUNDS_REPORTS:
+        fn = getattr(lib, name)
+        fn.argtypes = [ctypes.POINTER(c_int * 4)]
+        fn.restype = c_int
+        rec = (c_int * 4)()
+        r = fn(ctypes.byref(rec))
+        if r < 0:
+            raise KernelError(f"{name} failed with CUDA error {-r}")
+        if r == 1 and rec[0]:
+            found.append((name[len("bspec_bounds_report_"):], BOUNDS_CODES.get(rec[0], str(rec[0])), rec[1], rec[2], rec[3]))
+    return found
+
+
+def bounds_build() -> bool:
+    """Whether the loaded library is the checked build."""
+    load_library()
+    return _BOUNDS_ACTIVE
+
+
+def check_bounds() -> None:
+    """Raise if the checked build recorded an index outside its range (no-op in an ordinary build)."""
+    if not _BOUNDS_ACTIVE:
+        return
+    found = bounds_reports()
+    if found:
+        raise KernelError("the checked build found indices outside their ranges (the accesses were skipped): " +
+                          "; ".join(f"{src}: {what} {value} not in [0, {limit}) in block {block}"
+                                    for src, what, value, limit, block in found))
 
 
 _status_host = {}
@@ -529,8 +583,8 @@ def linear_qkv_rope(x: torch.Tensor, wqkv: torch.Tensor, n_heads: int, n_kv_head
     _check(load_library().bspec_gemm_tc_qkv_rope(
         x.data_ptr(), wqkv.data_ptr(), out.data_ptr(), M, N, K, _status_word(x.device).data_ptr(), sm_count(x.device),
         inv_freq.data_ptr(), positions.data_ptr(), tok_entry.data_ptr(), kv_indptr.data_ptr(), kv_indices.data_ptr(),
-        cache.data_ptr(), n_heads, n_kv_heads, int(page_size), int(bool(interleaved)), int(bool(write_kv)), _stream()),
-        "gemm_tc_qkv_rope")
+        cache.data_ptr(), n_heads, n_kv_heads, int(page_size), int(bool(interleaved)), int(bool(write_kv)),
+        cache.shape[0], _stream()), "gemm_tc_qkv_rope")
     return out
 
 
