@@ -160,7 +160,19 @@ def run_steps_in_process(engine, steps):
         for rid in s["end"]:
             engine.release(rid)
         engine.cache.check_invariants()
+    assert_unused_pages_untouched(engine)
     return out
+
+
+def assert_unused_pages_untouched(engine):
+    """Pages are handed out lowest id first and freed ones are used again before new ones, so the ids from a
+    pool's high-water mark up were never handed out: they must still hold the zeros they were allocated with.
+    A stray write of any kernel (a wrong page id, a row beyond a page) into them shows here."""
+    for grp in engine.cache.groups:
+        pool = grp.pool
+        if getattr(grp, "pages", None) is not None and pool.high_water < pool.num_pages:
+            spare = grp.pages[:, pool.high_water:pool.num_pages]
+            assert not bool(spare.any()), f"a page that was never handed out was written (group of {grp.spec.policy})"
 
 
 def run_trace_subprocess(folder, dtype, steps, out_dir, max_tokens, extra_args=(), env=None, timeout=900):
