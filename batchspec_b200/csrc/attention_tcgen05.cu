@@ -377,7 +377,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_
       const uint32_t id_s = idesc(KT, false), id_o = idesc(HD, true);
       const uint64_t qdesc = desc_kmajor(Qs + tt * QTILE);
       uint32_t kv_base = 0;      // key tiles of the items before this one (all of them pass through the ring)
-      uint32_t sq = 0;           // key tiles of this Q tile before this item: S and P buffers alternate with it
+      uint32_t sq = 0;           // key tiles of this Q tile before this item: the S buffers (and P in them) alternate with it
       uint32_t n_mine = 0;       // items before this one in which this Q tile had rows
       bool ok = true;
       while (ok && NEXT_ITEM()) {
@@ -405,7 +405,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_
           if (j == my_tiles - 1) tc_commit(q_free + tt);     // the item's last S: its Q tile may be replaced
           return true;
         };
-        // S runs two key tiles ahead of P V (two S buffers and two P buffers per Q tile, three K/V stages)
+        // S runs two key tiles ahead of P V (two S buffers per Q tile, four K/V stages)
         for (int j = 0; j < 2 && j < my_tiles && ok; ++j) ok = issue_s(j);
         for (int j = 0; j < n_tiles && ok; ++j) {
           const uint32_t kn = kv_base + (uint32_t)j;
@@ -435,7 +435,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_
           for (int kk = 0; kk < KT / 16; ++kk)          // 16 keys: 8 columns of P, 16 rows of V
             tc_mma_a_tmem(d, p_tmem + (uint32_t)(8 * kk), vdesc + (uint64_t)(kk * ((16 * 128) >> 4)), id_o,
                           (j > 0 || kk > 0) ? 1u : 0u);
-          tc_commit(pv_done + 2 * tt + bf);              // O holds key tiles 0..j, this P buffer may be overwritten
+          tc_commit(pv_done + 2 * tt + bf);              // O holds key tiles 0..j
           tc_commit(kv_empty + st);                      // this Q tile no longer reads K_j and V_j
           // S of key tile j + 2 (its K was fetched into the stage that the P V of tile j - 1 released)
           if (j + 2 < my_tiles) ok = issue_s(j + 2);

@@ -462,7 +462,7 @@ def _raise_status(dev, code: int) -> None:
             b.zero_()
     raise KernelError(f"a kernel on {dev} gave up a bounded wait (code {code}: GEMM 1 = stage never freed, "
                       f"2 = operands never arrived, 3 = accumulator never completed; decode attention 11/13 = stage "
-                      f"never freed, 12/14 = keys never arrived; prompt attention 21/22 the same, 31-38 = a role of "
+                      f"never freed, 12/14 = keys never arrived; prompt attention 21/22 the same, 31-41 = a role of "
                       f"the tensor-core prompt kernel).  The results of the steps "
                       f"since the last check are not valid.")
 
