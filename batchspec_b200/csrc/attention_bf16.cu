@@ -472,7 +472,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
     for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
 
   if (warp == 4) {
-    // ---- producer: one lane issues every copy
+    // ---- producer: the copies of a key tile are dealt to the lanes (see attn_decode_shares_kernel)
     if (n_tiles > 0) {
       const int first_pg = max(k_begin, lo_key) / page_size, last_pg = (k_end - 1) / page_size;
       const int n_pg = last_pg - first_pg + 1;
@@ -481,33 +481,33 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
         for (int i = lane; i < n_pg; i += 32) tbl[i] = table[first_pg + i];
         __syncwarp();
       }
-      if (lane == 0) {
-        const int pages_per_tile = KT / page_size;
-        constexpr uint32_t tile_bytes = 2u * TILE_ELEMS * 2u;
-        bool waited = false;
-        for (int it = 0; it < n_tiles; ++it) {
-          const int s = it % TMA_STAGES;
-          const uint32_t ph = (uint32_t)(it / TMA_STAGES) & 1u;
-          if (!waited && (it >= TMA_STAGES || k_begin + (it + 1) * KT > t.pos0)) {
-            bspec::pdl_wait();             // this tile holds new keys, or a stage must first be released by consumers
-            waited = true;
-          }
-          if (!mbar_wait(empty + s, ph ^ 1u, abort_flag, status, 11)) break;
-          __nv_bfloat16* Ks = KV + (size_t)s * 2 * TILE_ELEMS;
-          mbar_expect_tx(full + s, tile_bytes);
-          const int key0 = k_begin + it * KT;
-          for (int pp = 0; pp < pages_per_tile; ++pp) {
-            int pg = (key0 + pp * page_size) / page_size;
-            pg = min(max(pg, first_pg), last_pg);
-            const int page = in_smem ? tbl[pg - first_pg] : table[pg];
-            const int row_k = ((page * 2) * Hkv + g) * page_size;           // first cache row of this page's K
-            const int row_v = row_k + Hkv * page_size;
-#pragma unroll
-            for (int c = 0; c < HD / 64; ++c) {
-              tma_load_2d(Ks + c * (KT * 64) + pp * page_size * 64, &kv_map, full + s, c * 64, row_k);
-              tma_load_2d(Ks + TILE_ELEMS + c * (KT * 64) + pp * page_size * 64, &kv_map, full + s, c * 64, row_v);
-            }
-          }
+      const int pages_per_tile = KT / page_size;
+      constexpr uint32_t tile_bytes = 2u * TILE_ELEMS * 2u;
+      constexpr int PER_PAGE = 2 * (HD / 64);
+      bool waited = false;
+      int ok = 1;
+      for (int it = 0; it < n_tiles; ++it) {
+        const int s = it % TMA_STAGES;
+        const uint32_t ph = (uint32_t)(it / TMA_STAGES) & 1u;
+        if (!waited && (it >= TMA_STAGES || k_begin + (it + 1) * KT > t.pos0)) {
+          bspec::pdl_wait();             // this tile holds new keys, or a stage must first be released by consumers
+          waited = true;
+        }
+        if (lane == 0) {
+          ok = mbar_wait(empty + s, ph ^ 1u, abort_flag, status, 11) ? 1 : 0;
+          if (ok) mbar_expect_tx(full + s, tile_bytes);
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        __nv_bfloat16* Ks = KV + (size_t)s * 2 * TILE_ELEMS;
+        const int key0 = k_begin + it * KT;
+        for (int bx = lane; bx < pages_per_tile * PER_PAGE; bx += 32) {
+          const int pp = bx / PER_PAGE, rem = bx - pp * PER_PAGE, c = rem >> 1, is_v = rem & 1;
+          int pg = key0 / page_size + pp;
+          pg = min(max(pg, first_pg), last_pg);
+          const int page = in_smem ? tbl[pg - first_pg] : table[pg];
+          const int row = ((page * 2 + is_v) * Hkv + g) * page_size;           // first cache row of this page's K (or V)
+          tma_load_2d(Ks + is_v * TILE_ELEMS + c * (KT * 64) + pp * page_size * 64, &kv_map, full + s, c * 64, row);
         }
       }
     }
@@ -814,8 +814,11 @@ attn_decode_shares_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv
   uint32_t tile_no = 0;                  // tiles this CTA has been through: stage and phase follow from it
 
   if (warp == 4) {
-    // ---- producer: one lane issues every copy
-    bool waited = false, ok = true;
+    // ---- producer: the copies of a key tile are dealt to the lanes (a single thread issuing all sixteen 2 KB
+    // copies of a tile runs at about two thirds of what one thread can issue at all)
+    bool waited = false;
+    int ok = 1;
+    const int pages_per_tile = KT / page_size;
     for (long long pos = share_begin; pos < share_end && ok;) {
       Piece pc;
       piece_at(pc, pos, share_end, b, sh, pos0_of, rows_of, n_entries, Hq, Hkv, row_tiles, window);
@@ -829,36 +832,32 @@ attn_decode_shares_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv
       if (in_smem)
         for (int i = lane; i < n_pg; i += 32) tbl[i] = table[first_pg + i];
       __syncwarp();
-      if (lane == 0) {
-        const int pages_per_tile = KT / page_size;
-        constexpr uint32_t tile_bytes = 2u * TILE_ELEMS * 2u;
-        for (int k = 0; k < pc.n_tiles; ++k, ++tile_no) {
-          const int s = tile_no % TMA_STAGES;
-          const uint32_t ph = (tile_no / TMA_STAGES) & 1u;
-          if (!waited && (tile_no >= TMA_STAGES || pc.k_begin + (k + 1) * KT > pc.t.pos0)) {
-            bspec::pdl_wait();           // this tile holds new keys, or a stage must first be released by consumers
-            waited = true;
-          }
-          if (!mbar_wait(empty + s, ph ^ 1u, abort_flag, status, 13)) { ok = false; break; }
-          __nv_bfloat16* Ks = KV + (size_t)s * 2 * TILE_ELEMS;
-          mbar_expect_tx(full + s, tile_bytes);
-          const int key0 = pc.k_begin + k * KT;
-          for (int pp = 0; pp < pages_per_tile; ++pp) {
-            int pg = (key0 + pp * page_size) / page_size;
-            pg = min(max(pg, first_pg), last_pg);
-            const int page = in_smem ? tbl[pg - first_pg] : table[pg];
-            const int row_k = ((page * 2) * Hkv + pc.g) * page_size;           // first cache row of this page's K
-            const int row_v = row_k + Hkv * page_size;
-#pragma unroll
-            for (int c = 0; c < HD / 64; ++c) {
-              tma_load_2d(Ks + c * (KT * 64) + pp * page_size * 64, &kv_map, full + s, c * 64, row_k);
-              tma_load_2d(Ks + TILE_ELEMS + c * (KT * 64) + pp * page_size * 64, &kv_map, full + s, c * 64, row_v);
-            }
-          }
+      constexpr uint32_t tile_bytes = 2u * TILE_ELEMS * 2u;
+      for (int k = 0; k < pc.n_tiles; ++k, ++tile_no) {
+        const int s = tile_no % TMA_STAGES;
+        const uint32_t ph = (tile_no / TMA_STAGES) & 1u;
+        if (!waited && (tile_no >= TMA_STAGES || pc.k_begin + (k + 1) * KT > pc.t.pos0)) {
+          bspec::pdl_wait();           // this tile holds new keys, or a stage must first be released by consumers
+          waited = true;
+        }
+        if (lane == 0) {
+          ok = mbar_wait(empty + s, ph ^ 1u, abort_flag, status, 13) ? 1 : 0;
+          if (ok) mbar_expect_tx(full + s, tile_bytes);
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        // the tile's copies, one per (page, 64-column half, K or V), dealt to the lanes
+        __nv_bfloat16* Ks = KV + (size_t)s * 2 * TILE_ELEMS;
+        constexpr int PER_PAGE = 2 * (HD / 64);
+        for (int bx = lane; bx < pages_per_tile * PER_PAGE; bx += 32) {
+          const int pp = bx / PER_PAGE, rem = bx - pp * PER_PAGE, c = rem >> 1, is_v = rem & 1;
+          int pg = (pc.k_begin + k * KT) / page_size + pp;
+          pg = min(max(pg, first_pg), last_pg);
+          const int page = in_smem ? tbl[pg - first_pg] : table[pg];
+          const int row = ((page * 2 + is_v) * Hkv + pc.g) * page_size;       // first cache row of this page's K (or V)
+          tma_load_2d(Ks + is_v * TILE_ELEMS + c * (KT * 64) + pp * page_size * 64, &kv_map, full + s, c * 64, row);
         }
       }
-      ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-      tile_no = __shfl_sync(0xffffffffu, tile_no, 0);
     }
     return;
   }
