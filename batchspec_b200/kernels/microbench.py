@@ -59,6 +59,24 @@ class Timer:
             ts.append(s.elapsed_time(e))
         return statistics.median(ts)
 
+    def time_in_a_row(self, fn, reps: int, warmup=5, rounds=5) -> float:
+        """Median milliseconds per call when ``reps`` calls follow each other without a gap (no flush of the L2
+        between them: right for a kernel whose inputs the kernel before it has just written, and for kernels
+        whose inputs exceed the L2 anyway)."""
+        for _ in range(warmup):
+            fn()
+        ts = []
+        for _ in range(rounds):
+            torch.cuda.synchronize()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(reps):
+                fn()
+            e.record()
+            e.synchronize()
+            ts.append(s.elapsed_time(e) / reps)
+        return statistics.median(ts)
+
 
 def bench_gemms(cfg, ms, timer, pk, dev, only=None):
     d, I, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
@@ -88,7 +106,7 @@ def bench_gemms(cfg, ms, timer, pk, dev, only=None):
 ATTENTION_CASES = [(1, 1, 2304), (8, 1, 2304), (64, 1, 2304), (8, 1, 30000), (1, 2048, 2048), (4, 512, 4096)]
 
 
-def bench_attention(cfg, timer, pk, dev, page=16, cases=None):
+def bench_attention(cfg, timer, pk, dev, page=16, cases=None, in_a_row=False):
     Hq, Hkv, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
     print(f"{'attention':10s} {'batch':>5s} {'q_len':>5s} {'kv_len':>6s} | {'ms':>8s} {'GB/s':>7s} {'TF/s':>7s} | frac of {pk['source']} peak")
     for batch, q_len, kv_len in cases or ATTENTION_CASES:
@@ -106,7 +124,11 @@ def bench_attention(cfg, timer, pk, dev, page=16, cases=None):
             max_q_len=q_len, max_kv_len=kv_len, extras={"min_q_len": q_len})
         tables = SimpleNamespace(kv_indptr=i32([i * pages_per for i in range(batch + 1)]),
                                  kv_indices=torch.randperm(n_pages, device=dev).to(torch.int32), page_size=page)
-        t = timer.time(lambda: ops.paged_attention(qkv, out, cache, ctx, tables, Hq, Hkv, hd, hd ** -0.5, 0))
+        call = lambda: ops.paged_attention(qkv, out, cache, ctx, tables, Hq, Hkv, hd, hd ** -0.5, 0)
+        if in_a_row:                 # as many calls as take about 10 ms
+            t = timer.time_in_a_row(call, max(3, min(200, int(10.0 / max(timer.time(call, iters=3), 1e-3)))))
+        else:
+            t = timer.time(call)
         kv_bytes = batch * kv_len * 2 * Hkv * hd * 2
         pairs = batch * (q_len * (kv_len - q_len) + q_len * (q_len + 1) / 2)
         flops = 4.0 * pairs * Hq * hd
@@ -219,6 +241,8 @@ def main():
                     help="time only these projections")
     ap.add_argument("--attn-case", nargs=3, type=int, action="append", metavar=("BATCH", "Q_LEN", "KV_LEN"),
                     help="attention case(s) to time instead of the built-in list")
+    ap.add_argument("--in-a-row", action="store_true",
+                    help="attention: time calls that follow each other without a gap instead of single calls with a cold L2")
     a = ap.parse_args()
     dev = torch.device("cuda:0")
     ops.load_library()
@@ -230,7 +254,8 @@ def main():
         if "gemm" in a.what:
             bench_gemms(cfg, a.m, timer, pk, dev, only=a.gemm_only)
         if "attention" in a.what:
-            bench_attention(cfg, timer, pk, dev, cases=[tuple(c) for c in a.attn_case] if a.attn_case else None)
+            bench_attention(cfg, timer, pk, dev, cases=[tuple(c) for c in a.attn_case] if a.attn_case else None,
+                            in_a_row=a.in_a_row)
         if "small" in a.what:
             bench_small(cfg, [m for m in a.m if m <= 2048], timer, pk, dev)
     if "prompt-step" in a.what:
