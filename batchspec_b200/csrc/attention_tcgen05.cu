@@ -1,8 +1,9 @@
 // Paged causal flash attention for long portions of prompts on the 5th-generation tensor cores (bfloat16,
 // head_dim 128, page sizes 8 / 16 / 32 / 64).
 //
-// A CTA owns 256 rows, (token, query head of one kv group) pairs of one request and one kv head, as two Q tiles
-// of 128 rows with a softmax warpgroup each, and walks the visible keys in tiles of 64:
+// One persistent CTA per SM works through items of 256 rows, (token, query head of one kv group) pairs of one
+// request and one kv head, as two Q tiles of 128 rows with a softmax warpgroup each, and walks an item's visible
+// keys in tiles of 64 (how the items are dealt and handed from role to role stands at the kernel):
 //   warp 0    TMA: K and V pages of the key tile into a four-stage ring (one box per page and 64-column half,
 //             128-byte swizzle, completion on an mbarrier), and the Q tiles;
 //   warps 1, 10   one thread each issues tcgen05.mma for Q tile 0 / 1:  S = Q K^T  (128 x 64 x 128, operands
@@ -17,8 +18,7 @@
 // takes here (M = 128, K = 16: 48 clocks at N = 64, 64 at N = 128): with P in tensor memory the P V product
 // fetches only V (32 clocks per instruction instead of 64), and the softmax threads write no shared memory.
 // The softmax of a tile never waits for the tensor core in the steady state: S of the next key tile is ready.
-// The issuing threads are two, in different
-// warps, because they share their schedulers with softmax warps whose long runs of independent instructions keep
+// The issuing threads are two, in different warps, because they share their schedulers with softmax warps whose long runs of independent instructions keep
 // them waiting some 300 cycles at every mbarrier they look at: with one thread for both Q tiles those waits and
 // the (blocking) issues of both tiles stood in one line, and that line was the kernel's critical path.
 // Tensor memory: 2 x 2 S buffers of 64 columns, 2 O accumulators of 128 (all 512 columns).  Every mbarrier wait is
