@@ -79,14 +79,15 @@ struct TileGeom {
 template <int HD>
 __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* Ks, __nv_bfloat16* Vs, const __nv_bfloat16* cache,
                                              const int* table, int table_page0, int k0, int k_lo, int k_end,
-                                             int page_size, int Hkv, int g) {
+                                             int page_size, int Hkv, int g, long long n_pages) {
   constexpr int CH = HD / 8;                     // 16-byte chunks per row
   const size_t page_elems = (size_t)Hkv * page_size * HD;
   for (int idx = threadIdx.x; idx < KT * CH; idx += NTHREADS) {
     const int row = idx / CH, ch = idx - row * CH;
     const int key = k0 + row;
-    const bool valid = key < k_end && key >= k_lo;
+    bool valid = key < k_end && key >= k_lo;
     const __nv_bfloat16* src = cache;
+    if (valid && !bspec::in_range(table[key / page_size - table_page0], n_pages, 108)) valid = false;   // (checked build)
     if (valid) {
       const int pi = key / page_size;
       const int page = table[pi - table_page0];
@@ -315,7 +316,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride, 
                    const __nv_bfloat16* __restrict__ cache, const int* __restrict__ qo_indptr,
                    const int* __restrict__ positions, const int* __restrict__ kv_indptr,
                    const int* __restrict__ kv_indices, int Hq, int Hkv, int page_size, float scale_log2, int window,
-                   int n_splits, int row_tiles, int max_q_short) {
+                   int n_splits, int row_tiles, int max_q_short, long long n_pages) {
   bspec::pdl_prologue(8);
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);           // [16][HD]
@@ -369,7 +370,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride, 
     load_q_tile<HD>(Qs, q, q_row_stride, t, row0, 16);
     __syncthreads();
     const int n_tiles = (k_end - k_begin + KT - 1) / KT;
-    load_kv_tile<HD>(KV, KV + KT * HD, cache, table, table_page0, k_begin, lo_key, k_end, page_size, Hkv, g);
+    load_kv_tile<HD>(KV, KV + KT * HD, cache, table, table_page0, k_begin, lo_key, k_end, page_size, Hkv, g, n_pages);
     cp_async_commit();
     uint32_t qf[HD / 16][4];
     {
@@ -384,7 +385,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride, 
       if (it + 1 < n_tiles) {
         __nv_bfloat16* Kn = KV + ((it + 1) & 1) * 2 * KT * HD;
         load_kv_tile<HD>(Kn, Kn + KT * HD, cache, table, table_page0, k_begin + (it + 1) * KT, lo_key, k_end,
-                         page_size, Hkv, g);
+                         page_size, Hkv, g, n_pages);
         cp_async_commit();
         cp_async_wait<1>();
       } else {
@@ -1282,7 +1283,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
                     const __nv_bfloat16* __restrict__ cache, const int* __restrict__ qo_indptr,
                     const int* __restrict__ positions, const int* __restrict__ kv_indptr,
                     const int* __restrict__ kv_indices, int Hq, int Hkv, int page_size, float scale_log2, int window,
-                    int min_q_long) {
+                    int min_q_long, long long n_pages) {
   bspec::pdl_prologue(9);
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);           // [64][HD]
@@ -1322,7 +1323,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
 
   load_q_tile<HD>(Qs, q, q_row_stride, t, row0, 64);
   const int n_tiles = (k_end - k_begin + KT - 1) / KT;
-  load_kv_tile<HD>(KV, KV + KT * HD, cache, table, 0, k_begin, lo_key, k_end, page_size, Hkv, g);
+  load_kv_tile<HD>(KV, KV + KT * HD, cache, table, 0, k_begin, lo_key, k_end, page_size, Hkv, g, n_pages);
   cp_async_commit();
   __syncthreads();
   uint32_t qf[HD / 16][4];
@@ -1337,7 +1338,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
     __nv_bfloat16* Vs = Ks + KT * HD;
     if (it + 1 < n_tiles) {
       __nv_bfloat16* Kn = KV + ((it + 1) & 1) * 2 * KT * HD;
-      load_kv_tile<HD>(Kn, Kn + KT * HD, cache, table, 0, k_begin + (it + 1) * KT, lo_key, k_end, page_size, Hkv, g);
+      load_kv_tile<HD>(Kn, Kn + KT * HD, cache, table, 0, k_begin + (it + 1) * KT, lo_key, k_end, page_size, Hkv, g, n_pages);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -1384,7 +1385,8 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
            int* tile_counters, int* status, long long kv_rows, const __nv_bfloat16* cache, const int* qo_indptr, const int* positions, const int* tok_entry,
            const int* kv_indptr, const int* kv_indices, int n_entries, int n_tokens, int max_q_len, int Hq, int Hkv,
            int page_size, float scale, int window, int n_splits, int max_q_short, int run_decode, int run_prefill,
-           cudaStream_t stream, int balanced = 0, const int* kv_len = nullptr) {
+           cudaStream_t stream, int balanced = 0, const int* kv_len = nullptr,
+           long long check_pages = 0x7fffffffffffll) {
   const float scale_log2 = scale * 1.4426950408889634f;
   const int G = Hq / Hkv;
   // The opt-in to large shared memory and the resident-CTA count are facts of a device: set up once per device,
@@ -1436,7 +1438,7 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
     if (!launched)
       BSPEC_LAUNCH((attn_decode_kernel<HD>), grid, NTHREADS, decode_smem<HD>(), stream,
                    q, q_row_stride, out, o_part, ml_part, tile_counters, cache, qo_indptr, positions, kv_indptr,
-                   kv_indices, Hq, Hkv, page_size, scale_log2, window, n_splits, row_tiles, max_q_short);
+                   kv_indices, Hq, Hkv, page_size, scale_log2, window, n_splits, row_tiles, max_q_short, check_pages);
     const int err = (int)cudaGetLastError();
     if (err) return err;
   }
@@ -1459,7 +1461,7 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
       dim3 grid((max_q_len * G + 63) / 64, Hkv, n_entries);
       BSPEC_LAUNCH((attn_prefill_kernel<HD>), grid, NTHREADS, prefill_smem<HD>(), stream,
                    q, q_row_stride, out, cache, qo_indptr, positions, kv_indptr, kv_indices, Hq, Hkv, page_size,
-                   scale_log2, window, max_q_short + 1);
+                   scale_log2, window, max_q_short + 1, check_pages);
     }
     return (int)cudaGetLastError();
   }
@@ -1478,20 +1480,21 @@ int launch(const __nv_bfloat16* q, long long q_row_stride, __nv_bfloat16* out, f
 // kernel that gives every CTA an equal share of all key tiles.  n_splits is then the most partial results a row
 // tile may get, and the scratch is indexed by request (o_part [n_entries * min(max_q_len, max_q_short) * Hq *
 // n_splits * hd], ml_part likewise).  kv_len (may be null): [n_entries] each request's length after this step, which saves
-// those kernels the dependent load of positions[qo_indptr[e]].
+// those kernels the dependent load of positions[qo_indptr[e]].  pages_in_all: pages of the cache layer whether or
+// not n_pages is given (the checked build compares the page ids that the plain-copy kernels read with it; 0: unknown).
 BSPEC_API int bspec_attention_bf16(const void* q, long long q_row_stride, void* out, float* o_part, float* ml_part,
                                    int* tile_counters, int* status, long long n_pages, const void* cache, const int* qo_indptr, const int* positions,
                                    const int* tok_entry, const int* kv_indptr, const int* kv_indices, int n_entries,
                                    int n_tokens, int max_q_len, int Hq, int Hkv, int hd, int page_size, float scale,
                                    int window, int n_splits, int max_q_short, int run_decode, int run_prefill,
-                                   int balanced, const int* kv_len, cudaStream_t stream) {
+                                   int balanced, const int* kv_len, long long pages_in_all, cudaStream_t stream) {
   if (n_entries <= 0 || n_tokens <= 0) return 0;
   if (Hq % Hkv != 0 || n_splits < 1 || n_splits > 64) return (int)cudaErrorInvalidValue;
 #define GO(HDV)                                                                                                    \
   return launch<HDV>((const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, o_part, ml_part, tile_counters,   \
                      status, n_pages * 2 * Hkv * page_size, (const __nv_bfloat16*)cache, qo_indptr, positions, tok_entry, kv_indptr, kv_indices, n_entries, \
                      n_tokens, max_q_len, Hq, Hkv, page_size, scale, window, n_splits, max_q_short, run_decode,      \
-                     run_prefill, stream, balanced, kv_len)
+                     run_prefill, stream, balanced, kv_len, pages_in_all > 0 ? pages_in_all : 0x7fffffffffffll)
   if (hd == 64) GO(64);
   if (hd == 128) GO(128);
   if (hd == 256) GO(256);
@@ -1586,3 +1589,4 @@ BSPEC_API int bspec_attention_decode_noalloc(const void* q, long long q_row_stri
 }
 
 BSPEC_DEFINE_TRACE_SETTER(bspec_trace_set_attention_bf16)
+BSPEC_DEFINE_BOUNDS_REPORT(bspec_bounds_report_attention_bf16)

@@ -95,7 +95,7 @@ __device__ __forceinline__ void trace_mark(int kid, unsigned long long t_from) {
 // {code, value, limit, block} and the access is skipped: a wrong table then costs a wrong result and a report,
 // not a fault.  Each translation unit has its own record; BSPEC_DEFINE_BOUNDS_REPORT exports its reader.
 // Codes: 101 token id (embedding), 102 row (gather), 103 block-table slot and 104 page id (rotary + cache append),
-// 105 / 106 the same in the q/k/v product's epilogue, 107 page id (attention over plain loads).  Copies through
+// 105 / 106 the same in the q/k/v product's epilogue, 107 / 108 page id (attention over plain loads, float32 / bfloat16).  Copies through
 // TMA need no such check: the tensor map clips them.
 #ifdef BSPEC_BOUNDS
 static __device__ int g_bounds[4] = {0, 0, 0, 0};

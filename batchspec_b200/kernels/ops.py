@@ -50,7 +50,7 @@ _SIGNATURES = {
                                 c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_longlong, c_void_p],
     "bspec_attention_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong,
                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                             c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+                             c_int, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p],
     "bspec_gemm_tc_plan": [c_int, c_int, c_int, c_int, c_void_p],
     "bspec_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
     "bspec_gemm_tc_qkv_rope": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
@@ -423,7 +423,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, c
             qkv.data_ptr(), qkv.stride(0), out.data_ptr(), o_part, ml_part, counters, status,
             cache.shape[0] if tma else 0, cache.data_ptr(), qo, pos, tok_entry, kv_indptr, kv_indices, ctx.n_entries,
             ctx.n_tokens, ctx.max_q_len, n_heads, n_kv_heads, head_dim, tables.page_size, float(scale), int(window),
-            n_splits, short, run_decode, run_prefill, balanced, kv_len, _stream()), "attention_bf16")
+            n_splits, short, run_decode, run_prefill, balanced, kv_len, cache.shape[0], _stream()), "attention_bf16")
         global _launches
         _launches += 1 if run_decode and run_prefill else 0
         return
@@ -478,10 +478,11 @@ def check_status() -> None:
 
 
 _BOUNDS_REPORTS = ["bspec_bounds_report_elementwise", "bspec_bounds_report_gemm_tcgen05",
-                   "bspec_bounds_report_attention_generic"]
+                   "bspec_bounds_report_attention_generic", "bspec_bounds_report_attention_bf16"]
 BOUNDS_CODES = {101: "token id (embedding)", 102: "row (gather)", 103: "block-table slot (rotary + cache append)",
                 104: "page id (rotary + cache append)", 105: "block-table slot (q/k/v product's epilogue)",
-                106: "page id (q/k/v product's epilogue)", 107: "page id (attention over plain loads)"}
+                106: "page id (q/k/v product's epilogue)", 107: "page id (attention over plain loads)",
+                108: "page id (bfloat16 attention over plain loads)"}
 
 
 def bounds_reports() -> list:
