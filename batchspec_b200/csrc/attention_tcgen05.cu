@@ -82,6 +82,14 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&v)[32])
         "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31]), "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15};"
+      ::"r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+        "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ float ex2(float x) {          // 2^x on the special-function unit; 2^-inf = 0
@@ -531,43 +539,31 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_
         uint32_t packed[32];
         const uint64_t scale2 = pack2(scale_log2, scale_log2), neg_m2 = pack2(neg_m, neg_m);
         uint64_t l2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
-        if (need_mask) {                     // masked scores are -inf: their exponentials must be exactly 0
+        // Scaling and the row sum handle two values per instruction (fma/add.f32x2); the exponentials all go to the
+        // special-function unit (masked scores are -inf and come out as exactly 0).  Each half of P goes back into
+        // tensor memory as soon as it is complete, over the first half of the S buffer this thread has just read,
+        // so that the store's latency runs under the second half's arithmetic: the P V product takes its A
+        // operand from there.  What the columns held before (P of the key tile two before this one) was read by
+        // a product that was issued, and so completed, before this S.  (The threads of a warp may have taken
+        // different paths through the maximum above: they meet again before the warp-wide store.)
+        __syncwarp();
 #pragma unroll
-          for (int c = 0; c < 2; ++c)
+        for (int c = 0; c < 2; ++c) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              float p0, p1;
-              unpack2(fma2(pack2(__uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1])), scale2, neg_m2), p0, p1);
-              p0 = ex2(p0);
-              p1 = ex2(p1);
-              l2[(i >> 1) & 1] = add2(l2[(i >> 1) & 1], pack2(p0, p1));
-              __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
-              packed[16 * c + (i >> 1)] = *reinterpret_cast<uint32_t*>(&hh);
-            }
-        } else {
-          // Scaling and the row sum handle two values per instruction (fma/add.f32x2); the exponentials all go
-          // to the special-function unit (with P in shared memory a quarter of them, computed as a cubic on the
-          // FMA pipe, paid; with P in tensor memory the softmax is bound by the instructions it issues).
-#pragma unroll
-          for (int c = 0; c < 2; ++c)
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              float p0, p1;
-              unpack2(fma2(pack2(__uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1])), scale2, neg_m2), p0, p1);
-              p0 = ex2(p0);
-              p1 = ex2(p1);
-              l2[(i >> 1) & 1] = add2(l2[(i >> 1) & 1], pack2(p0, p1));
-              __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
-              packed[16 * c + (i >> 1)] = *reinterpret_cast<uint32_t*>(&hh);
-            }
+          for (int i = 0; i < 32; i += 2) {
+            float p0, p1;
+            unpack2(fma2(pack2(__uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1])), scale2, neg_m2), p0, p1);
+            p0 = ex2(p0);
+            p1 = ex2(p1);
+            l2[(i >> 1) & 1] = add2(l2[(i >> 1) & 1], pack2(p0, p1));
+            __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+            packed[16 * c + (i >> 1)] = *reinterpret_cast<uint32_t*>(&hh);
+          }
+          tc_st16(s_addr + 16u * c, packed + 16 * c);
         }
         float la, lb;
         unpack2(add2(l2[0], l2[1]), la, lb);
         l += la + lb;
-        // P goes back into tensor memory, over the first half of the S buffer this thread has just read: the P V
-        // product takes its A operand from there.  What the columns held before (P of the key tile two before
-        // this one) was read by a product that was issued, and so completed, before this S.
-        tc_st32(s_addr, packed);
         // rescale this row of O if its scale moved (the warp decides together: the TMEM access is warp-wide); the
         // P V of key tile j - 1 must have completed before O is touched
         if (j >= 1 && __any_sync(0xffffffffu, corr != 1.f)) {
