@@ -492,8 +492,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_
         if (lane == 0) mbar_arrive(q_ready + tt);
       }
       // m_ref: the maximum the probabilities and O are currently scaled by.  It follows the true running maximum
-      // lazily: O and l are rescaled only when the maximum has grown by more than 8 (a factor 256, harmless in
-      // float32 and bfloat16), which after the first tiles is rare.
+      // lazily: it is looked for again only when a tile's probabilities sum to more than 2^14, and O and l are then
+      // rescaled if it has grown by more than 8; after the first tiles of an item that is rare.
       float m_ref = -INFINITY, l = 0.f;
       for (int j = 0; j < my_tiles && ok; ++j) {
         const uint32_t n = sq + (uint32_t)j, b = n & 1u;
@@ -508,62 +508,76 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_
         tc_ld32(s_addr, sv[0]);
         tc_ld32(s_addr + 32u, sv[1]);
         tc_wait_ld();
-        // maximum of the raw scores (the scale is positive), masked entries set to -inf in place
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        if (need_mask) {                     // a tile on the diagonal, at the window's edge or at the end of the keys
+        // P = 2^(scale * S - m) for the row, its sum returned; scaling and the row sum handle two values per
+        // instruction (fma/add.f32x2), the exponentials all go to the special-function unit (masked scores are -inf
+        // and come out as exactly 0).  Each half of P goes back into tensor memory as soon as it is complete, over
+        // the first half of the S buffer this thread has just read, so that the store's latency runs under the
+        // second half's arithmetic: the P V product takes its A operand from there.  What the columns held before
+        // (P of the key tile two before this one) was read by a product that was issued, and so completed, before
+        // this S.  The stores are warp-wide: every path to this point is taken by the whole warp.
+        auto exponentials = [&](float neg_m) -> float {
+          uint32_t packed[32];
+          const uint64_t scale2 = pack2(scale_log2, scale_log2), neg_m2 = pack2(neg_m, neg_m);
+          uint64_t l2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
 #pragma unroll
-          for (int c = 0; c < 2; ++c)
+          for (int c = 0; c < 2; ++c) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int key = key0 + 32 * c + i;
-              if (!(key <= lim && key >= lo && key < my_k_end)) sv[c][i] = 0xff800000u;      // -inf
-              mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[c][i]));
+            for (int i = 0; i < 32; i += 2) {
+              float p0, p1;
+              unpack2(fma2(pack2(__uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1])), scale2, neg_m2), p0, p1);
+              p0 = ex2(p0);
+              p1 = ex2(p1);
+              l2[(i >> 1) & 1] = add2(l2[(i >> 1) & 1], pack2(p0, p1));
+              __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+              packed[16 * c + (i >> 1)] = *reinterpret_cast<uint32_t*>(&hh);
             }
-        } else {                             // most tiles: no comparisons of key indices at all
-#pragma unroll
-          for (int c = 0; c < 2; ++c)
-#pragma unroll
-            for (int i = 0; i < 32; i += 2)
-              mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1]));
-        }
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
-        float corr = 1.f;
-        if (mx > m_ref + 8.f || m_ref == -INFINITY) {           // (also the first tile that holds a visible key)
-          const float m_new = fmaxf(m_ref, mx);
-          corr = (m_new == -INFINITY) ? 1.f : ex2(m_ref - m_new);   // m_ref = -inf: O and l are still 0
-          m_ref = m_new;
-          l *= corr;
-        }
-        const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
-        // exponentials first (they do not need P's buffer), then wait until the previous P V has completed
-        uint32_t packed[32];
-        const uint64_t scale2 = pack2(scale_log2, scale_log2), neg_m2 = pack2(neg_m, neg_m);
-        uint64_t l2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
-        // Scaling and the row sum handle two values per instruction (fma/add.f32x2); the exponentials all go to the
-        // special-function unit (masked scores are -inf and come out as exactly 0).  Each half of P goes back into
-        // tensor memory as soon as it is complete, over the first half of the S buffer this thread has just read,
-        // so that the store's latency runs under the second half's arithmetic: the P V product takes its A
-        // operand from there.  What the columns held before (P of the key tile two before this one) was read by
-        // a product that was issued, and so completed, before this S.  (The threads of a warp may have taken
-        // different paths through the maximum above: they meet again before the warp-wide store.)
-        __syncwarp();
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float p0, p1;
-            unpack2(fma2(pack2(__uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1])), scale2, neg_m2), p0, p1);
-            p0 = ex2(p0);
-            p1 = ex2(p1);
-            l2[(i >> 1) & 1] = add2(l2[(i >> 1) & 1], pack2(p0, p1));
-            __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
-            packed[16 * c + (i >> 1)] = *reinterpret_cast<uint32_t*>(&hh);
+            tc_st16(s_addr + 16u * c, packed + 16 * c);
           }
-          tc_st16(s_addr + 16u * c, packed + 16 * c);
+          float la, lb;
+          unpack2(add2(l2[0], l2[1]), la, lb);
+          return la + lb;
+        };
+        // Most tiles need no new maximum: the probabilities are formed with the maximum the row is scaled by already,
+        // and their sum tells whether that was safe.  A sum of at most 2^14 bounds every one of them by 2^14, which
+        // float32 and bfloat16 carry without loss; a larger one (or infinity) sends the warp through the full
+        // path below, as do the first tile of an item and tiles that need a mask.
+        float corr = 1.f, row_sum = 0.f;
+        bool full_path = __any_sync(0xffffffffu, need_mask || m_ref == -INFINITY);
+        if (!full_path) {
+          row_sum = exponentials(-m_ref);
+          full_path = __any_sync(0xffffffffu, !(row_sum <= 16384.f));
+          if (full_path) tc_wait_st();          // the stores above land before the ones that replace them
         }
-        float la, lb;
-        unpack2(add2(l2[0], l2[1]), la, lb);
-        l += la + lb;
+        if (full_path) {
+          // maximum of the raw scores (the scale is positive), masked entries set to -inf in place
+          float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+          if (need_mask) {                   // a tile on the diagonal, at the window's edge or at the end of the keys
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const int key = key0 + 32 * c + i;
+                if (!(key <= lim && key >= lo && key < my_k_end)) sv[c][i] = 0xff800000u;      // -inf
+                mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[c][i]));
+              }
+          } else {
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+#pragma unroll
+              for (int i = 0; i < 32; i += 2)
+                mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1]));
+          }
+          const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+          if (mx > m_ref + 8.f || m_ref == -INFINITY) {         // (also the first tile that holds a visible key)
+            const float m_new = fmaxf(m_ref, mx);
+            corr = (m_new == -INFINITY) ? 1.f : ex2(m_ref - m_new);   // m_ref = -inf: O and l are still 0
+            m_ref = m_new;
+            l *= corr;
+          }
+          __syncwarp();
+          row_sum = exponentials((m_ref == -INFINITY) ? 0.f : -m_ref);
+        }
+        l += row_sum;
         // rescale this row of O if its scale moved (the warp decides together: the TMEM access is warp-wide); the
         // P V of key tile j - 1 must have completed before O is touched
         if (j >= 1 && __any_sync(0xffffffffu, corr != 1.f)) {
