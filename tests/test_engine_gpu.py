@@ -225,6 +225,16 @@ def test_captured_decode_steps_equal_plain_ones(tmp_path, dtype):
         outs[graphs] = {s.seq_id: s.output_ids for s in done}
         if graphs:
             assert any(g.graph is not None for g in eng._graphs.values()), "no decode step was captured"
+            # the same generation with every captured step timed on the device: same tokens, one time per decode
+            # step; in sum no longer than the steps' wall time (a step launched ahead starts inside the wall time
+            # of the step before it, so the two are not comparable step by step)
+            eng.time_decode_on_device = True
+            again = eng.generate([Sequence(i, p, max_new_tokens=40) for i, p in enumerate(prompts)])
+            assert {s.seq_id: s.output_ids for s in again} == outs[True]
+            st = eng.last_stats
+            assert len(st["decode_step_device_ms"]) == len(st["decode_step_ms"]) > 0
+            assert all(d > 0.0 for d in st["decode_step_device_ms"])
+            assert sum(st["decode_step_device_ms"]) <= sum(st["decode_step_ms"]) + 0.1
     assert outs[True] == outs[False]
 
 
